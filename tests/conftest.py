@@ -1,0 +1,25 @@
+import os
+import sys
+
+import pytest
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+GOLDEN = os.path.join(ROOT, "tests", "golden")
+
+
+def pytest_configure(config):
+    config.addinivalue_line("markers", "gpu: needs a CUDA device (run on a B200)")
+
+
+@pytest.fixture(autouse=True)
+def _reset_dispatch_failure():
+    """Every test starts in 'warn' mode, as in the reference's conftest.py:4-7."""
+    try:
+        import sten_b200
+        sten_b200.set_dispatch_failure("warn")
+    except Exception:
+        pass
+    yield
