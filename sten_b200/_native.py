@@ -1,0 +1,66 @@
+"""ctypes binding of ``libnmg_b200.so`` (the C ABI declared in ``include/nmg_b200.h``).
+
+The library is the only implementation of the arithmetic: if it cannot be loaded, or a tensor is not on a
+CUDA device, the operations raise -- there is no CPU or eager-PyTorch fallback.
+"""
+import ctypes
+import os
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_HERE, "libnmg_b200.so")
+
+NMG_F32, NMG_F16, NMG_BF16 = 0, 1, 2
+NMG_ACT_TOKEN_MAJOR, NMG_ACT_K_MAJOR = 0, 1
+NMG_ALGO_AUTO, NMG_ALGO_SIMT, NMG_ALGO_TENSOR = 0, 1, 2
+
+# name -> (restype, argtypes); must list every function of include/nmg_b200.h (checked by the test-suite)
+_i64, _int, _vp, _sz = ctypes.c_int64, ctypes.c_int, ctypes.c_void_p, ctypes.c_size_t
+SIGNATURES = {
+    "nmg_version": (_int, []),
+    "nmg_last_error": (ctypes.c_char_p, []),
+    "nmg_num_patterns": (_i64, [_int, _int]),
+    "nmg_pattern_order": (_int, [_int, _int, _vp]),
+    "nmg_sparsify": (_int, [_vp, _i64, _i64, _i64, _i64, _i64, _int, _int, _int, _int, _vp, _vp, _vp]),
+    "nmg_densify": (_int, [_vp, _vp, _i64, _i64, _i64, _int, _int, _int, _int, _vp, _i64, _i64, _vp]),
+    "nmg_spmm_workspace_bytes": (_sz, [_i64, _i64, _i64, _int, _int, _int, _int, _int, _int]),
+    "nmg_spmm": (_int, [_vp, _vp, _i64, _i64, _int, _int, _int, _int, _vp, _i64, _i64, _vp, _vp, _i64, _int, _int,
+                        _vp, _sz, _vp]),
+    "nmg_spmm_t_workspace_bytes": (_sz, [_i64, _i64, _i64, _int, _int, _int, _int, _int]),
+    "nmg_spmm_t": (_int, [_vp, _vp, _i64, _i64, _int, _int, _int, _int, _vp, _i64, _i64, _vp, _i64, _int, _vp, _sz,
+                          _vp]),
+    "nmg_profile_next": (_int, [_vp, _vp]),
+    "nmg_measure_fma_peak": (_int, [ctypes.POINTER(ctypes.c_double), _vp]),
+    "nmg_read_status": (_int, [_vp, ctypes.POINTER(_int)]),
+}
+
+_lib = None
+
+
+class NmgError(RuntimeError):
+    """A call into libnmg_b200.so returned a non-zero status."""
+
+    def __init__(self, status, message):
+        super().__init__(f"nmg_b200 status {status}: {message}")
+        self.status = status
+
+
+def lib():
+    """Load the library once.  Raises (never falls back) when it has not been built."""
+    global _lib
+    if _lib is None:
+        if not os.path.isfile(LIB_PATH):
+            raise ImportError(
+                f"{LIB_PATH} is missing: build it with `python -m sten_b200.build` (needs nvcc). "
+                "sten_b200 has no CPU or PyTorch fallback for the grouped n:m kernels.")
+        L = ctypes.CDLL(LIB_PATH)
+        for name, (res, args) in SIGNATURES.items():
+            fn = getattr(L, name)
+            fn.restype = res
+            fn.argtypes = args
+        _lib = L
+    return _lib
+
+
+def check(status):
+    if status != 0:
+        raise NmgError(status, lib().nmg_last_error().decode(errors="replace"))

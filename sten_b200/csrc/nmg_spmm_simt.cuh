@@ -1,0 +1,95 @@
+// Declarations shared by the matmul translation units.
+#pragma once
+#include "nmg_common.cuh"
+
+namespace nmg {
+
+inline int64_t round_up(int64_t a, int64_t b) { return (a + b - 1) / b * b; }
+
+// Activation re-layout pre-pass: src[rows][ld_src] (dtype) -> dst[cols][ld_dst] fp32, i.e. transpose + widen.
+int launch_transpose_to_f32(const void *src, int dtype, int64_t rows, int64_t cols, int64_t ld_src, float *dst,
+                            int64_t ld_dst, cudaStream_t st);
+// Copy + widen without transposing: src[rows][ld_src] (dtype) -> dst[rows][ld_dst] fp32.
+int launch_widen_to_f32(const void *src, int dtype, int64_t rows, int64_t cols, int64_t ld_src, float *dst,
+                        int64_t ld_dst, cudaStream_t st);
+
+// Column-order ("natural") copy of a weight: for every row-block mb and column k of the padded width Kp,
+// pat[mb][k] = pattern of that column, nval[mb][k][s] = its n kept values.
+int64_t natural_width(const Geo &geo);
+size_t natural_bytes(const Geo &geo, int dtype, size_t *pat_bytes_out);
+int launch_build_natural(const Geo &geo, int dtype, const void *val, const int16_t *idx, uint16_t *pat, void *nval,
+                         cudaStream_t st);
+
+// SIMT kernels (fp32 accumulate).  xt is the activation as [K][ld_xt] fp32 (tokens contiguous).
+size_t simt_fwd_workspace_bytes(const Geo &geo, int64_t tokens, int dtype, int layout);
+int simt_fwd(const Geo &geo, int dtype, const void *val, const int16_t *idx, const void *act, int64_t ld_act,
+             int64_t tokens, const void *bias, void *out, int64_t ld_out, int layout, void *ws, size_t ws_bytes,
+             cudaStream_t st);
+size_t simt_bwd_workspace_bytes(const Geo &geo, int64_t tokens, int dtype);
+int simt_bwd(const Geo &geo, int dtype, const void *val, const int16_t *idx, const void *dy, int64_t ld_dy,
+             int64_t tokens, void *dx, int64_t ld_dx, void *ws, size_t ws_bytes, cudaStream_t st);
+
+// ---- specialised forward kernel: parameters, shared-memory plan, per-(n, m) launchers
+struct FwdParams {
+    const void *val;
+    const int16_t *idx;
+    const void *bias;
+    void *out;
+    int64_t M, K, ntok, ld_out;
+    int64_t nb, nc;
+    int g, cc;
+    int box_rows, nbox;  // TMA boxes per chunk: nbox boxes of box_rows activation rows
+    int stages;
+    int *status;
+};
+
+constexpr int kWarps = 8;
+
+struct FwdSmemPlan {
+    size_t x_bytes, v_bytes, i_bytes, stage_bytes, total;
+};
+__host__ __device__ inline FwdSmemPlan fwd_smem_plan(int cc, int n, int rbc, int tokc, int nbox, int box_rows, size_t es, int stages) {
+    FwdSmemPlan p;
+    p.x_bytes = (size_t)nbox * box_rows * tokc * 4;
+    p.v_bytes = (((size_t)rbc * cc * n * es + 32) + 127) & ~(size_t)127;
+    p.i_bytes = (((size_t)rbc * cc * 2 + 32) + 127) & ~(size_t)127;
+    p.stage_bytes = p.x_bytes + p.v_bytes + p.i_bytes;
+    p.total = p.stage_bytes * stages + 128 /*barriers*/ + 128 /*alignment slack*/;
+    return p;
+}
+
+template <int N_, int M_>
+int simt_fwd_launch(int dtype, int tt, const FwdParams &p, const CUtensorMap &tm, int rbc, size_t smem, bool token_major,
+                    int64_t tokens, cudaStream_t st);
+
+// ---- specialised transposed kernel: parameters, shared-memory plan, per-(n, m) launchers
+struct BwdParams {
+    const uint16_t *pat;  // [nb][Kp]
+    const void *nval;     // [nb][Kp][n]
+    void *dx;
+    int64_t M, K, Kp, ntok, ld_dx, nb;
+    int rb_stage;    // row-blocks per pipeline stage
+    int *status;
+};
+
+constexpr int kBwdWarps = 8;
+constexpr int kKW = 16;                      // columns per warp
+constexpr int kColsCta = kBwdWarps * kKW;    // 128 columns per CTA
+constexpr int kBwdTT = 4;
+constexpr int kBwdTok = 32 * kBwdTT;         // 128 tokens per CTA
+
+struct BwdSmemPlan { size_t y_bytes, p_bytes, v_bytes, stage_bytes, total; };
+__host__ __device__ inline BwdSmemPlan bwd_smem_plan(int m, int n, int rb_stage, size_t es) {
+    BwdSmemPlan p;
+    p.y_bytes = (size_t)rb_stage * m * kBwdTok * 4;
+    p.p_bytes = ((size_t)rb_stage * kColsCta * 2 + 127) & ~(size_t)127;
+    p.v_bytes = ((size_t)rb_stage * kColsCta * n * es + 127) & ~(size_t)127;
+    p.stage_bytes = p.y_bytes + p.p_bytes + p.v_bytes;
+    p.total = 2 * p.stage_bytes + 256;
+    return p;
+}
+
+template <int N_, int M_>
+int simt_bwd_launch(int dtype, const BwdParams &p, const CUtensorMap &tm, int64_t tokens, cudaStream_t st);
+
+}  // namespace nmg

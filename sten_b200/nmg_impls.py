@@ -1,0 +1,131 @@
+"""The grouped n:m plugin: sparsifier and operator registrations (reference: src/sten/grouped_nm/sten_impls.py).
+
+Registered here, all backed by ``libnmg_b200.so``:
+
+* ``GroupedNMSparsifier`` : ``torch.Tensor -> GroupedNMTensor``                    (reference sten_impls.py:13-37)
+* ``F.linear``  forward for ``(Tensor, GroupedNMTensor, Tensor)`` -- the reference's only operator (:143-174) -- and for
+  ``(Tensor, GroupedNMTensor)``: a bias-free linear has two tensor inputs and would otherwise miss the registration
+  and silently densify;
+* ``torch.mm`` / ``torch.matmul`` forward for ``(GroupedNMTensor, Tensor)``;
+* the matching backward entries (``dX = dY W`` through the transposed kernel); the reference has none and installs a
+  failing stub (sten.py:1690-1693).
+
+Unlike the reference (sten_impls.py:53, which derives the transpose flag from contiguity and ends up reading a
+contiguous ``[tokens, K]`` activation as ``[K, tokens]``), the activation layout is stated explicitly:
+``F.linear`` is ``y = x W^T + b`` on ``x[tokens, K]``.
+"""
+import torch
+
+from . import _native as nat
+from . import dispatch as sten
+from . import ops
+from .grouped_nm_tensor import GroupedNMTensor
+
+
+class GroupedNMSparsifier:
+    def __init__(self, n, m, g):
+        self.n = n
+        self.m = m
+        self.g = g
+
+
+@sten.register_sparsifier_implementation(sparsifier=GroupedNMSparsifier, inp=torch.Tensor, out=GroupedNMTensor)
+def dense_to_grouped_nm(sparsifier, tensor, grad_fmt=None):
+    gnm = GroupedNMTensor.from_dense(tensor, sparsifier.n, sparsifier.m, sparse_dim=tensor.ndim - 2,
+                                     group_size=sparsifier.g, group_dim=tensor.ndim - 1)
+    return sten.SparseTensorWrapper.wrapped_from_dense(gnm, tensor, grad_fmt)
+
+
+@sten.register_sparsifier_implementation(sparsifier=sten.SameFormatSparsifier, inp=torch.Tensor, out=GroupedNMTensor)
+def dense_to_same_grouped_nm(sparsifier, tensor, grad_fmt=None):
+    """Re-sparsify a dense result with the (n, m, g, dims) of the reference tensor (fresh magnitude selection)."""
+    ref = sparsifier.ref_sp_ten
+    s = ref.wrapped_tensor.nm_strides
+    gnm = GroupedNMTensor.from_dense(tensor, s["n"], s["m"], sparse_dim=s["sparse_dim"], group_size=s["group_size"],
+                                     group_dim=s["group_dim"])
+    return sten.SparseTensorWrapper.wrapped_from_dense(gnm, tensor, grad_fmt if grad_fmt is not None else ref.grad_fmt)
+
+
+def _weight_geometry(weight):
+    gnm = weight.wrapped_tensor
+    s = gnm.nm_strides
+    if len(s["dense_shape"]) != 2 or s["sparse_dim"] != 0 or s["group_dim"] != 1:
+        raise sten.DispatchError("grouped n:m matmul needs a 2-D weight with n:m blocks along dim 0 and groups along dim 1")
+    M, K = s["dense_shape"]
+    return gnm, int(M), int(K), s["n"], s["m"], s["group_size"]
+
+
+def sparse_dense_mul_dispatch(weight, dense2d, bias, layout):
+    """One C-ABI call; replaces the compile-or-load + ctypes call of the reference (sten_impls.py:44-140)."""
+    gnm, M, K, n, m, g = _weight_geometry(weight)
+    return ops.spmm(gnm.val, gnm.idx, M, K, n, m, g, dense2d, bias=bias, layout=layout)
+
+
+def _linear_fwd(ctx, inputs, output_sparsifiers):
+    if len(inputs) == 3:
+        x, weight, bias = inputs
+    else:
+        (x, weight), bias = inputs, None
+    ctx.save_for_backward(x, weight, bias) if bias is not None else ctx.save_for_backward(x, weight)
+    x2d = x.reshape(-1, x.shape[-1])
+    y = sparse_dense_mul_dispatch(weight, x2d, bias, nat.NMG_ACT_TOKEN_MAJOR)
+    return y.reshape(*x.shape[:-1], y.shape[-1])
+
+
+_LIN_OUT = [(sten.KeepAll, torch.Tensor)]
+sparse_torch_nn_functional_linear = sten.register_fwd_op_impl(
+    operator=torch.nn.functional.linear, inp=(torch.Tensor, GroupedNMTensor, torch.Tensor), out=_LIN_OUT)(_linear_fwd)
+sten.register_fwd_op_impl(operator=torch.nn.functional.linear, inp=(torch.Tensor, GroupedNMTensor), out=_LIN_OUT)(_linear_fwd)
+
+
+def _linear_bwd(ctx, grad_outputs, input_sparsifiers):
+    saved = ctx.saved_tensors
+    x, weight = saved[0], saved[1]
+    has_bias = len(saved) == 3
+    [dy] = grad_outputs
+    needs = tuple(ctx.needs_input_grad[1:]) + (False,) * 3
+    gnm, M, K, n, m, g = _weight_geometry(weight)
+    dy2d = dy.reshape(-1, M)
+    dx = dw = db = None
+    if needs[0]:
+        dx = ops.spmm_t(gnm.val, gnm.idx, M, K, n, m, g, dy2d).reshape(x.shape)
+    if needs[1]:
+        # dense weight gradient (training of nmg weights is outside the inference hot path): plain GEMM
+        dw = dy2d.t().mm(x.reshape(-1, K))
+    if has_bias and needs[2]:
+        db = dy2d.sum(dim=0)
+    return (dx, dw, db) if has_bias else (dx, dw)
+
+
+_DENSE_GRAD = (sten.KeepAll, torch.Tensor)
+for _inp in ((torch.Tensor, GroupedNMTensor, torch.Tensor), (torch.Tensor, GroupedNMTensor)):
+    sten.register_bwd_op_impl(operator=torch.nn.functional.linear, grad_out=(torch.Tensor,),
+                              grad_inp=tuple(_DENSE_GRAD for _ in _inp), inp=_inp)(_linear_bwd)
+
+
+def _mm_fwd(ctx, inputs, output_sparsifiers):
+    weight, b = inputs
+    ctx.save_for_backward(weight, b)
+    if b.dim() != 2:
+        raise sten.DispatchError("grouped n:m matmul expects a 2-D right operand")
+    return sparse_dense_mul_dispatch(weight, b, None, nat.NMG_ACT_K_MAJOR)
+
+
+def _mm_bwd(ctx, grad_outputs, input_sparsifiers):
+    weight, b = ctx.saved_tensors
+    [dc] = grad_outputs  # [M, N]
+    needs = tuple(ctx.needs_input_grad[1:]) + (False,) * 2
+    gnm, M, K, n, m, g = _weight_geometry(weight)
+    dw = db = None
+    if needs[0]:
+        dw = dc.mm(b.t())
+    if needs[1]:
+        # dB = W^T dC : the transposed kernel computes (dC^T W)[N, K]; hand back its transpose
+        db = ops.spmm_t(gnm.val, gnm.idx, M, K, n, m, g, dc.t().contiguous()).t()
+    return dw, db
+
+
+for _op in (torch.mm, torch.matmul):
+    sten.register_fwd_op_impl(operator=_op, inp=(GroupedNMTensor, torch.Tensor), out=_LIN_OUT)(_mm_fwd)
+    sten.register_bwd_op_impl(operator=_op, grad_out=(torch.Tensor,), grad_inp=(_DENSE_GRAD, _DENSE_GRAD),
+                              inp=(GroupedNMTensor, torch.Tensor))(_mm_bwd)

@@ -1,0 +1,151 @@
+"""Tensor-level entry points: torch tensors in, one C-ABI call, torch tensors out.
+
+torch is used for device memory (caching allocator), the current stream and nothing else; all arithmetic
+happens inside ``libnmg_b200.so``.
+"""
+import math
+
+import torch
+
+from . import _native as nat
+
+_DTYPES = {torch.float32: nat.NMG_F32, torch.float16: nat.NMG_F16, torch.bfloat16: nat.NMG_BF16}
+
+
+def _dtype_code(t):
+    try:
+        return _DTYPES[t.dtype]
+    except KeyError:
+        raise TypeError(f"grouped n:m kernels support float32, float16 and bfloat16, got {t.dtype}") from None
+
+
+def _require_cuda(*tensors):
+    dev = None
+    for t in tensors:
+        if t is None:
+            continue
+        if not t.is_cuda:
+            raise RuntimeError(
+                "grouped n:m kernels run on CUDA devices only (there is no CPU fallback); move the tensor with .cuda()")
+        if dev is None:
+            dev = t.device
+        elif t.device != dev:
+            raise RuntimeError(f"operands live on different devices: {dev} and {t.device}")
+    return dev
+
+
+def _stream(dev):
+    return torch.cuda.current_stream(dev).cuda_stream
+
+
+def _workspace(nbytes, dev):
+    if nbytes == 0:
+        return None, 0
+    ws = torch.empty(nbytes, dtype=torch.uint8, device=dev)
+    return ws, nbytes
+
+
+def geometry(M, K, n, m, g):
+    C = math.comb(m, n)
+    cc = C * g
+    nb, nc = -(-M // m), -(-K // cc)
+    return C, cc, nb, nc
+
+
+def sparsify(dense3, n, m, g):
+    """dense3: [B, M, K] view with unit stride along K.  Returns (val [T, C, g, n], idx [T, C, g, 1])."""
+    assert dense3.dim() == 3
+    dev = _require_cuda(dense3)
+    code = _dtype_code(dense3)
+    if dense3.stride(2) != 1 or (dense3.shape[0] > 1 and dense3.stride(0) < dense3.shape[1] * dense3.stride(1)):
+        dense3 = dense3.contiguous()
+    B, M, K = dense3.shape
+    C, cc, nb, nc = geometry(M, K, n, m, g)
+    T = B * nc * nb
+    val = torch.empty((T, C, g, n), dtype=dense3.dtype, device=dev)
+    idx = torch.empty((T, C, g, 1), dtype=torch.int16, device=dev)
+    with torch.cuda.device(dev):
+        nat.check(nat.lib().nmg_sparsify(dense3.data_ptr(), B, M, K, dense3.stride(1), dense3.stride(0), n, m, g, code,
+                                         val.data_ptr(), idx.data_ptr(), _stream(dev)))
+    return val, idx
+
+
+def densify(val, idx, B, M, K, n, m, g):
+    """Returns the dense [B, M, K] tensor of a (val, idx) pair."""
+    dev = _require_cuda(val, idx)
+    code = _dtype_code(val)
+    val, idx = val.contiguous(), idx.contiguous()
+    out = torch.empty((B, M, K), dtype=val.dtype, device=dev)
+    with torch.cuda.device(dev):
+        nat.check(nat.lib().nmg_densify(val.data_ptr(), idx.data_ptr(), B, M, K, n, m, g, code, out.data_ptr(), K,
+                                        M * K, _stream(dev)))
+    return out
+
+
+def _row_major_2d(t):
+    if t.dim() != 2:
+        raise ValueError("expected a 2-D tensor")
+    if t.stride(1) != 1 or t.stride(0) < t.shape[1]:
+        t = t.contiguous()
+    return t
+
+
+def spmm(val, idx, M, K, n, m, g, act, bias=None, layout=nat.NMG_ACT_TOKEN_MAJOR, algo=nat.NMG_ALGO_AUTO, out=None):
+    """layout TOKEN_MAJOR: act [tokens, K] -> out [tokens, M] = act @ W^T (+ bias)
+       layout K_MAJOR:     act [K, tokens] -> out [M, tokens] = W @ act   (+ bias per row)"""
+    dev = _require_cuda(val, idx, act, bias)
+    code = _dtype_code(val)
+    if act.dtype != val.dtype or (bias is not None and bias.dtype != val.dtype):
+        raise TypeError(f"activation / bias dtype must match the weight dtype {val.dtype}")
+    act = _row_major_2d(act)
+    token_major = layout == nat.NMG_ACT_TOKEN_MAJOR
+    tokens = act.shape[0] if token_major else act.shape[1]
+    if (act.shape[1] if token_major else act.shape[0]) != K:
+        raise ValueError(f"activation shape {tuple(act.shape)} does not match K={K}")
+    if out is None:
+        out = torch.empty((tokens, M) if token_major else (M, tokens), dtype=val.dtype, device=dev)
+    if tokens == 0:
+        return out
+    val, idx = val.contiguous(), idx.contiguous()
+    if bias is not None:
+        bias = bias.contiguous()
+    L = nat.lib()
+    with torch.cuda.device(dev):
+        ws, nbytes = _workspace(L.nmg_spmm_workspace_bytes(M, K, tokens, n, m, g, code, layout, algo), dev)
+        nat.check(L.nmg_spmm(val.data_ptr(), idx.data_ptr(), M, K, n, m, g, code, act.data_ptr(), act.stride(0), tokens,
+                             bias.data_ptr() if bias is not None else None, out.data_ptr(), out.stride(0), layout, algo,
+                             ws.data_ptr() if ws is not None else None, nbytes, _stream(dev)))
+    return out
+
+
+def spmm_t(val, idx, M, K, n, m, g, dy, algo=nat.NMG_ALGO_AUTO):
+    """dy [tokens, M] -> dx [tokens, K] = dy @ W."""
+    dev = _require_cuda(val, idx, dy)
+    code = _dtype_code(val)
+    if dy.dtype != val.dtype:
+        raise TypeError(f"gradient dtype must match the weight dtype {val.dtype}")
+    dy = _row_major_2d(dy)
+    tokens = dy.shape[0]
+    if dy.shape[1] != M:
+        raise ValueError(f"gradient shape {tuple(dy.shape)} does not match M={M}")
+    dx = torch.empty((tokens, K), dtype=val.dtype, device=dev)
+    if tokens == 0:
+        return dx
+    val, idx = val.contiguous(), idx.contiguous()
+    L = nat.lib()
+    with torch.cuda.device(dev):
+        ws, nbytes = _workspace(L.nmg_spmm_t_workspace_bytes(M, K, tokens, n, m, g, code, algo), dev)
+        nat.check(L.nmg_spmm_t(val.data_ptr(), idx.data_ptr(), M, K, n, m, g, code, dy.data_ptr(), dy.stride(0), tokens,
+                               dx.data_ptr(), dx.stride(0), algo, ws.data_ptr() if ws is not None else None, nbytes,
+                               _stream(dev)))
+    return dx
+
+
+def read_status(dev=None):
+    """Synchronise the current stream and raise if any kernel's bounded wait ran out."""
+    import ctypes
+    dev = dev if dev is not None else torch.device("cuda", torch.cuda.current_device())
+    code = ctypes.c_int(0)
+    with torch.cuda.device(dev):
+        nat.check(nat.lib().nmg_read_status(_stream(dev), ctypes.byref(code)))
+    return code.value

@@ -1,0 +1,70 @@
+"""The C-ABI library: it loads, exports every symbol the public header declares, and its host-side
+validation answers with status codes (no GPU needed for any call made here)."""
+import ctypes
+import os
+import re
+
+import numpy as np
+import pytest
+
+from conftest import ROOT
+from sten_b200 import _native as nat
+from sten_b200.layout import make_n_m
+
+
+def _declared():
+    text = open(os.path.join(ROOT, "include", "nmg_b200.h")).read()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    return sorted(set(re.findall(r"\b(nmg_[a-z_0-9]+)\s*\(", text)))
+
+
+def test_library_exports_every_declared_symbol():
+    L = nat.lib()
+    names = _declared()
+    assert len(names) >= 11
+    for name in names:
+        assert hasattr(L, name), f"{name} is declared in include/nmg_b200.h but not exported"
+        assert name in nat.SIGNATURES, f"{name} has no ctypes signature in sten_b200/_native.py"
+    assert set(nat.SIGNATURES) == set(names)
+
+
+def test_host_only_entry_points():
+    L = nat.lib()
+    assert L.nmg_version() >= 100
+    for (n, m) in [(1, 4), (2, 4), (2, 8), (1, 16), (3, 6), (5, 12)]:
+        want = make_n_m(n, m)
+        assert L.nmg_num_patterns(n, m) == len(want)
+        buf = np.zeros((len(want), n), dtype=np.int8)
+        assert L.nmg_pattern_order(n, m, buf.ctypes.data_as(ctypes.c_void_p)) == 0
+        assert [tuple(r) for r in buf.tolist()] == want
+
+
+def test_invalid_arguments_return_status_not_abort():
+    L = nat.lib()
+    one = ctypes.c_void_p(16)  # never dereferenced: validation fails first
+    # n > m
+    assert L.nmg_sparsify(one, 1, 8, 8, 8, 64, 5, 4, 2, nat.NMG_F32, one, one, None) == 1
+    assert b"n" in L.nmg_last_error()
+    # comb(m, n) * g must fit int16
+    assert L.nmg_densify(one, one, 1, 8, 8, 2, 8, 2000, nat.NMG_F32, one, 8, 64, None) == 1
+    assert b"int16" in L.nmg_last_error()
+    # unknown dtype
+    assert L.nmg_sparsify(one, 1, 8, 8, 8, 64, 2, 4, 2, 7, one, one, None) == 1
+    # NULL operands
+    assert L.nmg_spmm(None, None, 8, 8, 2, 4, 2, nat.NMG_F32, None, 8, 4, None, None, 8, 0, 0, None, 0, None) == 1
+    # leading dimension too small
+    assert L.nmg_spmm(one, one, 8, 8, 2, 4, 2, nat.NMG_F32, one, 4, 4, None, one, 8, 0, 0, None, 0, None) == 1
+    assert b"ld_act" in L.nmg_last_error()
+    assert L.nmg_spmm_t(one, one, 8, 8, 2, 4, 2, nat.NMG_F32, one, 8, 4, one, 4, 0, None, 0, None) == 1
+    with pytest.raises(nat.NmgError):
+        nat.check(1)
+    # workspace queries are pure arithmetic
+    assert L.nmg_spmm_workspace_bytes(4096, 4096, 4096, 2, 4, 16, nat.NMG_F32, 0, 0) >= 4096 * 4096 * 4
+    assert L.nmg_spmm_t_workspace_bytes(64, 64, 8, 2, 4, 2, nat.NMG_F32, 0) > 0
+
+
+def test_cpu_tensors_are_rejected_loudly():
+    import torch
+    import sten_b200 as sten
+    with pytest.raises(RuntimeError, match="CUDA"):
+        sten.GroupedNMTensor.from_dense(torch.randn(8, 12), 2, 4, sparse_dim=0, group_size=2, group_dim=1)

@@ -1,0 +1,135 @@
+"""The plugin surface end to end on a GPU: SparsityBuilder -> F.linear / torch.mm dispatch -> backward, pickling,
+device moves.  Numerical reference is torch on the densified weight (fp32 tolerance 1e-5 relative Frobenius)."""
+import io
+import warnings
+
+import numpy as np
+import pytest
+import torch
+
+from gpu_util import cuda, np_of, rel_fro, seeded_normal
+
+pytestmark = pytest.mark.gpu
+
+
+class FFN(torch.nn.Module):
+    def __init__(self, d=768, h=3072):
+        super().__init__()
+        self.fc1 = torch.nn.Linear(d, h)
+        self.act = torch.nn.GELU()
+        self.fc2 = torch.nn.Linear(h, d)
+
+    def forward(self, x):
+        return self.fc2(self.act(self.fc1(x)))
+
+
+def _sparsify(model, n, m, g):
+    import sten_b200 as sten
+    sb = sten.SparsityBuilder()
+    for name, mod in model.named_modules():
+        if isinstance(mod, torch.nn.Linear):
+            sb.set_weight(name=name + ".weight", initial_sparsifier=sten.GroupedNMSparsifier(n=n, m=m, g=g),
+                          out_format=sten.GroupedNMTensor)
+    return sb.get_sparse_model(model)
+
+
+def _densified_copy(sparse_model, template):
+    import copy
+    import sten_b200 as sten
+    dense = copy.deepcopy(template)
+    for (name, p), (_, q) in zip(sparse_model.named_parameters(), dense.named_parameters()):
+        src = p.wrapped_tensor.to_dense() if isinstance(p, sten.SparseTensorWrapper) else p
+        q.data.copy_(src.detach())
+    return dense
+
+
+def test_ffn_pair_forward_and_dx_backward_bert_base_shapes():
+    """BERT-base FFN pair at 1:4, linear -> GELU -> linear, forward plus the dX pass."""
+    import sten_b200 as sten
+    torch.manual_seed(0)
+    model = FFN().to(cuda())
+    sparse = _sparsify(model, 1, 4, 16)
+    assert isinstance(sparse.fc1.weight, sten.SparseParameterWrapper)
+    dense = _densified_copy(sparse, model).double()
+    x = seeded_normal((8, 512, 768), 1).to(cuda()).requires_grad_(True)
+    sten.set_dispatch_failure("raise")  # any fall-back to dense would raise: the CUDA kernels must be the path
+    y = sparse(x)
+    xd = x.detach().double().requires_grad_(True)
+    yd = dense(xd)
+    assert rel_fro(np_of(y), yd.detach().cpu().numpy()) <= 1e-5
+    dy = seeded_normal((8, 512, 768), 2).to(cuda())
+    for p in sparse.parameters():
+        p.requires_grad_(False)
+    y.backward(dy)
+    yd.backward(dy.double())
+    assert rel_fro(np_of(x.grad), xd.grad.cpu().numpy()) <= 1e-5
+
+
+def test_bias_free_linear_uses_the_kernel_and_mm_dispatch():
+    import sten_b200 as sten
+    sten.set_dispatch_failure("raise")
+    lin = torch.nn.Linear(200, 64, bias=False).to(cuda())
+    sparse = _sparsify(torch.nn.Sequential(lin), 2, 4, 8)
+    x = seeded_normal((50, 200), 3).to(cuda())
+    w = sparse[0].weight
+    with warnings.catch_warnings():
+        warnings.simplefilter("error", sten.DispatchWarning)
+        y = sparse(x)
+        wd = w.wrapped_tensor.to_dense()
+        assert rel_fro(np_of(y), np_of(x).astype(np.float64) @ np_of(wd).astype(np.float64).T) <= 1e-5
+        b = seeded_normal((200, 33), 4).to(cuda()).requires_grad_(True)
+        c = torch.mm(w, b)
+        assert rel_fro(np_of(c), np_of(wd).astype(np.float64) @ np_of(b).astype(np.float64)) <= 1e-5
+        c.sum().backward()
+        want = np_of(wd).astype(np.float64).T @ np.ones((64, 33))
+        assert rel_fro(np_of(b.grad), want) <= 1e-5
+
+
+def test_trainable_weight_gets_dense_gradient_wrapper():
+    import sten_b200 as sten
+    lin = torch.nn.Linear(96, 32).to(cuda())
+    sparse = _sparsify(torch.nn.Sequential(lin), 2, 4, 4)
+    x = seeded_normal((10, 96), 6).to(cuda())
+    sparse(x).sum().backward()
+    g = sparse[0].weight.grad
+    assert isinstance(g, sten.SparseTensorWrapper) and isinstance(g.wrapped_tensor, sten.DenseTensor)
+    assert rel_fro(np_of(g.wrapped_tensor.to_dense()), np.ones((32, 10)) @ np_of(x).astype(np.float64)) <= 1e-5
+
+
+def test_pickle_round_trip_and_device_move():
+    import sten_b200 as sten
+    lin = torch.nn.Linear(120, 48).to(cuda())
+    sparse = _sparsify(torch.nn.Sequential(lin), 2, 8, 2)
+    x = seeded_normal((7, 120), 8).to(cuda())
+    y = sparse(x)
+    buf = io.BytesIO()
+    torch.save(sparse, buf)
+    buf.seek(0)
+    again = torch.load(buf, weights_only=False)
+    t = again[0].weight.wrapped_tensor
+    assert set(vars(t)) == {"val", "idx", "nm_strides"}
+    assert t.idx.dtype == torch.int16 and t.idx.shape[-1] == 1 and t.val.shape[-1] == 2
+    assert torch.equal(again(x), y)
+    w = sparse[0].weight
+    w_cpu = w.to("cpu")
+    assert isinstance(w_cpu.wrapped_tensor, sten.GroupedNMTensor) and w_cpu.wrapped_tensor.val.device.type == "cpu"
+    w_back = w_cpu.to(cuda())
+    assert torch.equal(w_back.wrapped_tensor.idx, w.wrapped_tensor.idx)
+    half = w.to(torch.float16)
+    assert half.wrapped_tensor.val.dtype == torch.float16 and torch.equal(half.wrapped_tensor.idx, w.wrapped_tensor.idx)
+    assert w.shape == (48, 120) and w.dtype == torch.float32
+
+
+def test_fp16_encoder_layer_shapes_run_through_the_kernels():
+    """One BERT-large-shaped block of linears at 2:4 in fp16 (the configuration of the encoder benchmark)."""
+    import sten_b200 as sten
+    sten.set_dispatch_failure("raise")
+    torch.manual_seed(0)
+    block = torch.nn.Sequential(torch.nn.Linear(1024, 4096), torch.nn.GELU(), torch.nn.Linear(4096, 1024)).to(cuda()).half()
+    sparse = _sparsify(block, 2, 4, 16)
+    x = seeded_normal((4, 96, 1024), 9).to(cuda()).half()
+    with torch.no_grad():
+        y = sparse(x)
+        dense = _densified_copy(sparse, block)
+        yd = dense.float()(x.float())
+    assert rel_fro(np_of(y), np_of(yd)) <= 1e-2

@@ -1,0 +1,142 @@
+"""Parity of the CUDA matmuls (forward in both activation layouts, transposed backward), through the C ABI.
+
+fp32: relative Frobenius error <= 1e-5 against (a) the CPU oracle, which follows the reference micro-kernel's
+accumulation structure, (b) float64 matmul on the densified weight, and (c) stored outputs of the reference's own
+AVX micro-kernels.  fp16 / bf16: <= 1e-2 against float64 matmul of the rounded operands."""
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from conftest import GOLDEN
+from gpu_util import cuda, np_of, rel_fro, seeded_normal
+from oracle import nmg_oracle as orc
+
+pytestmark = pytest.mark.gpu
+
+TOL_F32 = 1e-5
+TOL_HALF = 1e-2
+
+
+def _problem(M, K, n, m, g, tokens, seed, dtype=torch.float32):
+    from sten_b200 import ops
+    w = seeded_normal((M, K), seed).to(dtype)
+    x = seeded_normal((tokens, K), seed + 1).to(dtype)
+    val, idx = ops.sparsify(w.to(cuda()).unsqueeze(0), n, m, g)
+    dense = ops.densify(val, idx, 1, M, K, n, m, g)[0]
+    return val, idx, x.to(cuda()), dense
+
+
+CASES = [
+    # n, m, g, M, K, tokens   (remainders in M, K and tokens on purpose)
+    (2, 4, 4, 1024, 1024, 256),      # the 1024 x 1024 plumbing configuration
+    (2, 4, 16, 256, 1000, 200),
+    (1, 4, 16, 130, 512, 77),
+    (1, 8, 16, 96, 1024, 128),
+    (2, 8, 16, 72, 900, 130),
+    (1, 16, 16, 100, 777, 64),
+    (3, 6, 4, 60, 333, 50),
+    (2, 4, 64, 64, 2000, 33),
+    (4, 8, 1, 16, 150, 40),          # not specialised: generic kernels
+    (5, 12, 2, 24, 1600, 9),         # generic, C = 792 patterns
+    (1, 4, 1, 9, 7, 1),
+]
+
+
+@pytest.mark.parametrize("n,m,g,M,K,tokens", CASES)
+def test_forward_token_major_fp32(n, m, g, M, K, tokens):
+    from sten_b200 import ops
+    val, idx, x, dense = _problem(M, K, n, m, g, tokens, 10 * n + m + g)
+    bias = seeded_normal((M,), 5).to(cuda())
+    y = ops.spmm(val, idx, M, K, n, m, g, x, bias=bias)
+    ref64 = np_of(x).astype(np.float64) @ np_of(dense).astype(np.float64).T + np_of(bias).astype(np.float64)
+    assert rel_fro(np_of(y), ref64) <= TOL_F32
+    y_nb = ops.spmm(val, idx, M, K, n, m, g, x)
+    want = orc.spmm(np_of(val), np_of(idx), np_of(x), M, K, n, m, g)[:, :M]
+    assert rel_fro(np_of(y_nb), want) <= TOL_F32
+    assert torch.equal(y_nb, ops.spmm(val, idx, M, K, n, m, g, x))  # deterministic
+
+
+@pytest.mark.parametrize("n,m,g,M,K,tokens", CASES[:8])
+def test_forward_k_major_fp32(n, m, g, M, K, tokens):
+    from sten_b200 import _native as nat, ops
+    val, idx, x, dense = _problem(M, K, n, m, g, tokens, 20 * n + m + g)
+    b = x.t().contiguous()  # [K, tokens]
+    c = ops.spmm(val, idx, M, K, n, m, g, b, layout=nat.NMG_ACT_K_MAJOR)
+    ref64 = np_of(dense).astype(np.float64) @ np_of(b).astype(np.float64)
+    assert c.shape == (M, tokens)
+    assert rel_fro(np_of(c), ref64) <= TOL_F32
+
+
+@pytest.mark.parametrize("n,m,g,M,K,tokens", CASES)
+def test_transposed_fp32(n, m, g, M, K, tokens):
+    from sten_b200 import ops
+    val, idx, _, dense = _problem(M, K, n, m, g, tokens, 30 * n + m + g)
+    dy = seeded_normal((tokens, M), 99).to(cuda())
+    dx = ops.spmm_t(val, idx, M, K, n, m, g, dy)
+    ref64 = np_of(dy).astype(np.float64) @ np_of(dense).astype(np.float64)
+    assert dx.shape == (tokens, K)
+    assert rel_fro(np_of(dx), ref64) <= TOL_F32
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("n,m,g,M,K,tokens", [(2, 4, 16, 256, 1000, 200), (1, 4, 16, 128, 512, 64), (2, 8, 16, 72, 900, 130)])
+def test_half_precision(dtype, n, m, g, M, K, tokens):
+    from sten_b200 import ops
+    val, idx, x, dense = _problem(M, K, n, m, g, tokens, 40 * n + m, dtype)
+    y = ops.spmm(val, idx, M, K, n, m, g, x)
+    assert y.dtype == dtype
+    ref64 = np_of(x).astype(np.float64) @ np_of(dense).astype(np.float64).T
+    assert rel_fro(np_of(y), ref64) <= TOL_HALF
+    dy = seeded_normal((tokens, M), 98).to(dtype).to(cuda())
+    dx = ops.spmm_t(val, idx, M, K, n, m, g, dy)
+    assert rel_fro(np_of(dx), np_of(dy).astype(np.float64) @ np_of(dense).astype(np.float64)) <= TOL_HALF
+
+
+def test_against_stored_reference_microkernel_outputs():
+    from sten_b200 import ops
+    data = np.load(os.path.join(GOLDEN, "spmm_cases.npz"))
+    names = sorted({k.split("/")[0] for k in data.files})
+    for name in names:
+        n, m, g, shape, ntok = name.split("_")
+        n, m, g = int(n), int(m), int(g)
+        M, K = map(int, shape.split("x"))
+        w = torch.from_numpy(data[name + "/w"]).to(cuda())
+        x = torch.from_numpy(data[name + "/x"]).to(cuda())
+        val, idx = ops.sparsify(w.unsqueeze(0), n, m, g)
+        y = ops.spmm(val, idx, M, K, n, m, g, x)
+        for isa in ("avx2", "avx512"):
+            if f"{name}/{isa}" in data.files:
+                assert rel_fro(np_of(y), data[f"{name}/{isa}"][:, :M]) <= TOL_F32, (name, isa)
+
+
+def test_linearity_and_strided_operands():
+    from sten_b200 import ops
+    M, K, n, m, g, tokens = 128, 600, 2, 4, 16, 96
+    val, idx, x, dense = _problem(M, K, n, m, g, tokens, 77)
+    x2 = seeded_normal((tokens, K), 78).to(cuda())
+    a = ops.spmm(val, idx, M, K, n, m, g, x) + 2 * ops.spmm(val, idx, M, K, n, m, g, x2)
+    b = ops.spmm(val, idx, M, K, n, m, g, x + 2 * x2)
+    assert rel_fro(np_of(a), np_of(b)) <= 1e-5
+    wide = torch.zeros(tokens, K + 24, device=cuda())
+    wide[:, 8:8 + K] = x
+    y = ops.spmm(val, idx, M, K, n, m, g, wide[:, 8:8 + K])  # leading dimension != K, unaligned start
+    assert torch.equal(y, ops.spmm(val, idx, M, K, n, m, g, x))
+
+
+def test_workspace_and_argument_errors():
+    from sten_b200 import _native as nat, ops
+    M, K, n, m, g, tokens = 64, 96, 2, 4, 4, 32
+    val, idx, x, _ = _problem(M, K, n, m, g, tokens, 5)
+    L = nat.lib()
+    out = torch.empty(tokens, M, device=cuda())
+    st = torch.cuda.current_stream().cuda_stream
+    rc = L.nmg_spmm(val.data_ptr(), idx.data_ptr(), M, K, n, m, g, nat.NMG_F32, x.data_ptr(), K, tokens, None,
+                    out.data_ptr(), M, 0, 0, None, 0, st)
+    assert rc == 4 and b"workspace" in L.nmg_last_error()
+    with pytest.raises(ValueError):
+        ops.spmm(val, idx, M, K, n, m, g, x[:, :-1])
+    with pytest.raises(TypeError):
+        ops.spmm(val, idx, M, K, n, m, g, x.half())
+    assert ops.read_status() == 0
