@@ -258,6 +258,9 @@ def run_ours(args):
         n, m = 2, 4
         val, idx = packs[(n, m)]
         ks, ke = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        ks.record()
+        ke.record()  # torch creates the underlying CUDA events on first record
+        torch.cuda.synchronize()
         kernel_ms = []
         for _ in range(8):
             nat.check(L.nmg_profile_next(ks.cuda_event, ke.cuda_event))

@@ -57,15 +57,17 @@ def sparsify(dense3, n, m, g):
     assert dense3.dim() == 3
     dev = _require_cuda(dense3)
     code = _dtype_code(dense3)
-    if dense3.stride(2) != 1 or (dense3.shape[0] > 1 and dense3.stride(0) < dense3.shape[1] * dense3.stride(1)):
-        dense3 = dense3.contiguous()
     B, M, K = dense3.shape
+    if dense3.stride(2) != 1 or dense3.stride(1) < K or (B > 1 and dense3.stride(0) < M * dense3.stride(1)):
+        dense3 = dense3.contiguous()
+    # size-1 dims may carry arbitrary strides even in a contiguous tensor: state the packed strides then
+    ld, bs = (K, M * K) if dense3.is_contiguous() else (dense3.stride(1), dense3.stride(0))
     C, cc, nb, nc = geometry(M, K, n, m, g)
     T = B * nc * nb
     val = torch.empty((T, C, g, n), dtype=dense3.dtype, device=dev)
     idx = torch.empty((T, C, g, 1), dtype=torch.int16, device=dev)
     with torch.cuda.device(dev):
-        nat.check(nat.lib().nmg_sparsify(dense3.data_ptr(), B, M, K, dense3.stride(1), dense3.stride(0), n, m, g, code,
+        nat.check(nat.lib().nmg_sparsify(dense3.data_ptr(), B, M, K, ld, bs, n, m, g, code,
                                          val.data_ptr(), idx.data_ptr(), _stream(dev)))
     return val, idx
 
@@ -83,11 +85,12 @@ def densify(val, idx, B, M, K, n, m, g):
 
 
 def _row_major_2d(t):
+    """(tensor, leading dimension) of a 2-D operand with unit stride along its rows."""
     if t.dim() != 2:
         raise ValueError("expected a 2-D tensor")
     if t.stride(1) != 1 or t.stride(0) < t.shape[1]:
         t = t.contiguous()
-    return t
+    return t, (t.shape[1] if t.is_contiguous() else t.stride(0))
 
 
 def spmm(val, idx, M, K, n, m, g, act, bias=None, layout=nat.NMG_ACT_TOKEN_MAJOR, algo=nat.NMG_ALGO_AUTO, out=None):
@@ -97,7 +100,7 @@ def spmm(val, idx, M, K, n, m, g, act, bias=None, layout=nat.NMG_ACT_TOKEN_MAJOR
     code = _dtype_code(val)
     if act.dtype != val.dtype or (bias is not None and bias.dtype != val.dtype):
         raise TypeError(f"activation / bias dtype must match the weight dtype {val.dtype}")
-    act = _row_major_2d(act)
+    act, ld_act = _row_major_2d(act)
     token_major = layout == nat.NMG_ACT_TOKEN_MAJOR
     tokens = act.shape[0] if token_major else act.shape[1]
     if (act.shape[1] if token_major else act.shape[0]) != K:
@@ -112,8 +115,8 @@ def spmm(val, idx, M, K, n, m, g, act, bias=None, layout=nat.NMG_ACT_TOKEN_MAJOR
     L = nat.lib()
     with torch.cuda.device(dev):
         ws, nbytes = _workspace(L.nmg_spmm_workspace_bytes(M, K, tokens, n, m, g, code, layout, algo), dev)
-        nat.check(L.nmg_spmm(val.data_ptr(), idx.data_ptr(), M, K, n, m, g, code, act.data_ptr(), act.stride(0), tokens,
-                             bias.data_ptr() if bias is not None else None, out.data_ptr(), out.stride(0), layout, algo,
+        nat.check(L.nmg_spmm(val.data_ptr(), idx.data_ptr(), M, K, n, m, g, code, act.data_ptr(), ld_act, tokens,
+                             bias.data_ptr() if bias is not None else None, out.data_ptr(), (out.shape[1] if out.is_contiguous() else out.stride(0)), layout, algo,
                              ws.data_ptr() if ws is not None else None, nbytes, _stream(dev)))
     return out
 
@@ -124,7 +127,7 @@ def spmm_t(val, idx, M, K, n, m, g, dy, algo=nat.NMG_ALGO_AUTO):
     code = _dtype_code(val)
     if dy.dtype != val.dtype:
         raise TypeError(f"gradient dtype must match the weight dtype {val.dtype}")
-    dy = _row_major_2d(dy)
+    dy, ld_dy = _row_major_2d(dy)
     tokens = dy.shape[0]
     if dy.shape[1] != M:
         raise ValueError(f"gradient shape {tuple(dy.shape)} does not match M={M}")
@@ -135,8 +138,8 @@ def spmm_t(val, idx, M, K, n, m, g, dy, algo=nat.NMG_ALGO_AUTO):
     L = nat.lib()
     with torch.cuda.device(dev):
         ws, nbytes = _workspace(L.nmg_spmm_t_workspace_bytes(M, K, tokens, n, m, g, code, algo), dev)
-        nat.check(L.nmg_spmm_t(val.data_ptr(), idx.data_ptr(), M, K, n, m, g, code, dy.data_ptr(), dy.stride(0), tokens,
-                               dx.data_ptr(), dx.stride(0), algo, ws.data_ptr() if ws is not None else None, nbytes,
+        nat.check(L.nmg_spmm_t(val.data_ptr(), idx.data_ptr(), M, K, n, m, g, code, dy.data_ptr(), ld_dy, tokens,
+                               dx.data_ptr(), K, algo, ws.data_ptr() if ws is not None else None, nbytes,
                                _stream(dev)))
     return dx
 

@@ -1,0 +1,65 @@
+"""Run one kernel of the library a few times on a seeded problem, for use under a profiler.
+
+    python -m sten_b200.profile_case --op fwd --nm 2:4 --g 16 --rows 4096 --cols 4096 --tokens 4096 --dtype f32 --reps 3
+
+``--op`` is one of ``fwd`` (y = x W^T), ``fwd_kmajor`` (C = W B), ``bwd`` (dX = dY W), ``sparsify``, ``densify``.
+Prints the mean device time per call measured with CUDA events (meaningless under a profiler, useful without).
+"""
+import argparse
+
+import torch
+
+from . import _native as nat
+from . import ops
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--op", default="fwd", choices=["fwd", "fwd_kmajor", "bwd", "sparsify", "densify"])
+    ap.add_argument("--nm", default="2:4")
+    ap.add_argument("--g", type=int, default=16)
+    ap.add_argument("--rows", type=int, default=4096)
+    ap.add_argument("--cols", type=int, default=4096)
+    ap.add_argument("--tokens", type=int, default=4096)
+    ap.add_argument("--dtype", default="f32", choices=["f32", "f16", "bf16"])
+    ap.add_argument("--algo", default="auto", choices=["auto", "simt", "tensor"])
+    ap.add_argument("--reps", type=int, default=3)
+    a = ap.parse_args()
+    n, m = map(int, a.nm.split(":"))
+    dtype = {"f32": torch.float32, "f16": torch.float16, "bf16": torch.bfloat16}[a.dtype]
+    algo = {"auto": nat.NMG_ALGO_AUTO, "simt": nat.NMG_ALGO_SIMT, "tensor": nat.NMG_ALGO_TENSOR}[a.algo]
+    dev = torch.device("cuda", 0)
+    M, K, g = a.rows, a.cols, a.g
+    w = torch.randn(M, K, generator=torch.Generator().manual_seed(0)).to(dev)
+    val, idx = ops.sparsify(w.unsqueeze(0), n, m, g)
+    val = val.to(dtype)
+    x = torch.randn(a.tokens, K, generator=torch.Generator().manual_seed(1)).to(dev).to(dtype)
+    dy = torch.randn(a.tokens, M, generator=torch.Generator().manual_seed(2)).to(dev).to(dtype)
+    xt = x.t().contiguous()
+    wd = w.to(dtype).unsqueeze(0)
+
+    def call():
+        if a.op == "fwd":
+            return ops.spmm(val, idx, M, K, n, m, g, x, algo=algo)
+        if a.op == "fwd_kmajor":
+            return ops.spmm(val, idx, M, K, n, m, g, xt, layout=nat.NMG_ACT_K_MAJOR, algo=algo)
+        if a.op == "bwd":
+            return ops.spmm_t(val, idx, M, K, n, m, g, dy, algo=algo)
+        if a.op == "sparsify":
+            return ops.sparsify(wd, n, m, g)
+        return ops.densify(val, idx, 1, M, K, n, m, g)
+
+    call()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(a.reps):
+        call()
+    e1.record()
+    torch.cuda.synchronize()
+    ops.read_status(dev)
+    print(f"{a.op} {a.nm} g={g} {M}x{K} tokens={a.tokens} {a.dtype}: {e0.elapsed_time(e1) / a.reps:.4f} ms per call")
+
+
+if __name__ == "__main__":
+    main()
