@@ -73,27 +73,42 @@ int nmg_sparsify(const void *dense, int64_t batch, int64_t M, int64_t K, int64_t
 int nmg_densify(const void *val, const int16_t *idx, int64_t batch, int64_t M, int64_t K, int n, int m,
                 int g, int dtype, void *dense, int64_t ld_dense, int64_t batch_stride, void *stream);
 
+/* Column-ordered device copy of a weight ("packed" form), the second half of the format conversion: for every
+ * row-block and column it holds the column's pattern id and its n kept values, i.e. val / idx re-ordered from
+ * pattern-sorted to natural column order.  The tensor-core matmul and the transposed matmul read it; building it
+ * once per weight and passing it to nmg_spmm / nmg_spmm_t saves the re-ordering pass of every call.  The copy is
+ * an internal cache: it is derived from (val, idx), never serialised, and its layout may change between
+ * versions.  No counterpart in the reference (its kernels read val / idx directly).
+ *   packed: device buffer of at least nmg_packed_bytes(...) bytes, 256-byte aligned. */
+size_t nmg_packed_bytes(int64_t M, int64_t K, int n, int m, int g, int dtype);
+int nmg_pack(const void *val, const int16_t *idx, int64_t M, int64_t K, int n, int m, int g, int dtype, void *packed,
+             size_t packed_bytes, void *stream);
+
 /* Sparse weight x dense activation.  Replaces `__program_nmg_<hash>(state, A_idx, A_val, B, C, groups)`
  * (src/sten/grouped_nm/sten_impls.py:111-138, generated by dace_gnm_mult.py:572-1007) and the crop / bias add of
  * sparse_torch_nn_functional_linear (sten_impls.py:170-173).
  *   layout NMG_ACT_TOKEN_MAJOR: act = X[tokens][ld_act >= K], out = Y[tokens][ld_out >= M], out = X W^T (+ bias[M])
  *   layout NMG_ACT_K_MAJOR:     act = B[K][ld_act >= tokens], out = C[M][ld_out >= tokens], out = W B (+ bias[M] per row)
  * act, out, val and bias share `dtype`; accumulation is fp32.  bias may be NULL.
+ * packed: result of nmg_pack for the same weight, or NULL (then it is built in the workspace when the chosen kernel
+ * needs it).  have_packed in the workspace query says which of the two the caller will do.
  * workspace: device scratch of at least nmg_spmm_workspace_bytes(...) bytes, 256-byte aligned, owned by the
- * caller for the duration of the call (may be NULL when the query returns 0). */
+ * caller for the duration of the call (may be NULL when the query returns 0).
+ * algo: NMG_ALGO_AUTO uses the tensor-core kernel for fp16 / bf16 weights with m in {4, 8, 16} and token-major
+ * activations whose rows are 16-byte aligned, the SIMT kernels otherwise. */
 size_t nmg_spmm_workspace_bytes(int64_t M, int64_t K, int64_t tokens, int n, int m, int g, int dtype,
-                                int layout, int algo);
-int nmg_spmm(const void *val, const int16_t *idx, int64_t M, int64_t K, int n, int m, int g, int dtype,
-             const void *act, int64_t ld_act, int64_t tokens, const void *bias, void *out, int64_t ld_out,
-             int layout, int algo, void *workspace, size_t workspace_bytes, void *stream);
+                                int layout, int algo, int have_packed);
+int nmg_spmm(const void *val, const int16_t *idx, const void *packed, int64_t M, int64_t K, int n, int m, int g,
+             int dtype, const void *act, int64_t ld_act, int64_t tokens, const void *bias, void *out,
+             int64_t ld_out, int layout, int algo, void *workspace, size_t workspace_bytes, void *stream);
 
 /* Transposed product for the backward pass: dX[tokens][ld_dx >= K] = dY[tokens][ld_dy >= M] * W.
  * The reference has no counterpart (its dispatcher installs a failing backward stub: src/sten/sten.py:1690-1693);
  * the registration shape follows the CSR linear backward (sten.py:2362-2383). */
 size_t nmg_spmm_t_workspace_bytes(int64_t M, int64_t K, int64_t tokens, int n, int m, int g, int dtype,
-                                  int algo);
-int nmg_spmm_t(const void *val, const int16_t *idx, int64_t M, int64_t K, int n, int m, int g, int dtype,
-               const void *dy, int64_t ld_dy, int64_t tokens, void *dx, int64_t ld_dx, int algo,
+                                  int algo, int have_packed);
+int nmg_spmm_t(const void *val, const int16_t *idx, const void *packed, int64_t M, int64_t K, int n, int m, int g,
+               int dtype, const void *dy, int64_t ld_dy, int64_t tokens, void *dx, int64_t ld_dx, int algo,
                void *workspace, size_t workspace_bytes, void *stream);
 
 /* Measurement helpers (no counterpart in the reference; its profiling is wall-clock around whole operators,

@@ -22,11 +22,13 @@ SIGNATURES = {
     "nmg_pattern_order": (_int, [_int, _int, _vp]),
     "nmg_sparsify": (_int, [_vp, _i64, _i64, _i64, _i64, _i64, _int, _int, _int, _int, _vp, _vp, _vp]),
     "nmg_densify": (_int, [_vp, _vp, _i64, _i64, _i64, _int, _int, _int, _int, _vp, _i64, _i64, _vp]),
-    "nmg_spmm_workspace_bytes": (_sz, [_i64, _i64, _i64, _int, _int, _int, _int, _int, _int]),
-    "nmg_spmm": (_int, [_vp, _vp, _i64, _i64, _int, _int, _int, _int, _vp, _i64, _i64, _vp, _vp, _i64, _int, _int,
+    "nmg_packed_bytes": (_sz, [_i64, _i64, _int, _int, _int, _int]),
+    "nmg_pack": (_int, [_vp, _vp, _i64, _i64, _int, _int, _int, _int, _vp, _sz, _vp]),
+    "nmg_spmm_workspace_bytes": (_sz, [_i64, _i64, _i64, _int, _int, _int, _int, _int, _int, _int]),
+    "nmg_spmm": (_int, [_vp, _vp, _vp, _i64, _i64, _int, _int, _int, _int, _vp, _i64, _i64, _vp, _vp, _i64, _int, _int,
                         _vp, _sz, _vp]),
-    "nmg_spmm_t_workspace_bytes": (_sz, [_i64, _i64, _i64, _int, _int, _int, _int, _int]),
-    "nmg_spmm_t": (_int, [_vp, _vp, _i64, _i64, _int, _int, _int, _int, _vp, _i64, _i64, _vp, _i64, _int, _vp, _sz,
+    "nmg_spmm_t_workspace_bytes": (_sz, [_i64, _i64, _i64, _int, _int, _int, _int, _int, _int]),
+    "nmg_spmm_t": (_int, [_vp, _vp, _vp, _i64, _i64, _int, _int, _int, _int, _vp, _i64, _i64, _vp, _i64, _int, _vp, _sz,
                           _vp]),
     "nmg_profile_next": (_int, [_vp, _vp]),
     "nmg_measure_fma_peak": (_int, [ctypes.POINTER(ctypes.c_double), _vp]),

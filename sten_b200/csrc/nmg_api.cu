@@ -1,4 +1,5 @@
-// C-ABI entry points of the matmul: argument validation and choice of kernel family.
+// C-ABI entry points of the matmul and of the packed (column-ordered) weight copy: argument validation, choice of
+// kernel family, workspace carving.
 #include "nmg_spmm_simt.cuh"
 
 using namespace nmg;
@@ -11,17 +12,69 @@ static int check_common(int dtype, int64_t tokens, const void *a, const void *b,
     return NMG_OK;
 }
 
-extern "C" size_t nmg_spmm_workspace_bytes(int64_t M, int64_t K, int64_t tokens, int n, int m, int g, int dtype,
-                                           int layout, int algo) {
-    Geo geo;
-    if (make_geo(M, K, n, m, g, &geo) || tokens < 1) return 0;
-    (void)algo;
-    return simt_fwd_workspace_bytes(geo, tokens, dtype, layout);
+static char *align256(void *p) { return reinterpret_cast<char *>(((uintptr_t)p + 255) & ~(uintptr_t)255); }
+
+// The tensor-core kernel reads the activation through a TMA descriptor: 16-bit dtype, reduction axis contiguous,
+// 16-byte aligned base and row pitch.
+static bool tensor_ok(const Geo &geo, int dtype, const void *act, int64_t ld_act) {
+    return tc_supported(geo, dtype) && (((uintptr_t)act) & 15) == 0 && (ld_act % 8) == 0;
 }
 
-extern "C" int nmg_spmm(const void *val, const int16_t *idx, int64_t M, int64_t K, int n, int m, int g, int dtype,
-                        const void *act, int64_t ld_act, int64_t tokens, const void *bias, void *out, int64_t ld_out,
-                        int layout, int algo, void *workspace, size_t workspace_bytes, void *stream) {
+extern "C" size_t nmg_packed_bytes(int64_t M, int64_t K, int n, int m, int g, int dtype) {
+    Geo geo;
+    if (make_geo(M, K, n, m, g, &geo) || n < 1) return 0;
+    return natural_bytes(geo, dtype, nullptr) + 256;
+}
+
+extern "C" int nmg_pack(const void *val, const int16_t *idx, int64_t M, int64_t K, int n, int m, int g, int dtype,
+                        void *packed, size_t packed_bytes, void *stream) {
+    Geo geo;
+    int rc = make_geo(M, K, n, m, g, &geo);
+    if (rc) return rc;
+    if ((rc = check_common(dtype, 1, val, idx, packed, packed))) return rc;
+    if (n < 1) NMG_FAIL(NMG_ERR_INVALID, "n must be >= 1");
+    size_t pat_bytes = 0;
+    const size_t need = natural_bytes(geo, dtype, &pat_bytes) + 256;
+    if (packed_bytes < need) NMG_FAIL(NMG_ERR_WORKSPACE, "packed buffer of %zu bytes required, got %zu", need, packed_bytes);
+    char *base = align256(packed);
+    return launch_build_natural(geo, dtype, val, idx, reinterpret_cast<uint16_t *>(base), base + pat_bytes, (cudaStream_t)stream);
+}
+
+// Resolve the column-ordered copy: the caller's, or one built at the front of the workspace.  Advances *ws.
+static int resolve_packed(const Geo &geo, int dtype, const void *val, const int16_t *idx, const void *packed, char **ws,
+                          size_t *ws_left, const uint16_t **pat, const void **nval, cudaStream_t st) {
+    size_t pat_bytes = 0;
+    const size_t nat = natural_bytes(geo, dtype, &pat_bytes);
+    if (packed) {
+        char *base = align256(const_cast<void *>(packed));
+        *pat = reinterpret_cast<const uint16_t *>(base);
+        *nval = base + pat_bytes;
+        return NMG_OK;
+    }
+    if (!*ws || *ws_left < nat + 256) NMG_FAIL(NMG_ERR_WORKSPACE, "workspace too small for the column-ordered weight copy (%zu bytes)", nat + 256);
+    char *base = align256(*ws);
+    *pat = reinterpret_cast<const uint16_t *>(base);
+    *nval = base + pat_bytes;
+    *ws_left -= (size_t)(base + nat - *ws);
+    *ws = base + nat;
+    return launch_build_natural(geo, dtype, val, idx, reinterpret_cast<uint16_t *>(base), base + pat_bytes, st);
+}
+
+extern "C" size_t nmg_spmm_workspace_bytes(int64_t M, int64_t K, int64_t tokens, int n, int m, int g, int dtype,
+                                           int layout, int algo, int have_packed) {
+    Geo geo;
+    if (make_geo(M, K, n, m, g, &geo) || tokens < 1 || n < 1) return 0;
+    size_t simt = simt_fwd_workspace_bytes(geo, tokens, dtype, layout);
+    size_t tensor = 0;
+    if (algo != NMG_ALGO_SIMT && tc_supported(geo, dtype) && layout == NMG_ACT_TOKEN_MAJOR && !have_packed)
+        tensor = natural_bytes(geo, dtype, nullptr) + 512;
+    if (algo == NMG_ALGO_TENSOR) return tensor;
+    return simt > tensor ? simt : tensor;  // AUTO may take either path depending on operand alignment
+}
+
+extern "C" int nmg_spmm(const void *val, const int16_t *idx, const void *packed, int64_t M, int64_t K, int n, int m,
+                        int g, int dtype, const void *act, int64_t ld_act, int64_t tokens, const void *bias, void *out,
+                        int64_t ld_out, int layout, int algo, void *workspace, size_t workspace_bytes, void *stream) {
     Geo geo;
     int rc = make_geo(M, K, n, m, g, &geo);
     if (rc) return rc;
@@ -31,23 +84,34 @@ extern "C" int nmg_spmm(const void *val, const int16_t *idx, int64_t M, int64_t 
     const bool tm = layout == NMG_ACT_TOKEN_MAJOR;
     if (ld_act < (tm ? K : tokens)) NMG_FAIL(NMG_ERR_INVALID, "ld_act=%lld is smaller than the activation row", (long long)ld_act);
     if (ld_out < (tm ? M : tokens)) NMG_FAIL(NMG_ERR_INVALID, "ld_out=%lld is smaller than the output row", (long long)ld_out);
-    if (algo == NMG_ALGO_TENSOR) NMG_FAIL(NMG_ERR_UNSUPPORTED, "tensor-core path is not available for this problem");
-    if (algo != NMG_ALGO_AUTO && algo != NMG_ALGO_SIMT) NMG_FAIL(NMG_ERR_INVALID, "unknown algo %d", algo);
-    return simt_fwd(geo, dtype, val, idx, act, ld_act, tokens, bias, out, ld_out, layout, workspace, workspace_bytes,
-                    (cudaStream_t)stream);
+    if (algo != NMG_ALGO_AUTO && algo != NMG_ALGO_SIMT && algo != NMG_ALGO_TENSOR) NMG_FAIL(NMG_ERR_INVALID, "unknown algo %d", algo);
+    cudaStream_t st = (cudaStream_t)stream;
+    const bool can_tensor = tm && tensor_ok(geo, dtype, act, ld_act);
+    if (algo == NMG_ALGO_TENSOR && !can_tensor)
+        NMG_FAIL(NMG_ERR_UNSUPPORTED, "tensor-core path needs fp16/bf16, m in {4,8,16}, token-major activations with 16-byte aligned rows");
+    if (algo != NMG_ALGO_SIMT && can_tensor) {
+        char *ws = static_cast<char *>(workspace);
+        size_t left = workspace_bytes;
+        const uint16_t *pat = nullptr;
+        const void *nval = nullptr;
+        if ((rc = resolve_packed(geo, dtype, val, idx, packed, &ws, &left, &pat, &nval, st))) return rc;
+        return tc_matmul(geo, dtype, false, pat, nval, act, ld_act, tokens, bias, out, ld_out, 1, st);
+    }
+    return simt_fwd(geo, dtype, val, idx, act, ld_act, tokens, bias, out, ld_out, layout, workspace, workspace_bytes, st);
 }
 
 extern "C" size_t nmg_spmm_t_workspace_bytes(int64_t M, int64_t K, int64_t tokens, int n, int m, int g, int dtype,
-                                             int algo) {
+                                             int algo, int have_packed) {
     Geo geo;
-    if (make_geo(M, K, n, m, g, &geo) || tokens < 1) return 0;
-    (void)algo;
-    return simt_bwd_workspace_bytes(geo, tokens, dtype);
+    if (make_geo(M, K, n, m, g, &geo) || tokens < 1 || n < 1) return 0;
+    size_t bytes = have_packed ? 0 : natural_bytes(geo, dtype, nullptr) + 512;
+    if (algo != NMG_ALGO_TENSOR) bytes += simt_bwd_workspace_bytes(geo, tokens, dtype) + 256;
+    return bytes;
 }
 
-extern "C" int nmg_spmm_t(const void *val, const int16_t *idx, int64_t M, int64_t K, int n, int m, int g, int dtype,
-                          const void *dy, int64_t ld_dy, int64_t tokens, void *dx, int64_t ld_dx, int algo,
-                          void *workspace, size_t workspace_bytes, void *stream) {
+extern "C" int nmg_spmm_t(const void *val, const int16_t *idx, const void *packed, int64_t M, int64_t K, int n, int m,
+                          int g, int dtype, const void *dy, int64_t ld_dy, int64_t tokens, void *dx, int64_t ld_dx,
+                          int algo, void *workspace, size_t workspace_bytes, void *stream) {
     Geo geo;
     int rc = make_geo(M, K, n, m, g, &geo);
     if (rc) return rc;
@@ -55,7 +119,17 @@ extern "C" int nmg_spmm_t(const void *val, const int16_t *idx, int64_t M, int64_
     if (n < 1) NMG_FAIL(NMG_ERR_INVALID, "n must be >= 1");
     if (ld_dy < M) NMG_FAIL(NMG_ERR_INVALID, "ld_dy=%lld is smaller than M", (long long)ld_dy);
     if (ld_dx < K) NMG_FAIL(NMG_ERR_INVALID, "ld_dx=%lld is smaller than K", (long long)ld_dx);
-    if (algo == NMG_ALGO_TENSOR) NMG_FAIL(NMG_ERR_UNSUPPORTED, "tensor-core path is not available for this problem");
-    if (algo != NMG_ALGO_AUTO && algo != NMG_ALGO_SIMT) NMG_FAIL(NMG_ERR_INVALID, "unknown algo %d", algo);
-    return simt_bwd(geo, dtype, val, idx, dy, ld_dy, tokens, dx, ld_dx, workspace, workspace_bytes, (cudaStream_t)stream);
+    if (algo != NMG_ALGO_AUTO && algo != NMG_ALGO_SIMT && algo != NMG_ALGO_TENSOR) NMG_FAIL(NMG_ERR_INVALID, "unknown algo %d", algo);
+    cudaStream_t st = (cudaStream_t)stream;
+    const bool can_tensor = tensor_ok(geo, dtype, dy, ld_dy);
+    if (algo == NMG_ALGO_TENSOR && !can_tensor)
+        NMG_FAIL(NMG_ERR_UNSUPPORTED, "tensor-core path needs fp16/bf16, m in {4,8,16} and 16-byte aligned gradient rows");
+    char *ws = static_cast<char *>(workspace);
+    size_t left = workspace_bytes;
+    const uint16_t *pat = nullptr;
+    const void *nval = nullptr;
+    if ((rc = resolve_packed(geo, dtype, val, idx, packed, &ws, &left, &pat, &nval, st))) return rc;
+    if (algo != NMG_ALGO_SIMT && can_tensor)
+        return tc_matmul(geo, dtype, true, pat, nval, dy, ld_dy, tokens, nullptr, dx, ld_dx, 1, st);
+    return simt_bwd(geo, dtype, pat, nval, dy, ld_dy, tokens, dx, ld_dx, ws, left, st);
 }

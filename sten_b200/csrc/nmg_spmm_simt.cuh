@@ -25,9 +25,16 @@ size_t simt_fwd_workspace_bytes(const Geo &geo, int64_t tokens, int dtype, int l
 int simt_fwd(const Geo &geo, int dtype, const void *val, const int16_t *idx, const void *act, int64_t ld_act,
              int64_t tokens, const void *bias, void *out, int64_t ld_out, int layout, void *ws, size_t ws_bytes,
              cudaStream_t st);
+// pat / nval: the column-ordered copy; the workspace only holds the fp32 transpose of dY
 size_t simt_bwd_workspace_bytes(const Geo &geo, int64_t tokens, int dtype);
-int simt_bwd(const Geo &geo, int dtype, const void *val, const int16_t *idx, const void *dy, int64_t ld_dy,
+int simt_bwd(const Geo &geo, int dtype, const uint16_t *pat, const void *nval, const void *dy, int64_t ld_dy,
              int64_t tokens, void *dx, int64_t ld_dx, void *ws, size_t ws_bytes, cudaStream_t st);
+
+// Tensor-core kernels (nmg_spmm_tc.cu).  act: [tokens][ld_act] with the reduction axis contiguous.
+bool tc_supported(const Geo &geo, int dtype);
+int tc_matmul(const Geo &geo, int dtype, bool transposed, const uint16_t *pat, const void *nval, const void *act,
+              int64_t ld_act, int64_t tokens, const void *bias, void *out, int64_t ld_out, int out_token_major,
+              cudaStream_t st);
 
 // ---- specialised forward kernel: parameters, shared-memory plan, per-(n, m) launchers
 struct FwdParams {

@@ -100,22 +100,16 @@ static int bwd_rb_stage(int m) {  // rows per stage <= 64 keeps one TMA box (256
 }
 
 size_t simt_bwd_workspace_bytes(const Geo &geo, int64_t tokens, int dtype) {
-    size_t bytes = natural_bytes(geo, dtype, nullptr) + 256;
-    if (bwd_specialised(geo.n, geo.m)) bytes += (size_t)geo.M * (size_t)round_up(tokens, 128) * 4 + 256;
-    return bytes;
+    (void)dtype;
+    return bwd_specialised(geo.n, geo.m) ? (size_t)geo.M * (size_t)round_up(tokens, 128) * 4 + 256 : 0;
 }
 
-int simt_bwd(const Geo &geo, int dtype, const void *val, const int16_t *idx, const void *dy, int64_t ld_dy,
+int simt_bwd(const Geo &geo, int dtype, const uint16_t *pat, const void *nval, const void *dy, int64_t ld_dy,
              int64_t tokens, void *dx, int64_t ld_dx, void *ws, size_t ws_bytes, cudaStream_t st) {
     const size_t need = simt_bwd_workspace_bytes(geo, tokens, dtype);
-    if (!ws || ws_bytes < need) NMG_FAIL(NMG_ERR_WORKSPACE, "workspace of %zu bytes required, got %zu", need, ws_bytes);
+    if (need && (!ws || ws_bytes < need)) NMG_FAIL(NMG_ERR_WORKSPACE, "workspace of %zu bytes required, got %zu", need, ws_bytes);
     char *base = reinterpret_cast<char *>(((uintptr_t)ws + 255) & ~(uintptr_t)255);
-    size_t pat_bytes = 0;
-    const size_t nat = natural_bytes(geo, dtype, &pat_bytes);
-    uint16_t *pat = reinterpret_cast<uint16_t *>(base);
-    void *nval = base + pat_bytes;
-    int rc = launch_build_natural(geo, dtype, val, idx, pat, nval, st);
-    if (rc) return rc;
+    int rc = NMG_OK;
     const int64_t Kp = natural_width(geo);
 
     if (!bwd_specialised(geo.n, geo.m)) {
@@ -132,7 +126,7 @@ int simt_bwd(const Geo &geo, int dtype, const void *val, const int16_t *idx, con
         return NMG_OK;
     }
 
-    float *yt = reinterpret_cast<float *>(base + nat);
+    float *yt = reinterpret_cast<float *>(base);
     const int64_t ld_yt = round_up(tokens, 128);
     if ((rc = launch_transpose_to_f32(dy, dtype, tokens, geo.M, ld_dy, yt, ld_yt, st))) return rc;
     const int rs = bwd_rb_stage(geo.m);

@@ -1,0 +1,364 @@
+// Tensor-core matmul for fp16 / bf16 grouped n:m weights: tcgen05.mma with TMEM accumulators.
+//
+// In the format's orientation the n:m blocks run along the OUTPUT-feature axis of y = x W^T, so no operand of the
+// forward product is structured-sparse along the reduction axis and tcgen05.mma.sp does not apply.  What the
+// format does give is a weight that is 2/m .. n/m of its dense size in HBM and L2.  This kernel keeps it that
+// way: the weight stays compressed in global memory (column-ordered copy: one pattern id + n values per
+// (row-block, column)), is expanded tile by tile straight into the shared-memory operand layout of the
+// tensor core (128-byte swizzle, K-major) by dedicated warps, and is multiplied at dense tensor-core rate
+// against activation tiles that arrive by TMA.  The same kernel computes the transposed product dX = dY W: only
+// the expansion routine differs (the tile is W^T, the reduction runs over weight rows).
+//
+// CTA = 18 warps: warp 0 issues TMA loads of the activation tile (256 tokens x 64 reduction elements), warp 1
+// allocates TMEM and issues the MMAs (128 x 256 x 16, fp32 accumulate in TMEM), warps 2..17 form four groups
+// that expand the weight tile (128 output features x 64 reduction elements) of every fourth k-block each, so
+// that global-load latency of one group overlaps the work of the others.  Group 0 also runs the epilogue
+// (tcgen05.ld -> bias -> convert -> store).  All waits are bounded; a wait that runs out sets the status word
+// and the CTA drains to the common exit where TMEM is released.
+#include "nmg_spmm_simt.cuh"
+
+namespace nmg {
+
+constexpr int TC_BM = 128;    // output features per CTA (MMA M)
+constexpr int TC_BN = 256;    // tokens per CTA (MMA N)
+constexpr int TC_BK = 64;     // reduction elements per stage: one 128-byte swizzle span of 16-bit data
+constexpr int TC_STAGES = 4;
+constexpr int TC_GROUPS = 4;  // expansion groups of 4 warps
+constexpr int TC_THREADS = 32 * (2 + 4 * TC_GROUPS);
+constexpr int TC_A_BYTES = TC_BM * TC_BK * 2;  // 16 KB
+constexpr int TC_B_BYTES = TC_BN * TC_BK * 2;  // 32 KB
+constexpr int TC_TMEM_COLS = 256;
+
+struct TcParams {
+    const uint16_t *pat;  // [nb][Kpn]
+    const void *nval;     // [nb][Kpn][n]
+    const void *bias;     // [out_feats] or NULL
+    void *out;
+    int64_t out_feats;    // M (forward) or K (transposed)
+    int64_t red;          // reduction length: K (forward) or M (transposed)
+    int64_t ntok, ld_out, Kpn, nb;
+    int out_token_major;  // 1: out[token][feature], 0: out[feature][token]
+    int *status;
+};
+
+// ---- tcgen05 / TMEM primitives -------------------------------------------------------------------------
+__device__ __forceinline__ void tmem_alloc(uint32_t *smem_slot, uint32_t cols) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(smem_slot)), "r"(cols) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t cols) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(cols) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_commit(uint64_t *bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void tc_mma_f16(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+          "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+          "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr)
+        : "memory");
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void fence_proxy_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+__device__ __forceinline__ void mbar_arrive(uint64_t *bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+
+// Shared-memory matrix descriptor: K-major operand, 128-byte swizzle, rows of 128 bytes, 8-row groups 1024 bytes
+// apart.  Fields: start address >> 4 (bits 0-13), leading byte offset >> 4 (16-29, unused for swizzled K-major,
+// set to 1), stride byte offset >> 4 (32-45), descriptor version 1 (46-47), layout type 2 = SWIZZLE_128B (61-63).
+__device__ __forceinline__ uint64_t make_sw128_desc(uint32_t smem_addr) {
+    return (uint64_t)((smem_addr >> 4) & 0x3FFF) | ((uint64_t)1 << 16) | ((uint64_t)(1024 >> 4) << 32) | ((uint64_t)1 << 46) |
+           ((uint64_t)2 << 61);
+}
+// Instruction descriptor (kind::f16): D = fp32 (bits 4-5 = 1), A / B format (7-9, 10-12: 0 = f16, 1 = bf16), both
+// K-major (15, 16 = 0), N >> 3 (17-22), M >> 4 (24-28).
+template <typename T> __device__ __forceinline__ uint32_t make_idesc() {
+    const uint32_t fmt = sizeof(T) == 2 && DT<T>::id == NMG_BF16 ? 1u : 0u;
+    return (1u << 4) | (fmt << 7) | (fmt << 10) | ((uint32_t)(TC_BN >> 3) << 17) | ((uint32_t)(TC_BM >> 4) << 24);
+}
+
+template <typename T> __device__ __forceinline__ uint16_t bits16(T v);
+template <> __device__ __forceinline__ uint16_t bits16<__half>(__half v) { return __half_as_ushort(v); }
+template <> __device__ __forceinline__ uint16_t bits16<__nv_bfloat16>(__nv_bfloat16 v) { return __bfloat16_as_ushort(v); }
+
+// ---- weight-tile expansion ------------------------------------------------------------------------------
+// Forward: tile rows are weight rows feat0 .. feat0+127, tile columns are weight columns kb*64 .. +63.
+// A task is (row-block, 8-column chunk): it reads 8 pattern ids and 8*n values and writes, for each of the m rows
+// of the row-block, one 16-byte chunk of the swizzled tile.
+template <int N_, int M_, typename T>
+__device__ __forceinline__ void expand_forward(char *a_tile, const TcParams &prm, const uint32_t *tbl, int64_t feat0, int64_t kb,
+                                               int gtid) {
+    constexpr int RB = TC_BM / M_;
+    constexpr int C = Order<N_, M_>::C;
+    const uint16_t *nval = static_cast<const uint16_t *>(prm.nval);
+    for (int t = gtid; t < RB * 8; t += 128) {
+        const int c8 = t & 7, rbl = t >> 3;
+        const int64_t mb = feat0 / M_ + rbl;
+        uint32_t ord[8];
+        uint16_t v[8 * N_];
+        if (mb < prm.nb) {
+            const int64_t e0 = mb * prm.Kpn + kb * TC_BK + c8 * 8;
+            const uint4 pp = __ldg(reinterpret_cast<const uint4 *>(prm.pat + e0));
+            const uint32_t pw[4] = {pp.x, pp.y, pp.z, pp.w};
+#pragma unroll
+            for (int i = 0; i < 8; i++) ord[i] = tbl[min((pw[i >> 1] >> ((i & 1) * 16)) & 0xffffu, (uint32_t)(C - 1))];
+#pragma unroll
+            for (int q = 0; q < N_; q++) {
+                const uint4 vv = __ldg(reinterpret_cast<const uint4 *>(nval + e0 * N_) + q);
+                const uint32_t vw[4] = {vv.x, vv.y, vv.z, vv.w};
+#pragma unroll
+                for (int i = 0; i < 8; i++) v[q * 8 + i] = (uint16_t)((vw[i >> 1] >> ((i & 1) * 16)) & 0xffffu);
+            }
+        } else {
+#pragma unroll
+            for (int i = 0; i < 8; i++) ord[i] = 0xffffffffu;
+#pragma unroll
+            for (int i = 0; i < 8 * N_; i++) v[i] = 0;
+        }
+#pragma unroll
+        for (int r = 0; r < M_; r++) {
+            uint32_t w[4] = {0, 0, 0, 0};
+#pragma unroll
+            for (int kk = 0; kk < 8; kk++) {
+                uint32_t e = 0;
+#pragma unroll
+                for (int s = 0; s < N_; s++)
+                    if (((ord[kk] >> (8 * s)) & 0xffu) == (uint32_t)r) e = v[kk * N_ + s];
+                w[kk >> 1] |= e << ((kk & 1) * 16);
+            }
+            const int row = rbl * M_ + r;
+            *reinterpret_cast<uint4 *>(a_tile + row * 128 + ((c8 ^ (row & 7)) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
+        }
+    }
+}
+
+// Transposed: tile rows are weight columns feat0 .. feat0+127, tile columns are weight rows kb*64 .. +63.
+// A task is (weight column, 8-row chunk); the chunk spans 8 / m row-blocks (or half of one when m = 16).
+template <int N_, int M_, typename T>
+__device__ __forceinline__ void expand_transposed(char *a_tile, const TcParams &prm, const uint32_t *tbl, int64_t feat0, int64_t kb,
+                                                  int gtid) {
+    constexpr int C = Order<N_, M_>::C;
+    const uint16_t *nval = static_cast<const uint16_t *>(prm.nval);
+    for (int t = gtid; t < TC_BM * 8; t += 128) {
+        const int kcol = t & 127, c8 = t >> 7;
+        const int64_t kg = feat0 + kcol;
+        const int64_t r0 = kb * TC_BK + c8 * 8;  // first weight row of the chunk
+        uint32_t w[4] = {0, 0, 0, 0};
+        constexpr int ENT = M_ <= 8 ? 8 / M_ : 1;
+#pragma unroll
+        for (int j = 0; j < ENT; j++) {
+            const int64_t mb = r0 / M_ + j;
+            if (mb >= prm.nb) continue;
+            const int64_t e = mb * prm.Kpn + kg;
+            const uint32_t ord = tbl[min((uint32_t)__ldg(prm.pat + e), (uint32_t)(C - 1))];
+            const int base = M_ <= 8 ? j * M_ : 0;
+            const int first = M_ <= 8 ? 0 : (int)(r0 % M_);  // m = 16: this chunk covers rows first .. first+7 of the block
+#pragma unroll
+            for (int s = 0; s < N_; s++) {
+                const uint32_t val = __ldg(nval + e * N_ + s);
+                const int row = (int)((ord >> (8 * s)) & 0xffu) - first;
+#pragma unroll
+                for (int r = 0; r < (M_ <= 8 ? M_ : 8); r++)
+                    if (row == r) w[(base + r) >> 1] |= val << (((base + r) & 1) * 16);
+            }
+        }
+        *reinterpret_cast<uint4 *>(a_tile + kcol * 128 + ((c8 ^ (kcol & 7)) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
+    }
+}
+
+// ---- the kernel -------------------------------------------------------------------------------------------
+template <int N_, int M_, typename T, bool TRANSPOSED>
+__global__ void __launch_bounds__(TC_THREADS, 1)
+spmm_tc_kernel(const TcParams prm, const __grid_constant__ CUtensorMap tmap) {
+    static_assert(TC_BM % M_ == 0 && N_ <= 4, "tile must hold whole row-blocks; pattern rows are packed in 32 bits");
+    constexpr Order<N_, M_> ORD{};
+    constexpr int C = Order<N_, M_>::C;
+
+    extern __shared__ char smem_raw[];
+    char *smem = reinterpret_cast<char *>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    char *a_stages = smem;
+    char *b_stages = smem + TC_STAGES * TC_A_BYTES;
+    uint64_t *full_a = reinterpret_cast<uint64_t *>(smem + TC_STAGES * (TC_A_BYTES + TC_B_BYTES));
+    uint64_t *full_b = full_a + TC_STAGES;
+    uint64_t *empty = full_b + TC_STAGES;
+    uint64_t *tmem_full = empty + TC_STAGES;
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(tmem_full + 1);
+    uint32_t *tbl = tmem_slot + 2;  // [C] rows of the pattern's slots, 8 bits each
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int64_t tok0 = (int64_t)blockIdx.x * TC_BN;
+    const int64_t feat0 = (int64_t)blockIdx.y * TC_BM;
+    const int64_t nkb = (prm.red + TC_BK - 1) / TC_BK;
+
+    if (tid == 0) {
+        for (int s = 0; s < TC_STAGES; s++) {
+            mbar_init(&full_a[s], 128);
+            mbar_init(&full_b[s], 1);
+            mbar_init(&empty[s], 1);
+        }
+        mbar_init(tmem_full, 1);
+        mbar_fence_init();
+    }
+    for (int p = tid; p < C; p += TC_THREADS) {
+        // compile-time table -> shared memory (pattern ids index it at run time); unused slots hold 0xff
+        uint32_t packed = 0xffffffffu;
+        for (int s = 0; s < N_; s++) packed = (packed & ~(0xffu << (8 * s))) | ((uint32_t)(uint8_t)ORD.v[p * Order<N_, M_>::LD + s] << (8 * s));
+        tbl[p] = packed;
+    }
+    if (warp == 1) tmem_alloc(tmem_slot, TC_TMEM_COLS);
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0) {
+        // ------------------------------------------------------------------ TMA producer (one lane)
+        if (lane == 0) {
+            for (int64_t kb = 0; kb < nkb; kb++) {
+                const int s = (int)(kb % TC_STAGES);
+                const uint32_t ph = (uint32_t)((kb / TC_STAGES) & 1);
+                if (!mbar_wait_bounded(&empty[s], ph ^ 1, prm.status, 11)) break;
+                mbar_expect_tx(&full_b[s], TC_B_BYTES);
+                tma_load_2d(b_stages + s * TC_B_BYTES, &tmap, (int)(kb * TC_BK), (int)tok0, &full_b[s]);
+            }
+        }
+    } else if (warp == 1) {
+        // ------------------------------------------------------------------ MMA issuer (one lane)
+        if (lane == 0) {
+            const uint32_t idesc = make_idesc<T>();
+            bool ok = true;
+            for (int64_t kb = 0; kb < nkb && ok; kb++) {
+                const int s = (int)(kb % TC_STAGES);
+                const uint32_t ph = (uint32_t)((kb / TC_STAGES) & 1);
+                ok = mbar_wait_bounded(&full_a[s], ph, prm.status, 12) && mbar_wait_bounded(&full_b[s], ph, prm.status, 13);
+                if (!ok) break;
+                tc_fence_after();
+                const uint64_t adesc = make_sw128_desc(smem_u32(a_stages + s * TC_A_BYTES));
+                const uint64_t bdesc = make_sw128_desc(smem_u32(b_stages + s * TC_B_BYTES));
+#pragma unroll
+                for (int k = 0; k < TC_BK / 16; k++)  // 16 elements = 32 bytes = 2 descriptor units per step
+                    tc_mma_f16(tmem_base, adesc + 2 * k, bdesc + 2 * k, idesc, (kb | k) != 0 ? 1u : 0u);
+                tc_commit(&empty[s]);  // arrives when the MMAs above have read the stage
+            }
+            tc_commit(tmem_full);      // arrives when every MMA has written TMEM (also on the error path)
+        }
+    } else {
+        // ------------------------------------------------------------------ expansion groups
+        const int group = (warp - 2) >> 2;
+        const int gtid = tid - 64 - group * 128;
+        for (int64_t kb = group; kb < nkb; kb += TC_GROUPS) {
+            const int s = (int)(kb % TC_STAGES);
+            const uint32_t ph = (uint32_t)((kb / TC_STAGES) & 1);
+            if (!mbar_wait_bounded(&empty[s], ph ^ 1, prm.status, 14)) break;
+            char *a_tile = a_stages + s * TC_A_BYTES;
+            if (TRANSPOSED) expand_transposed<N_, M_, T>(a_tile, prm, tbl, feat0, kb, gtid);
+            else expand_forward<N_, M_, T>(a_tile, prm, tbl, feat0, kb, gtid);
+            fence_proxy_async_smem();  // generic-proxy stores -> visible to the tensor core's async-proxy reads
+            mbar_arrive(&full_a[s]);
+        }
+        if (group == 0) {
+            // -------------------------------------------------------------- epilogue
+            if (mbar_wait_bounded(tmem_full, 0, prm.status, 15)) {
+                tc_fence_after();
+                const int q = warp & 3;  // TMEM lane quarter this warp may read
+                const int64_t feat = feat0 + q * 32 + lane;
+                const bool feat_ok = feat < prm.out_feats;
+                T *out = static_cast<T *>(prm.out);
+                const float b = (prm.bias && feat_ok) ? DT<T>::to_f32(static_cast<const T *>(prm.bias)[feat]) : 0.f;
+                for (int c = 0; c < TC_BN / 32; c++) {
+                    uint32_t r[32];
+                    tmem_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(c * 32), r);
+                    if (tok0 + c * 32 >= prm.ntok) continue;  // warp-uniform
+                    if (feat_ok) {
+#pragma unroll
+                        for (int j = 0; j < 32; j++) {
+                            const int64_t tok = tok0 + c * 32 + j;
+                            if (tok < prm.ntok) {
+                                const T o = DT<T>::from_f32(__uint_as_float(r[j]) + b);
+                                if (prm.out_token_major) out[tok * prm.ld_out + feat] = o;
+                                else out[feat * prm.ld_out + tok] = o;
+                            }
+                        }
+                    }
+                }
+                tc_fence_before();
+            }
+        }
+    }
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        tmem_dealloc(tmem_base, TC_TMEM_COLS);
+    }
+}
+
+// ------------------------------------------------------------------------------------------------------ host side
+bool tc_supported(const Geo &geo, int dtype) {
+    if (dtype != NMG_F16 && dtype != NMG_BF16) return false;
+    return (geo.n == 1 && geo.m == 4) || (geo.n == 2 && geo.m == 4) || (geo.n == 1 && geo.m == 8) || (geo.n == 2 && geo.m == 8) ||
+           (geo.n == 1 && geo.m == 16);
+}
+
+static size_t tc_smem_bytes(int C) {
+    return (size_t)TC_STAGES * (TC_A_BYTES + TC_B_BYTES) + (3 * TC_STAGES + 1) * 8 + 16 + (size_t)C * 4 + 1024;
+}
+
+template <int N_, int M_, typename T, bool TR>
+static int tc_launch_one(const TcParams &p, const CUtensorMap &tm, cudaStream_t st) {
+    const size_t smem = tc_smem_bytes((int)comb(N_, M_));
+    dim3 grid((unsigned)((p.ntok + TC_BN - 1) / TC_BN), (unsigned)((p.out_feats + TC_BM - 1) / TC_BM));
+    if (grid.y > 65535) NMG_FAIL(NMG_ERR_UNSUPPORTED, "too many output features for one launch");
+    NMG_CUDA(cudaFuncSetAttribute(spmm_tc_kernel<N_, M_, T, TR>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    spmm_tc_kernel<N_, M_, T, TR><<<grid, TC_THREADS, smem, st>>>(p, tm);
+    NMG_CUDA(cudaGetLastError());
+    return NMG_OK;
+}
+
+template <int N_, int M_>
+static int tc_launch_nm(int dtype, bool transposed, const TcParams &p, const CUtensorMap &tm, cudaStream_t st) {
+    if (dtype == NMG_F16) return transposed ? tc_launch_one<N_, M_, __half, true>(p, tm, st) : tc_launch_one<N_, M_, __half, false>(p, tm, st);
+    return transposed ? tc_launch_one<N_, M_, __nv_bfloat16, true>(p, tm, st) : tc_launch_one<N_, M_, __nv_bfloat16, false>(p, tm, st);
+}
+
+// act: [tokens][ld_act] with the reduction axis contiguous (X for the forward, dY for the transposed product).
+int tc_matmul(const Geo &geo, int dtype, bool transposed, const uint16_t *pat, const void *nval, const void *act,
+              int64_t ld_act, int64_t tokens, const void *bias, void *out, int64_t ld_out, int out_token_major,
+              cudaStream_t st) {
+    const int64_t red = transposed ? geo.M : geo.K;
+    CUtensorMap tm;
+    int rc = encode_tmap_2d(&tm, dtype, act, (uint64_t)red, (uint64_t)tokens, (uint64_t)ld_act, TC_BK, TC_BN, 1);
+    if (rc) return rc;
+    int *status = nullptr;
+    if ((rc = get_status_word(&status))) return rc;
+    TcParams p{pat, nval, bias, out, transposed ? geo.K : geo.M, red, tokens, ld_out, natural_width(geo), geo.nb, out_token_major, status};
+    const ProfileEvents pe = take_profile_events();
+    if (pe.start) NMG_CUDA(cudaEventRecord(pe.start, st));
+    rc = NMG_ERR_UNSUPPORTED;
+    if (geo.n == 1 && geo.m == 4) rc = tc_launch_nm<1, 4>(dtype, transposed, p, tm, st);
+    else if (geo.n == 2 && geo.m == 4) rc = tc_launch_nm<2, 4>(dtype, transposed, p, tm, st);
+    else if (geo.n == 1 && geo.m == 8) rc = tc_launch_nm<1, 8>(dtype, transposed, p, tm, st);
+    else if (geo.n == 2 && geo.m == 8) rc = tc_launch_nm<2, 8>(dtype, transposed, p, tm, st);
+    else if (geo.n == 1 && geo.m == 16) rc = tc_launch_nm<1, 16>(dtype, transposed, p, tm, st);
+    else set_error("no tensor-core kernel for %d:%d", geo.n, geo.m);
+    if (rc == NMG_OK && pe.stop) NMG_CUDA(cudaEventRecord(pe.stop, st));
+    return rc;
+}
+
+}  // namespace nmg

@@ -108,6 +108,22 @@ class GroupedNMTensor:
     def shape(self):
         return torch.Size(self.nm_strides["dense_shape"])
 
+    def packed(self):
+        """Column-ordered device copy used by the tensor-core and transposed kernels (``nmg_pack``).
+
+        Built on first use and kept while ``val`` / ``idx`` are the same tensors at the same version; it is a
+        cache, never pickled."""
+        s = self.nm_strides
+        if len(s["dense_shape"]) != 2 or s["sparse_dim"] != 0:
+            raise ValueError("the packed copy exists for 2-D weights with n:m blocks along dim 0")
+        key = (self.val.data_ptr(), self.val._version, self.idx.data_ptr(), self.idx._version, self.val.dtype)
+        cache = self.__dict__.get("_packed_cache")
+        if cache is None or cache[0] != key:
+            M, K = s["dense_shape"]
+            cache = (key, ops.pack(self.val, self.idx, int(M), int(K), s["n"], s["m"], s["group_size"]))
+            self.__dict__["_packed_cache"] = cache
+        return cache[1]
+
     def to(self, device=None, dtype=None, non_blocking=False, copy=False):
         """Same layout on another device / in another floating dtype (indices are dtype independent)."""
         val = self.val.to(device=device, dtype=dtype, non_blocking=non_blocking, copy=copy)

@@ -55,10 +55,15 @@ def _weight_geometry(weight):
     return gnm, int(M), int(K), s["n"], s["m"], s["group_size"]
 
 
+def _packed_or_none(gnm):
+    """The cached column-ordered copy for 16-bit weights (the tensor-core kernels read it), else None."""
+    return gnm.packed() if gnm.val.dtype in (torch.float16, torch.bfloat16) and gnm.val.is_cuda else None
+
+
 def sparse_dense_mul_dispatch(weight, dense2d, bias, layout):
     """One C-ABI call; replaces the compile-or-load + ctypes call of the reference (sten_impls.py:44-140)."""
     gnm, M, K, n, m, g = _weight_geometry(weight)
-    return ops.spmm(gnm.val, gnm.idx, M, K, n, m, g, dense2d, bias=bias, layout=layout)
+    return ops.spmm(gnm.val, gnm.idx, M, K, n, m, g, dense2d, bias=bias, layout=layout, packed=_packed_or_none(gnm))
 
 
 def _linear_fwd(ctx, inputs, output_sparsifiers):
@@ -88,7 +93,7 @@ def _linear_bwd(ctx, grad_outputs, input_sparsifiers):
     dy2d = dy.reshape(-1, M)
     dx = dw = db = None
     if needs[0]:
-        dx = ops.spmm_t(gnm.val, gnm.idx, M, K, n, m, g, dy2d).reshape(x.shape)
+        dx = ops.spmm_t(gnm.val, gnm.idx, M, K, n, m, g, dy2d, packed=_packed_or_none(gnm)).reshape(x.shape)
     if needs[1]:
         # dense weight gradient (training of nmg weights is outside the inference hot path): plain GEMM
         dw = dy2d.t().mm(x.reshape(-1, K))
@@ -121,7 +126,7 @@ def _mm_bwd(ctx, grad_outputs, input_sparsifiers):
         dw = dc.mm(b.t())
     if needs[1]:
         # dB = W^T dC : the transposed kernel computes (dC^T W)[N, K]; hand back its transpose
-        db = ops.spmm_t(gnm.val, gnm.idx, M, K, n, m, g, dc.t().contiguous()).t()
+        db = ops.spmm_t(gnm.val, gnm.idx, M, K, n, m, g, dc.t().contiguous(), packed=_packed_or_none(gnm)).t()
     return dw, db
 
 

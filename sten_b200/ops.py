@@ -93,7 +93,21 @@ def _row_major_2d(t):
     return t, (t.shape[1] if t.is_contiguous() else t.stride(0))
 
 
-def spmm(val, idx, M, K, n, m, g, act, bias=None, layout=nat.NMG_ACT_TOKEN_MAJOR, algo=nat.NMG_ALGO_AUTO, out=None):
+def pack(val, idx, M, K, n, m, g):
+    """Column-ordered device copy of a weight (opaque uint8 buffer) for the tensor-core and transposed kernels."""
+    dev = _require_cuda(val, idx)
+    code = _dtype_code(val)
+    val, idx = val.contiguous(), idx.contiguous()
+    L = nat.lib()
+    nbytes = L.nmg_packed_bytes(M, K, n, m, g, code)
+    buf = torch.empty(nbytes, dtype=torch.uint8, device=dev)
+    with torch.cuda.device(dev):
+        nat.check(L.nmg_pack(val.data_ptr(), idx.data_ptr(), M, K, n, m, g, code, buf.data_ptr(), nbytes, _stream(dev)))
+    return buf
+
+
+def spmm(val, idx, M, K, n, m, g, act, bias=None, layout=nat.NMG_ACT_TOKEN_MAJOR, algo=nat.NMG_ALGO_AUTO, out=None,
+         packed=None):
     """layout TOKEN_MAJOR: act [tokens, K] -> out [tokens, M] = act @ W^T (+ bias)
        layout K_MAJOR:     act [K, tokens] -> out [M, tokens] = W @ act   (+ bias per row)"""
     dev = _require_cuda(val, idx, act, bias)
@@ -114,14 +128,16 @@ def spmm(val, idx, M, K, n, m, g, act, bias=None, layout=nat.NMG_ACT_TOKEN_MAJOR
         bias = bias.contiguous()
     L = nat.lib()
     with torch.cuda.device(dev):
-        ws, nbytes = _workspace(L.nmg_spmm_workspace_bytes(M, K, tokens, n, m, g, code, layout, algo), dev)
-        nat.check(L.nmg_spmm(val.data_ptr(), idx.data_ptr(), M, K, n, m, g, code, act.data_ptr(), ld_act, tokens,
+        ws, nbytes = _workspace(L.nmg_spmm_workspace_bytes(M, K, tokens, n, m, g, code, layout, algo,
+                                                           1 if packed is not None else 0), dev)
+        nat.check(L.nmg_spmm(val.data_ptr(), idx.data_ptr(), packed.data_ptr() if packed is not None else None, M, K, n,
+                             m, g, code, act.data_ptr(), ld_act, tokens,
                              bias.data_ptr() if bias is not None else None, out.data_ptr(), (out.shape[1] if out.is_contiguous() else out.stride(0)), layout, algo,
                              ws.data_ptr() if ws is not None else None, nbytes, _stream(dev)))
     return out
 
 
-def spmm_t(val, idx, M, K, n, m, g, dy, algo=nat.NMG_ALGO_AUTO):
+def spmm_t(val, idx, M, K, n, m, g, dy, algo=nat.NMG_ALGO_AUTO, packed=None):
     """dy [tokens, M] -> dx [tokens, K] = dy @ W."""
     dev = _require_cuda(val, idx, dy)
     code = _dtype_code(val)
@@ -137,8 +153,10 @@ def spmm_t(val, idx, M, K, n, m, g, dy, algo=nat.NMG_ALGO_AUTO):
     val, idx = val.contiguous(), idx.contiguous()
     L = nat.lib()
     with torch.cuda.device(dev):
-        ws, nbytes = _workspace(L.nmg_spmm_t_workspace_bytes(M, K, tokens, n, m, g, code, algo), dev)
-        nat.check(L.nmg_spmm_t(val.data_ptr(), idx.data_ptr(), M, K, n, m, g, code, dy.data_ptr(), ld_dy, tokens,
+        ws, nbytes = _workspace(L.nmg_spmm_t_workspace_bytes(M, K, tokens, n, m, g, code, algo,
+                                                             1 if packed is not None else 0), dev)
+        nat.check(L.nmg_spmm_t(val.data_ptr(), idx.data_ptr(), packed.data_ptr() if packed is not None else None, M, K,
+                               n, m, g, code, dy.data_ptr(), ld_dy, tokens,
                                dx.data_ptr(), K, algo, ws.data_ptr() if ws is not None else None, nbytes,
                                _stream(dev)))
     return dx

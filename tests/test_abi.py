@@ -21,7 +21,7 @@ def _declared():
 def test_library_exports_every_declared_symbol():
     L = nat.lib()
     names = _declared()
-    assert len(names) >= 11
+    assert len(names) >= 15
     for name in names:
         assert hasattr(L, name), f"{name} is declared in include/nmg_b200.h but not exported"
         assert name in nat.SIGNATURES, f"{name} has no ctypes signature in sten_b200/_native.py"
@@ -51,16 +51,17 @@ def test_invalid_arguments_return_status_not_abort():
     # unknown dtype
     assert L.nmg_sparsify(one, 1, 8, 8, 8, 64, 2, 4, 2, 7, one, one, None) == 1
     # NULL operands
-    assert L.nmg_spmm(None, None, 8, 8, 2, 4, 2, nat.NMG_F32, None, 8, 4, None, None, 8, 0, 0, None, 0, None) == 1
+    assert L.nmg_spmm(None, None, None, 8, 8, 2, 4, 2, nat.NMG_F32, None, 8, 4, None, None, 8, 0, 0, None, 0, None) == 1
     # leading dimension too small
-    assert L.nmg_spmm(one, one, 8, 8, 2, 4, 2, nat.NMG_F32, one, 4, 4, None, one, 8, 0, 0, None, 0, None) == 1
+    assert L.nmg_spmm(one, one, None, 8, 8, 2, 4, 2, nat.NMG_F32, one, 4, 4, None, one, 8, 0, 0, None, 0, None) == 1
     assert b"ld_act" in L.nmg_last_error()
-    assert L.nmg_spmm_t(one, one, 8, 8, 2, 4, 2, nat.NMG_F32, one, 8, 4, one, 4, 0, None, 0, None) == 1
+    assert L.nmg_spmm_t(one, one, None, 8, 8, 2, 4, 2, nat.NMG_F32, one, 8, 4, one, 4, 0, None, 0, None) == 1
     with pytest.raises(nat.NmgError):
         nat.check(1)
     # workspace queries are pure arithmetic
-    assert L.nmg_spmm_workspace_bytes(4096, 4096, 4096, 2, 4, 16, nat.NMG_F32, 0, 0) >= 4096 * 4096 * 4
-    assert L.nmg_spmm_t_workspace_bytes(64, 64, 8, 2, 4, 2, nat.NMG_F32, 0) > 0
+    assert L.nmg_spmm_workspace_bytes(4096, 4096, 4096, 2, 4, 16, nat.NMG_F32, 0, 0, 0) >= 4096 * 4096 * 4
+    assert L.nmg_spmm_t_workspace_bytes(64, 64, 8, 2, 4, 2, nat.NMG_F32, 0, 0) > 0
+    assert L.nmg_packed_bytes(64, 64, 2, 4, 2, nat.NMG_F16) > 64 * 64 // 4 * 6
 
 
 def test_cpu_tensors_are_rejected_loudly():

@@ -94,6 +94,51 @@ def test_half_precision(dtype, n, m, g, M, K, tokens):
     assert rel_fro(np_of(dx), np_of(dy).astype(np.float64) @ np_of(dense).astype(np.float64)) <= TOL_HALF
 
 
+TC_CASES = [
+    # n, m, g, M, K, tokens: multiples of the 128 x 256 x 64 tile, and every kind of remainder
+    (2, 4, 16, 256, 512, 512),
+    (2, 4, 16, 200, 1000, 300),
+    (1, 4, 16, 128, 520, 77),
+    (1, 8, 16, 96, 1024, 256),
+    (2, 8, 16, 264, 904, 130),
+    (1, 16, 16, 400, 776, 64),
+    (2, 4, 4, 1024, 1024, 256),
+]
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("n,m,g,M,K,tokens", TC_CASES)
+def test_tensor_core_forward_and_transposed(dtype, n, m, g, M, K, tokens):
+    from sten_b200 import _native as nat, ops
+    val, idx, x, dense = _problem(M, K, n, m, g, tokens, 50 * n + m + g, dtype)
+    bias = seeded_normal((M,), 6).to(dtype).to(cuda())
+    y = ops.spmm(val, idx, M, K, n, m, g, x, bias=bias, algo=nat.NMG_ALGO_TENSOR)
+    ref64 = np_of(x).astype(np.float64) @ np_of(dense).astype(np.float64).T + np_of(bias).astype(np.float64)
+    assert rel_fro(np_of(y), ref64) <= TOL_HALF
+    # same numbers whether the column-ordered copy is built per call or once
+    packed = ops.pack(val, idx, M, K, n, m, g)
+    assert torch.equal(ops.spmm(val, idx, M, K, n, m, g, x, bias=bias, algo=nat.NMG_ALGO_TENSOR, packed=packed), y)
+    # the SIMT kernels agree with the tensor cores to half-precision rounding
+    y_simt = ops.spmm(val, idx, M, K, n, m, g, x, bias=bias, algo=nat.NMG_ALGO_SIMT)
+    assert rel_fro(np_of(y), np_of(y_simt)) <= TOL_HALF
+    dy = seeded_normal((tokens, M), 97).to(dtype).to(cuda())
+    dx = ops.spmm_t(val, idx, M, K, n, m, g, dy, algo=nat.NMG_ALGO_TENSOR, packed=packed)
+    assert rel_fro(np_of(dx), np_of(dy).astype(np.float64) @ np_of(dense).astype(np.float64)) <= TOL_HALF
+    assert ops.read_status() == 0
+
+
+def test_tensor_core_is_the_default_for_half_precision_and_rejects_fp32():
+    from sten_b200 import _native as nat, ops
+    M, K, n, m, g, tokens = 256, 512, 2, 4, 16, 256
+    val, idx, x, dense = _problem(M, K, n, m, g, tokens, 3, torch.bfloat16)
+    auto = ops.spmm(val, idx, M, K, n, m, g, x)
+    assert torch.equal(auto, ops.spmm(val, idx, M, K, n, m, g, x, algo=nat.NMG_ALGO_TENSOR))
+    val32, idx32, x32, _ = _problem(M, K, n, m, g, tokens, 3)
+    with pytest.raises(nat.NmgError) as e:
+        ops.spmm(val32, idx32, M, K, n, m, g, x32, algo=nat.NMG_ALGO_TENSOR)
+    assert e.value.status == 2
+
+
 def test_against_stored_reference_microkernel_outputs():
     from sten_b200 import ops
     data = np.load(os.path.join(GOLDEN, "spmm_cases.npz"))
@@ -132,7 +177,7 @@ def test_workspace_and_argument_errors():
     L = nat.lib()
     out = torch.empty(tokens, M, device=cuda())
     st = torch.cuda.current_stream().cuda_stream
-    rc = L.nmg_spmm(val.data_ptr(), idx.data_ptr(), M, K, n, m, g, nat.NMG_F32, x.data_ptr(), K, tokens, None,
+    rc = L.nmg_spmm(val.data_ptr(), idx.data_ptr(), None, M, K, n, m, g, nat.NMG_F32, x.data_ptr(), K, tokens, None,
                     out.data_ptr(), M, 0, 0, None, 0, st)
     assert rc == 4 and b"workspace" in L.nmg_last_error()
     with pytest.raises(ValueError):
