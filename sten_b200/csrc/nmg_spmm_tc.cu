@@ -9,10 +9,10 @@
 // against activation tiles that arrive by TMA.  The same kernel computes the transposed product dX = dY W: only
 // the expansion routine differs (the tile is W^T, the reduction runs over weight rows).
 //
-// CTA = 18 warps: warp 0 issues TMA loads of the activation tile (256 tokens x 64 reduction elements), warp 1
-// allocates TMEM and issues the MMAs (128 x 256 x 16, fp32 accumulate in TMEM), warps 2..17 form four groups
-// that expand the weight tile (128 output features x 64 reduction elements) of every fourth k-block each, so
-// that global-load latency of one group overlaps the work of the others.  Group 0 also runs the epilogue
+// CTA = 14 warps: warp 0 issues TMA loads of the activation tile (256 tokens x 64 reduction elements), warp 1
+// allocates TMEM and issues the MMAs (128 x 256 x 16, fp32 accumulate in TMEM), warps 2..13 form three groups
+// that expand the weight tile (128 output features x 64 reduction elements) of every third k-block each; every
+// group fetches its next tile's compressed data into registers before it scatters the current one.  Group 0 also runs the epilogue
 // (tcgen05.ld -> bias -> convert -> store).  All waits are bounded; a wait that runs out sets the status word
 // and the CTA drains to the common exit where TMEM is released.
 #include "nmg_spmm_simt.cuh"
@@ -23,7 +23,7 @@ constexpr int TC_BM = 128;    // output features per CTA (MMA M)
 constexpr int TC_BN = 256;    // tokens per CTA (MMA N)
 constexpr int TC_BK = 64;     // reduction elements per stage: one 128-byte swizzle span of 16-bit data
 constexpr int TC_STAGES = 4;
-constexpr int TC_GROUPS = 4;  // expansion groups of 4 warps
+constexpr int TC_GROUPS = 3;  // expansion groups of 4 warps
 constexpr int TC_THREADS = 32 * (2 + 4 * TC_GROUPS);
 constexpr int TC_A_BYTES = TC_BM * TC_BK * 2;  // 16 KB
 constexpr int TC_B_BYTES = TC_BN * TC_BK * 2;  // 32 KB
@@ -38,8 +38,21 @@ struct TcParams {
     int64_t red;          // reduction length: K (forward) or M (transposed)
     int64_t ntok, ld_out, Kpn, nb;
     int out_token_major;  // 1: out[token][feature], 0: out[feature][token]
+    int tiles_f, tiles_t; // output tiles along features / tokens
     int *status;
 };
+
+// Tile order: feature tiles are taken in bands of TC_BAND; inside a band the CTA index runs over the band's feature
+// tiles first, then over token tiles.  CTAs that are resident together then share a few activation tiles (the big
+// operand) through L2 while a band's compressed weight stays L2-resident across consecutive waves.
+constexpr int TC_BAND = 16;
+__device__ __forceinline__ void tile_of_cta(int lin, int tiles_f, int tiles_t, int &tf, int &tt) {
+    const int per_band = TC_BAND * tiles_t;
+    const int band = lin / per_band, within = lin - band * per_band;
+    const int width = min(TC_BAND, tiles_f - band * TC_BAND);
+    tt = within / width;
+    tf = band * TC_BAND + (within - tt * width);
+}
 
 // ---- tcgen05 / TMEM primitives -------------------------------------------------------------------------
 __device__ __forceinline__ void tmem_alloc(uint32_t *smem_slot, uint32_t cols) {
@@ -99,95 +112,136 @@ template <> __device__ __forceinline__ uint16_t bits16<__half>(__half v) { retur
 template <> __device__ __forceinline__ uint16_t bits16<__nv_bfloat16>(__nv_bfloat16 v) { return __bfloat16_as_ushort(v); }
 
 // ---- weight-tile expansion ------------------------------------------------------------------------------
+// A column of a row-block is n values plus a pattern id; its dense form (m halfs, n of them non-zero) is a byte
+// permutation of the packed values and zero.  The per-pattern permutation selectors are tabulated once per CTA
+// in shared memory: sel[p][q] is the PRMT selector that turns (v0 | v1 << 16, 0) into (row 2q | row 2q+1 << 16).
+// Expansion is then M_/2 PRMTs per column, the tile is written with full-width, conflict-free stores, and no
+// separate clearing pass exists.
+//
+// Swizzled K-major tile: element (row, e) lives at row*128 + (((e >> 3) ^ (row & 7)) << 4) + (e & 7)*2.
+template <int M_> struct SelWords {  // the M_/2 16-bit selectors of one pattern, as 32-bit words
+    static constexpr int W = M_ / 4;
+    uint32_t w[W];
+};
+template <int M_> __device__ __forceinline__ SelWords<M_> load_sel(const uint16_t *sel, uint32_t p) {
+    SelWords<M_> r;
+    if constexpr (M_ == 4) r.w[0] = *reinterpret_cast<const uint32_t *>(sel + p * 2);
+    else if constexpr (M_ == 8) { const uint2 v = *reinterpret_cast<const uint2 *>(sel + p * 4); r.w[0] = v.x; r.w[1] = v.y; }
+    else { const uint4 v = *reinterpret_cast<const uint4 *>(sel + p * 8); r.w[0] = v.x; r.w[1] = v.y; r.w[2] = v.z; r.w[3] = v.w; }
+    return r;
+}
+// rows (2q, 2q+1) of the column whose packed values are vv
+template <int M_> __device__ __forceinline__ uint32_t expand_pair(const SelWords<M_> &s, uint32_t vv, int q) {
+    return __byte_perm(vv, 0u, (s.w[q >> 1] >> ((q & 1) * 16)) & 0xffffu);
+}
+
 // Forward: tile rows are weight rows feat0 .. feat0+127, tile columns are weight columns kb*64 .. +63.
-// A task is (row-block, 8-column chunk): it reads 8 pattern ids and 8*n values and writes, for each of the m rows
-// of the row-block, one 16-byte chunk of the swizzled tile.
-template <int N_, int M_, typename T>
-__device__ __forceinline__ void expand_forward(char *a_tile, const TcParams &prm, const uint32_t *tbl, int64_t feat0, int64_t kb,
-                                               int gtid) {
-    constexpr int RB = TC_BM / M_;
-    constexpr int C = Order<N_, M_>::C;
-    const uint16_t *nval = static_cast<const uint16_t *>(prm.nval);
-    for (int t = gtid; t < RB * 8; t += 128) {
-        const int c8 = t & 7, rbl = t >> 3;
-        const int64_t mb = feat0 / M_ + rbl;
-        uint32_t ord[8];
-        uint16_t v[8 * N_];
+// Lane l of a warp owns columns 2l, 2l+1 of the k-block; warp w of the group owns row-blocks w, w+4, ...
+// For every row of the row-block the warp's 32 lanes write the 32 words of the 128-byte tile row at once.
+template <int N_, int M_> struct FwdRegs {
+    static constexpr int RBW = TC_BM / M_ / 4;  // row-blocks per warp
+    uint32_t pat[RBW];                           // pattern ids of the two columns (16 bits each)
+    uint32_t val[RBW][N_];                       // 2 * n halfs
+};
+
+template <int N_, int M_>
+__device__ __forceinline__ void fetch_forward(FwdRegs<N_, M_> &t, const TcParams &prm, int64_t feat0, int64_t kb, int gwarp, int lane) {
+    constexpr int RBW = FwdRegs<N_, M_>::RBW;
+    const uint32_t *nval = static_cast<const uint32_t *>(prm.nval);
+#pragma unroll
+    for (int i = 0; i < RBW; i++) {
+        const int64_t mb = feat0 / M_ + gwarp + 4 * i;
+        const int64_t e2 = (mb * prm.Kpn + kb * TC_BK) / 2 + lane;  // index of the column pair
         if (mb < prm.nb) {
-            const int64_t e0 = mb * prm.Kpn + kb * TC_BK + c8 * 8;
-            const uint4 pp = __ldg(reinterpret_cast<const uint4 *>(prm.pat + e0));
-            const uint32_t pw[4] = {pp.x, pp.y, pp.z, pp.w};
+            t.pat[i] = __ldg(reinterpret_cast<const uint32_t *>(prm.pat) + e2);
 #pragma unroll
-            for (int i = 0; i < 8; i++) ord[i] = tbl[min((pw[i >> 1] >> ((i & 1) * 16)) & 0xffffu, (uint32_t)(C - 1))];
-#pragma unroll
-            for (int q = 0; q < N_; q++) {
-                const uint4 vv = __ldg(reinterpret_cast<const uint4 *>(nval + e0 * N_) + q);
-                const uint32_t vw[4] = {vv.x, vv.y, vv.z, vv.w};
-#pragma unroll
-                for (int i = 0; i < 8; i++) v[q * 8 + i] = (uint16_t)((vw[i >> 1] >> ((i & 1) * 16)) & 0xffffu);
-            }
+            for (int q = 0; q < N_; q++) t.val[i][q] = __ldg(nval + e2 * N_ + q);
         } else {
+            t.pat[i] = 0xffffffffu;
 #pragma unroll
-            for (int i = 0; i < 8; i++) ord[i] = 0xffffffffu;
-#pragma unroll
-            for (int i = 0; i < 8 * N_; i++) v[i] = 0;
-        }
-#pragma unroll
-        for (int r = 0; r < M_; r++) {
-            uint32_t w[4] = {0, 0, 0, 0};
-#pragma unroll
-            for (int kk = 0; kk < 8; kk++) {
-                uint32_t e = 0;
-#pragma unroll
-                for (int s = 0; s < N_; s++)
-                    if (((ord[kk] >> (8 * s)) & 0xffu) == (uint32_t)r) e = v[kk * N_ + s];
-                w[kk >> 1] |= e << ((kk & 1) * 16);
-            }
-            const int row = rbl * M_ + r;
-            *reinterpret_cast<uint4 *>(a_tile + row * 128 + ((c8 ^ (row & 7)) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
+            for (int q = 0; q < N_; q++) t.val[i][q] = 0;
         }
     }
 }
 
-// Transposed: tile rows are weight columns feat0 .. feat0+127, tile columns are weight rows kb*64 .. +63.
-// A task is (weight column, 8-row chunk); the chunk spans 8 / m row-blocks (or half of one when m = 16).
-template <int N_, int M_, typename T>
-__device__ __forceinline__ void expand_transposed(char *a_tile, const TcParams &prm, const uint32_t *tbl, int64_t feat0, int64_t kb,
-                                                  int gtid) {
-    constexpr int C = Order<N_, M_>::C;
-    const uint16_t *nval = static_cast<const uint16_t *>(prm.nval);
-    for (int t = gtid; t < TC_BM * 8; t += 128) {
-        const int kcol = t & 127, c8 = t >> 7;
-        const int64_t kg = feat0 + kcol;
-        const int64_t r0 = kb * TC_BK + c8 * 8;  // first weight row of the chunk
-        uint32_t w[4] = {0, 0, 0, 0};
-        constexpr int ENT = M_ <= 8 ? 8 / M_ : 1;
+template <int N_, int M_>
+__device__ __forceinline__ void write_forward(const FwdRegs<N_, M_> &t, char *a_tile, const uint16_t *sel, int gwarp, int lane) {
+    constexpr int C = (int)comb(N_, M_);
+    constexpr int RBW = FwdRegs<N_, M_>::RBW;
+    const uint32_t col_off = (uint32_t)((lane & 3) * 4);  // word inside the 16-byte chunk
+    const int c8 = lane >> 2;                              // chunk of the two columns
 #pragma unroll
-        for (int j = 0; j < ENT; j++) {
-            const int64_t mb = r0 / M_ + j;
-            if (mb >= prm.nb) continue;
-            const int64_t e = mb * prm.Kpn + kg;
-            const uint32_t ord = tbl[min((uint32_t)__ldg(prm.pat + e), (uint32_t)(C - 1))];
-            const int base = M_ <= 8 ? j * M_ : 0;
-            const int first = M_ <= 8 ? 0 : (int)(r0 % M_);  // m = 16: this chunk covers rows first .. first+7 of the block
+    for (int i = 0; i < RBW; i++) {
+        const int row0 = (gwarp + 4 * i) * M_;
+        const bool live = t.pat[i] != 0xffffffffu;
+        const SelWords<M_> s0 = load_sel<M_>(sel, min(t.pat[i] & 0xffffu, (uint32_t)(C - 1)));
+        const SelWords<M_> s1 = load_sel<M_>(sel, min(t.pat[i] >> 16, (uint32_t)(C - 1)));
+        uint32_t v0, v1;  // packed values (slot 0 | slot 1 << 16) of the lane's two columns
+        if (N_ == 2) { v0 = t.val[i][0]; v1 = t.val[i][1]; }
+        else { v0 = t.val[i][0] & 0xffffu; v1 = t.val[i][0] >> 16; }
 #pragma unroll
-            for (int s = 0; s < N_; s++) {
-                const uint32_t val = __ldg(nval + e * N_ + s);
-                const int row = (int)((ord >> (8 * s)) & 0xffu) - first;
-#pragma unroll
-                for (int r = 0; r < (M_ <= 8 ? M_ : 8); r++)
-                    if (row == r) w[(base + r) >> 1] |= val << (((base + r) & 1) * 16);
-            }
+        for (int q = 0; q < M_ / 2; q++) {
+            const uint32_t a = live ? expand_pair<M_>(s0, v0, q) : 0u;  // rows 2q, 2q+1 of column 0
+            const uint32_t b = live ? expand_pair<M_>(s1, v1, q) : 0u;  // rows 2q, 2q+1 of column 1
+            const int r = row0 + 2 * q;
+            *reinterpret_cast<uint32_t *>(a_tile + r * 128 + (((c8 ^ r) & 7) << 4) + col_off) = __byte_perm(a, b, 0x5410);
+            *reinterpret_cast<uint32_t *>(a_tile + (r + 1) * 128 + (((c8 ^ (r + 1)) & 7) << 4) + col_off) = __byte_perm(a, b, 0x7632);
         }
-        *reinterpret_cast<uint4 *>(a_tile + kcol * 128 + ((c8 ^ (kcol & 7)) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
     }
+}
+
+// Transposed: tile rows are weight columns feat0 .. feat0+127 (one per thread of the group), the tile's K axis is
+// weight rows kb*64 .. +63, i.e. 64/m row-blocks whose expanded columns lie side by side in the thread's row.
+template <int N_, int M_> struct TrRegs {
+    static constexpr int E = TC_BK / M_;  // row-blocks per k-block
+    uint32_t pat[E];                       // 0xffffffff = row-block past the end of the weight
+    uint32_t val[E];                       // n <= 2 halfs
+};
+
+template <int N_, int M_>
+__device__ __forceinline__ void fetch_transposed(TrRegs<N_, M_> &t, const TcParams &prm, int64_t feat0, int64_t kb, int row) {
+    constexpr int E = TrRegs<N_, M_>::E;
+    const int64_t kg = feat0 + row;
+    const uint16_t *nval = static_cast<const uint16_t *>(prm.nval);
+#pragma unroll
+    for (int j = 0; j < E; j++) {
+        const int64_t mb = kb * E + j;
+        t.pat[j] = 0xffffffffu;
+        t.val[j] = 0;
+        if (mb < prm.nb) {
+            const int64_t e = mb * prm.Kpn + kg;
+            t.pat[j] = __ldg(prm.pat + e);
+            if (N_ == 2) t.val[j] = __ldg(reinterpret_cast<const uint32_t *>(nval + e * 2));
+            else t.val[j] = __ldg(nval + e);
+        }
+    }
+}
+
+template <int N_, int M_>
+__device__ __forceinline__ void write_transposed(const TrRegs<N_, M_> &t, char *a_tile, const uint16_t *sel, int row) {
+    constexpr int C = (int)comb(N_, M_);
+    constexpr int E = TrRegs<N_, M_>::E;
+    constexpr int WPE = M_ / 2;  // 32-bit words per expanded column
+    uint32_t w[TC_BK / 2];       // the thread's whole tile row
+#pragma unroll
+    for (int j = 0; j < E; j++) {
+        const bool live = t.pat[j] != 0xffffffffu;
+        const SelWords<M_> s = load_sel<M_>(sel, min(t.pat[j], (uint32_t)(C - 1)));
+#pragma unroll
+        for (int q = 0; q < WPE; q++) w[j * WPE + q] = live ? expand_pair<M_>(s, t.val[j], q) : 0u;
+    }
+    char *rowp = a_tile + row * 128;
+#pragma unroll
+    for (int c = 0; c < 8; c++)
+        *reinterpret_cast<uint4 *>(rowp + (((c ^ row) & 7) << 4)) = make_uint4(w[4 * c], w[4 * c + 1], w[4 * c + 2], w[4 * c + 3]);
 }
 
 // ---- the kernel -------------------------------------------------------------------------------------------
 template <int N_, int M_, typename T, bool TRANSPOSED>
 __global__ void __launch_bounds__(TC_THREADS, 1)
 spmm_tc_kernel(const TcParams prm, const __grid_constant__ CUtensorMap tmap) {
-    static_assert(TC_BM % M_ == 0 && N_ <= 4, "tile must hold whole row-blocks; pattern rows are packed in 32 bits");
+    static_assert((3 * TC_STAGES + 1) * 8 <= 112, "barriers overlap the TMEM slot");
+    static_assert(TC_BM % (4 * M_) == 0 && TC_BK % M_ == 0 && M_ % 4 == 0 && N_ <= 2, "tile must hold whole row-blocks; pattern rows are packed in 32 bits");
     constexpr Order<N_, M_> ORD{};
     constexpr int C = Order<N_, M_>::C;
 
@@ -199,12 +253,15 @@ spmm_tc_kernel(const TcParams prm, const __grid_constant__ CUtensorMap tmap) {
     uint64_t *full_b = full_a + TC_STAGES;
     uint64_t *empty = full_b + TC_STAGES;
     uint64_t *tmem_full = empty + TC_STAGES;
-    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(tmem_full + 1);
-    uint32_t *tbl = tmem_slot + 2;  // [C] rows of the pattern's slots, 8 bits each
+    char *misc = smem + TC_STAGES * (TC_A_BYTES + TC_B_BYTES);        // 1024-byte aligned: barriers first
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(misc + 112);
+    uint16_t *sel = reinterpret_cast<uint16_t *>(misc + 128);          // [C][M_/2] PRMT selectors, 16-byte aligned
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int64_t tok0 = (int64_t)blockIdx.x * TC_BN;
-    const int64_t feat0 = (int64_t)blockIdx.y * TC_BM;
+    int tile_f, tile_t;
+    tile_of_cta((int)blockIdx.x, prm.tiles_f, prm.tiles_t, tile_f, tile_t);
+    const int64_t tok0 = (int64_t)tile_t * TC_BN;
+    const int64_t feat0 = (int64_t)tile_f * TC_BM;
     const int64_t nkb = (prm.red + TC_BK - 1) / TC_BK;
 
     if (tid == 0) {
@@ -216,11 +273,17 @@ spmm_tc_kernel(const TcParams prm, const __grid_constant__ CUtensorMap tmap) {
         mbar_init(tmem_full, 1);
         mbar_fence_init();
     }
-    for (int p = tid; p < C; p += TC_THREADS) {
-        // compile-time table -> shared memory (pattern ids index it at run time); unused slots hold 0xff
-        uint32_t packed = 0xffffffffu;
-        for (int s = 0; s < N_; s++) packed = (packed & ~(0xffu << (8 * s))) | ((uint32_t)(uint8_t)ORD.v[p * Order<N_, M_>::LD + s] << (8 * s));
-        tbl[p] = packed;
+    for (int e = tid; e < C * (M_ / 2); e += TC_THREADS) {
+        // selector for rows (2q, 2q+1) of pattern p: bytes of slot 0 are 0,1, of slot 1 are 2,3, byte 4 is zero
+        const int p = e / (M_ / 2), q = e - p * (M_ / 2);
+        uint32_t code = 0;
+        for (int h = 0; h < 2; h++) {
+            uint32_t nib = 0x44;
+            for (int sl = 0; sl < N_; sl++)
+                if (ORD.v[p * Order<N_, M_>::LD + sl] == 2 * q + h) nib = sl == 0 ? 0x10 : 0x32;
+            code |= nib << (8 * h);
+        }
+        sel[e] = (uint16_t)code;
     }
     if (warp == 1) tmem_alloc(tmem_slot, TC_TMEM_COLS);
     tc_fence_before();
@@ -262,16 +325,37 @@ spmm_tc_kernel(const TcParams prm, const __grid_constant__ CUtensorMap tmap) {
     } else {
         // ------------------------------------------------------------------ expansion groups
         const int group = (warp - 2) >> 2;
+        const int gwarp = (warp - 2) & 3;
         const int gtid = tid - 64 - group * 128;
-        for (int64_t kb = group; kb < nkb; kb += TC_GROUPS) {
-            const int s = (int)(kb % TC_STAGES);
-            const uint32_t ph = (uint32_t)((kb / TC_STAGES) & 1);
-            if (!mbar_wait_bounded(&empty[s], ph ^ 1, prm.status, 14)) break;
-            char *a_tile = a_stages + s * TC_A_BYTES;
-            if (TRANSPOSED) expand_transposed<N_, M_, T>(a_tile, prm, tbl, feat0, kb, gtid);
-            else expand_forward<N_, M_, T>(a_tile, prm, tbl, feat0, kb, gtid);
-            fence_proxy_async_smem();  // generic-proxy stores -> visible to the tensor core's async-proxy reads
-            mbar_arrive(&full_a[s]);
+        // Two register buffers in ping-pong: the global loads of the group's next tile are in flight while the
+        // current one is written, and nothing is copied between the buffers.
+        auto run_group = [&](auto fetch, auto write, auto &buf_a, auto &buf_b) {
+            auto publish = [&](int64_t kb, auto &buf) -> bool {
+                const int s = (int)(kb % TC_STAGES);
+                const uint32_t ph = (uint32_t)((kb / TC_STAGES) & 1);
+                if (!mbar_wait_bounded(&empty[s], ph ^ 1, prm.status, 14)) return false;
+                write(buf, a_stages + s * TC_A_BYTES);
+                fence_proxy_async_smem();  // generic-proxy stores -> visible to the tensor core's async-proxy reads
+                mbar_arrive(&full_a[s]);
+                return true;
+            };
+            if (group < nkb) fetch(buf_a, (int64_t)group);
+            for (int64_t kb = group; kb < nkb; kb += 2 * TC_GROUPS) {
+                if (kb + TC_GROUPS < nkb) fetch(buf_b, kb + TC_GROUPS);
+                if (!publish(kb, buf_a)) break;
+                if (kb + TC_GROUPS >= nkb) break;
+                if (kb + 2 * TC_GROUPS < nkb) fetch(buf_a, kb + 2 * TC_GROUPS);
+                if (!publish(kb + TC_GROUPS, buf_b)) break;
+            }
+        };
+        if (TRANSPOSED) {
+            TrRegs<N_, M_> ra, rb;
+            run_group([&](TrRegs<N_, M_> &t, int64_t kb) { fetch_transposed<N_, M_>(t, prm, feat0, kb, gtid); },
+                      [&](const TrRegs<N_, M_> &t, char *tile) { write_transposed<N_, M_>(t, tile, sel, gtid); }, ra, rb);
+        } else {
+            FwdRegs<N_, M_> ra, rb;
+            run_group([&](FwdRegs<N_, M_> &t, int64_t kb) { fetch_forward<N_, M_>(t, prm, feat0, kb, gwarp, lane); },
+                      [&](const FwdRegs<N_, M_> &t, char *tile) { write_forward<N_, M_>(t, tile, sel, gwarp, lane); }, ra, rb);
         }
         if (group == 0) {
             // -------------------------------------------------------------- epilogue
@@ -317,14 +401,15 @@ bool tc_supported(const Geo &geo, int dtype) {
 }
 
 static size_t tc_smem_bytes(int C) {
-    return (size_t)TC_STAGES * (TC_A_BYTES + TC_B_BYTES) + (3 * TC_STAGES + 1) * 8 + 16 + (size_t)C * 4 + 1024;
+    return (size_t)TC_STAGES * (TC_A_BYTES + TC_B_BYTES) + 128 + (size_t)C * 16 + 1024;
 }
 
 template <int N_, int M_, typename T, bool TR>
 static int tc_launch_one(const TcParams &p, const CUtensorMap &tm, cudaStream_t st) {
     const size_t smem = tc_smem_bytes((int)comb(N_, M_));
-    dim3 grid((unsigned)((p.ntok + TC_BN - 1) / TC_BN), (unsigned)((p.out_feats + TC_BM - 1) / TC_BM));
-    if (grid.y > 65535) NMG_FAIL(NMG_ERR_UNSUPPORTED, "too many output features for one launch");
+    const int64_t ctas = (int64_t)p.tiles_f * p.tiles_t;
+    if (ctas > 0x7fffffff) NMG_FAIL(NMG_ERR_UNSUPPORTED, "too many output tiles for one launch");
+    dim3 grid((unsigned)ctas);
     NMG_CUDA(cudaFuncSetAttribute(spmm_tc_kernel<N_, M_, T, TR>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     spmm_tc_kernel<N_, M_, T, TR><<<grid, TC_THREADS, smem, st>>>(p, tm);
     NMG_CUDA(cudaGetLastError());
@@ -347,7 +432,9 @@ int tc_matmul(const Geo &geo, int dtype, bool transposed, const uint16_t *pat, c
     if (rc) return rc;
     int *status = nullptr;
     if ((rc = get_status_word(&status))) return rc;
-    TcParams p{pat, nval, bias, out, transposed ? geo.K : geo.M, red, tokens, ld_out, natural_width(geo), geo.nb, out_token_major, status};
+    const int64_t feats = transposed ? geo.K : geo.M;
+    TcParams p{pat, nval, bias, out, feats, red, tokens, ld_out, natural_width(geo), geo.nb, out_token_major,
+               (int)((feats + TC_BM - 1) / TC_BM), (int)((tokens + TC_BN - 1) / TC_BN), status};
     const ProfileEvents pe = take_profile_events();
     if (pe.start) NMG_CUDA(cudaEventRecord(pe.start, st));
     rc = NMG_ERR_UNSUPPORTED;

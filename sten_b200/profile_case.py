@@ -24,6 +24,7 @@ def main():
     ap.add_argument("--dtype", default="f32", choices=["f32", "f16", "bf16"])
     ap.add_argument("--algo", default="auto", choices=["auto", "simt", "tensor"])
     ap.add_argument("--reps", type=int, default=3)
+    ap.add_argument("--no-packed", action="store_true", help="rebuild the column-ordered weight copy in every call")
     a = ap.parse_args()
     n, m = map(int, a.nm.split(":"))
     dtype = {"f32": torch.float32, "f16": torch.float16, "bf16": torch.bfloat16}[a.dtype]
@@ -37,14 +38,15 @@ def main():
     dy = torch.randn(a.tokens, M, generator=torch.Generator().manual_seed(2)).to(dev).to(dtype)
     xt = x.t().contiguous()
     wd = w.to(dtype).unsqueeze(0)
+    packed = None if (a.no_packed or dtype == torch.float32) else ops.pack(val, idx, M, K, n, m, g)
 
     def call():
         if a.op == "fwd":
-            return ops.spmm(val, idx, M, K, n, m, g, x, algo=algo)
+            return ops.spmm(val, idx, M, K, n, m, g, x, algo=algo, packed=packed)
         if a.op == "fwd_kmajor":
             return ops.spmm(val, idx, M, K, n, m, g, xt, layout=nat.NMG_ACT_K_MAJOR, algo=algo)
         if a.op == "bwd":
-            return ops.spmm_t(val, idx, M, K, n, m, g, dy, algo=algo)
+            return ops.spmm_t(val, idx, M, K, n, m, g, dy, algo=algo, packed=packed)
         if a.op == "sparsify":
             return ops.sparsify(wd, n, m, g)
         return ops.densify(val, idx, 1, M, K, n, m, g)
