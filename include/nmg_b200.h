@@ -111,6 +111,24 @@ int nmg_spmm_t(const void *val, const int16_t *idx, const void *packed, int64_t 
                int dtype, const void *dy, int64_t ld_dy, int64_t tokens, void *dx, int64_t ld_dx, int algo,
                void *workspace, size_t workspace_bytes, void *stream);
 
+/* Matmul for callers that cannot allocate device memory (no counterpart in the reference, whose host code allocates
+ * every buffer with torch: src/sten/grouped_nm/grouped_nm_tensor.py:652-672, sten_impls.py:127).
+ * Meant for code that runs where cudaMalloc is not an option: under CUDA-graph capture or another stream-ordered
+ * region, in a server that partitioned all of HBM up front, in a callback that may not take allocator locks.
+ * Same arguments and result as nmg_spmm with NMG_ALGO_SIMT, minus the workspace: the scratch (fp32 re-layout of the
+ * activation, 256 + K * round_up(tokens, 128) * 4 bytes) lives in a fixed device array inside the library.
+ *   - limit: that size must not exceed NMG_NOALLOC_SCRATCH_BYTES, else NMG_ERR_UNSUPPORTED (nothing is truncated);
+ *     only n:m in {1:4, 2:4, 1:8, 2:8, 1:16, 3:6} are served (others need an allocated pattern table);
+ *   - every GPU that loads the library holds the array until the process exits;
+ *   - all calls on a device share it: calls that overlap in time on one GPU race and must be serialised by the caller;
+ *   - the first call on a device resolves the array's address and clears its status word (synchronous); make
+ *     it before any stream capture begins.
+ * Calls no cudaMalloc / cudaFree and no allocating library routine. */
+#define NMG_NOALLOC_SCRATCH_BYTES (32u << 20)
+int nmg_spmm_noalloc(const void *val, const int16_t *idx, int64_t M, int64_t K, int n, int m, int g, int dtype,
+                     const void *act, int64_t ld_act, int64_t tokens, const void *bias, void *out, int64_t ld_out,
+                     int layout, void *stream);
+
 /* Measurement helpers (no counterpart in the reference; its profiling is wall-clock around whole operators,
  * src/sten/sten.py:30-49).
  * nmg_profile_next: the next nmg_spmm / nmg_spmm_t call made by this thread records `start_event` immediately before

@@ -12,6 +12,7 @@ LIB_PATH = os.path.join(_HERE, "libnmg_b200.so")
 NMG_F32, NMG_F16, NMG_BF16 = 0, 1, 2
 NMG_ACT_TOKEN_MAJOR, NMG_ACT_K_MAJOR = 0, 1
 NMG_ALGO_AUTO, NMG_ALGO_SIMT, NMG_ALGO_TENSOR = 0, 1, 2
+NMG_NOALLOC_SCRATCH_BYTES = 32 << 20
 
 # name -> (restype, argtypes); must list every function of include/nmg_b200.h (checked by the test-suite)
 _i64, _int, _vp, _sz = ctypes.c_int64, ctypes.c_int, ctypes.c_void_p, ctypes.c_size_t
@@ -30,6 +31,7 @@ SIGNATURES = {
     "nmg_spmm_t_workspace_bytes": (_sz, [_i64, _i64, _i64, _int, _int, _int, _int, _int, _int]),
     "nmg_spmm_t": (_int, [_vp, _vp, _vp, _i64, _i64, _int, _int, _int, _int, _vp, _i64, _i64, _vp, _i64, _int, _vp, _sz,
                           _vp]),
+    "nmg_spmm_noalloc": (_int, [_vp, _vp, _i64, _i64, _int, _int, _int, _int, _vp, _i64, _i64, _vp, _vp, _i64, _int, _vp]),
     "nmg_profile_next": (_int, [_vp, _vp]),
     "nmg_measure_fma_peak": (_int, [ctypes.POINTER(ctypes.c_double), _vp]),
     "nmg_read_status": (_int, [_vp, ctypes.POINTER(_int)]),

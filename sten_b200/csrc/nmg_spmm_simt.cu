@@ -105,14 +105,13 @@ __global__ void spmm_fwd_generic_kernel(const GenFwdParams prm) {
 }
 
 // ------------------------------------------------------------------------------------------ host side
-static bool specialised(int n, int m) {
+bool simt_fwd_specialised(int n, int m) {
     return (n == 1 && m == 4) || (n == 2 && m == 4) || (n == 1 && m == 8) || (n == 2 && m == 8) || (n == 1 && m == 16) ||
            (n == 3 && m == 6);
 }
 
-struct FwdChoice { int tt, stages; };
 // Largest token tile (then two stages before one) whose shared-memory plan fits.
-static bool choose_fwd(const Geo &geo, size_t es, FwdChoice *c, int *box_rows, int *nbox) {
+bool choose_fwd(const Geo &geo, size_t es, FwdChoice *c, int *box_rows, int *nbox) {
     const int rbc = kWarps * (16 / geo.m > 0 ? 16 / geo.m : 1);
     *box_rows = geo.cc < 256 ? geo.cc : 256;
     *nbox = (geo.cc + *box_rows - 1) / *box_rows;
@@ -126,7 +125,7 @@ static bool choose_fwd(const Geo &geo, size_t es, FwdChoice *c, int *box_rows, i
 }
 
 size_t simt_fwd_workspace_bytes(const Geo &geo, int64_t tokens, int dtype, int layout) {
-    if (!specialised(geo.n, geo.m)) return 0;
+    if (!simt_fwd_specialised(geo.n, geo.m)) return 0;
     FwdChoice ch; int br, nbx;
     if (!choose_fwd(geo, dtype_size(dtype), &ch, &br, &nbx)) return 0;  // generic kernel, no scratch
     // fp32 activation copy [K][ld], ld padded to the token tile; always taken so the result does not depend
@@ -140,7 +139,7 @@ int simt_fwd(const Geo &geo, int dtype, const void *val, const int16_t *idx, con
              cudaStream_t st) {
     const bool token_major = layout == NMG_ACT_TOKEN_MAJOR;
     FwdChoice ch; int box_rows, nbox;
-    const bool fast = specialised(geo.n, geo.m) && choose_fwd(geo, dtype_size(dtype), &ch, &box_rows, &nbox);
+    const bool fast = simt_fwd_specialised(geo.n, geo.m) && choose_fwd(geo, dtype_size(dtype), &ch, &box_rows, &nbox);
     if (!fast) {
         PatternTable tab;
         int rc = get_pattern_table(geo.n, geo.m, &tab);

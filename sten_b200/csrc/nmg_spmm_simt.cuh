@@ -65,6 +65,11 @@ __host__ __device__ inline FwdSmemPlan fwd_smem_plan(int cc, int n, int rbc, int
     return p;
 }
 
+// Which (n, m) have a specialised forward kernel, and the tile configuration chosen for a geometry.
+struct FwdChoice { int tt, stages; };
+bool simt_fwd_specialised(int n, int m);
+bool choose_fwd(const Geo &geo, size_t es, FwdChoice *c, int *box_rows, int *nbox);
+
 template <int N_, int M_>
 int simt_fwd_launch(int dtype, int tt, const FwdParams &p, const CUtensorMap &tm, int rbc, size_t smem, bool token_major,
                     int64_t tokens, cudaStream_t st);
