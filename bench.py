@@ -1,25 +1,28 @@
 #!/usr/bin/env python
-"""Benchmark of the grouped n:m hot path:  python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
+"""Benchmark of the grouped n:m hot path.
 
-Workload ("sweep"): the density sweep on one layer -- weight 4096 x 4096 ~ N(0,1) (seed 0) sparsified to grouped
-n:m for n:m in {1:4, 2:4, 1:8, 2:8, 1:16} with g = 16, activations 4096 tokens x 4096 ~ N(0,1) (seed 1), fp32.
-One step is one pass of the hot path over that batch: y = x W^T for each of the five sparse weights.
-metric = useful (non-zero) GFLOP/s = sum over the five of 2*M*K*tokens*n/m, divided by the step time.
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload sharded|sweep] [--impl reference]
+    torchrun --nproc-per-node N ... bench.py --gpus N ...          (one rank per GPU, NCCL)
 
-With N > 1 ranks (torchrun) every rank runs the same sweep on its own 4096-token shard of the batch (token rows
-are independent, so no collective is on the data path): weak scaling, value = N * per-rank work / max-over-ranks
-time.
+Workload "sharded" (default, every N): the large row-sharded matmul.  W 16384 x 16384 ~ N(0, 0.02) (seed 0), rounded
+to bf16, grouped n:m 2:8 with g = 16, split by output rows over the N ranks; activations X 16384 tokens x 16384
+~ N(0, 1) (seed 1) bf16, replicated.  One step computes y = x W^T: every rank multiplies by its row shard and the
+output slices are combined with an NCCL all-gather (overlapped per token panel); with N = 1 there is no collective.
+Total work is fixed, so scaling is "strong".  metric = useful (non-zero) GFLOP/s = 2*M*K*tokens*n/m / step time.
 
-Printed JSON (one line, rank 0):
-  value        device-resident throughput (inputs already in HBM), CUDA events around exactly K steps
-  e2e          same metric through the public plugin API (F.linear on SparseParameterWrapper weights) with pinned
-               HOST activations: the H2D copy of x and the D2H copy of every y are inside the timed region
-  roofline     the dominant kernel (SIMT forward, 2:4) against the fp32 FMA peak measured on this GPU
-  cpu_baseline the reference's CPU-SIMD kernels (oracle/_ref) or the oracle port on this host's cores
-  sweep        per-pattern device times, fp32 and bf16, next to torch.mm (cuBLAS) on the densified weight
-`--impl reference` times only the CPU implementation on a bounded token sample and prints the same line shape.
+Workload "sweep": the 4096 x 4096 density sweep in fp32 (n:m in {1:4, 2:4, 1:8, 2:8, 1:16}, g = 16, 4096 tokens);
+one step is the five matmuls; with N > 1 every rank runs it on its own token shard (weak scaling, no collective).
+
+JSON line (rank 0):
+  value        operands resident in HBM, CUDA events around exactly K steps, max over ranks
+  e2e          same step through the public API with pinned HOST buffers: H2D of x and D2H of y inside the timed region
+  roofline     the dominant kernel, timed alone with events recorded around its launch (nmg_profile_next)
+  cpu_baseline the reference's CPU-SIMD kernels (oracle/_ref) on this host's cores, on a bounded sample
+  sweep        (N = 1) per-pattern device times of the 4096^2 sweep in fp32 and bf16 next to cuBLAS on the densified weight
+`--impl reference` times only the reference's CPU implementation on the bounded sample and prints the same line shape.
 """
 import argparse
+import ctypes
 import json
 import os
 import subprocess
@@ -31,82 +34,92 @@ ROOT = os.path.dirname(os.path.abspath(__file__))
 if ROOT not in sys.path:
     sys.path.insert(0, ROOT)
 
-SWEEP = [(1, 4), (2, 4), (1, 8), (2, 8), (1, 16)]
-G = 16
-M = K = 4096
-TOKENS = 4096
 METRIC = "nmg_spmm_useful_gflops"
 UNIT = "GFLOP/s"
+G = 16
+SWEEP = [(1, 4), (2, 4), (1, 8), (2, 8), (1, 16)]
+SW_M = SW_K = SW_TOK = 4096
+SH_M = SH_K = SH_TOK = 16384
+SH_N, SH_MM = 2, 8
+# bounded CPU sample of the sharded workload: one of eight row shards x 1024 tokens
+CPU_ROWS, CPU_TOK = 2048, 1024
 
 
-def useful_flops(n, m, tokens=TOKENS):
+def useful_flops(M, K, tokens, n, m):
     return 2.0 * M * K * tokens * n / m
 
 
-def step_flops(tokens=TOKENS):
-    return sum(useful_flops(n, m, tokens) for n, m in SWEEP)
+def measured_peaks():
+    try:
+        with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
+            return json.load(f), "MEASURED_PEAKS.json"
+    except (OSError, ValueError):
+        return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}, "fallback"
 
 
-def config_dict(n_gpus):
+def config_dict(workload, n_gpus):
+    if workload == "sharded":
+        return {"workload": "row-sharded matmul: W 16384x16384 N(0,0.02) seed 0 bf16, nmg 2:8 g=16, X 16384x16384 N(0,1) seed 1 bf16",
+                "group_size": G, "parallelism": f"weight rows split over {n_gpus} rank(s), NCCL all-gather of output slices",
+                "l2": "operands (0.5 GB activations + 0.5 GB output per step) exceed the 126 MB L2"}
     return {"workload": "density sweep: W 4096x4096 N(0,1) seed 0, nmg {1:4,2:4,1:8,2:8,1:16} g=16, X 4096x4096 fp32 seed 1",
-            "tokens_per_gpu": TOKENS, "group_size": G, "parallelism": f"token-sharded x{n_gpus}, no collective",
-            "l2": "per-step working set ~0.5 GB (5 outputs of 64 MiB + activations + weights) exceeds the 126 MB L2"}
+            "tokens_per_gpu": SW_TOK, "group_size": G, "parallelism": f"token-sharded x{n_gpus}, no collective",
+            "l2": "per-step working set ~0.5 GB exceeds the 126 MB L2"}
 
 
 # ------------------------------------------------------------------------------------------------ CPU side
-def cpu_spmm_fn(n, m):
-    """(callable(val, idx, x) -> y, kind): the reference's micro-kernels when built for this problem, else the oracle port."""
+def cpu_spmm_fn(M, K, n, m):
+    """(callable(val, idx, x) -> y, kind): the reference's micro-kernels when built for this K, else the oracle port."""
     from oracle import build_ref, nmg_oracle
     if build_ref.load(n, m, G, K) is not None:
         return (lambda val, idx, x: build_ref.spmm(val, idx, x, M, K, n, m, G)), "reference"
     return (lambda val, idx, x: nmg_oracle.spmm(val, idx, x, M, K, n, m, G)), "port"
 
 
-def cpu_problem(tokens):
+def time_cpu(workload, steps, warmup):
+    """Seconds per step of the bounded CPU sample, its useful flops, kind, threads, description."""
     import numpy as np
     import torch
     from oracle import nmg_oracle
-    w = torch.randn(M, K, generator=torch.Generator().manual_seed(0)).numpy()
-    x = torch.randn(TOKENS, K, generator=torch.Generator().manual_seed(1)).numpy()[:tokens]
-    packs = {}
-    for n, m in SWEEP:
-        packs[(n, m)] = nmg_oracle.sparsify(w, n, m, G)
-    return packs, np.ascontiguousarray(x)
-
-
-def time_cpu(steps, warmup, tokens):
-    """Seconds per step (one pass over the five patterns on `tokens` tokens), kind, threads."""
-    from oracle import nmg_oracle
-    packs, x = cpu_problem(tokens)
-    fns = {nm: cpu_spmm_fn(*nm) for nm in SWEEP}
-    kind = "reference" if all(k == "reference" for _, k in fns.values()) else "port"
+    if workload == "sharded":
+        w = (torch.randn(CPU_ROWS, SH_K, generator=torch.Generator().manual_seed(0)) * 0.02).bfloat16().float().numpy()
+        x = torch.randn(CPU_TOK, SH_K, generator=torch.Generator().manual_seed(1)).bfloat16().float().numpy()
+        jobs = [(CPU_ROWS, SH_K, SH_N, SH_MM, *nmg_oracle.sparsify(w, SH_N, SH_MM, G))]
+        flops = useful_flops(CPU_ROWS, SH_K, CPU_TOK, SH_N, SH_MM)
+        desc = f"rows 0..{CPU_ROWS - 1} of W (one of eight row shards) x {CPU_TOK} of {SH_TOK} tokens, fp32 arithmetic"
+    else:
+        w = torch.randn(SW_M, SW_K, generator=torch.Generator().manual_seed(0)).numpy()
+        x = torch.randn(SW_TOK, SW_K, generator=torch.Generator().manual_seed(1)).numpy()[:CPU_TOK]
+        jobs = [(SW_M, SW_K, n, m, *nmg_oracle.sparsify(w, n, m, G)) for n, m in SWEEP]
+        flops = sum(useful_flops(SW_M, SW_K, CPU_TOK, n, m) for n, m in SWEEP)
+        desc = f"{CPU_TOK} of {SW_TOK} tokens, all five patterns, fp32"
+    x = np.ascontiguousarray(x)
+    fns = [cpu_spmm_fn(M, K, n, m) for (M, K, n, m, _, _) in jobs]
+    kind = "reference" if all(k == "reference" for _, k in fns) else "port"
 
     def one_step():
-        for nm in SWEEP:
-            fns[nm][0](packs[nm][0], packs[nm][1], x)
+        for (fn, _), (M, K, n, m, val, idx) in zip(fns, jobs):
+            fn(val, idx, x)
 
     for _ in range(warmup):
         one_step()
     t0 = time.perf_counter()
     for _ in range(steps):
         one_step()
-    dt = (time.perf_counter() - t0) / steps
-    return dt, kind, nmg_oracle.num_threads()
+    return (time.perf_counter() - t0) / steps, flops, kind, nmg_oracle.num_threads(), desc
 
 
 def run_reference(args):
-    rank = int(os.environ.get("RANK", "0"))
-    if rank != 0:
+    if int(os.environ.get("RANK", "0")) != 0:
         return 0
-    tokens = 1024  # bounded sample: a quarter of the batch, every pattern
-    dt, kind, cores = time_cpu(args.steps, args.warmup, tokens)
-    val = step_flops(tokens) / dt / 1e9
-    sample = f"{tokens} of {TOKENS} tokens, all five patterns, fp32, {cores} threads"
+    dt, flops, kind, cores, desc = time_cpu(args.workload, args.steps, args.warmup)
+    val = flops / dt / 1e9
     print(json.dumps({
         "impl": "reference", "metric": METRIC, "value": val, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
-        "warmup": args.warmup, "ms_per_step": dt * 1e3, "higher_is_better": True, "scaling": "weak",
-        "vs_baseline": None, "dtype": "f32", "data": "synthetic", "config": config_dict(args.gpus),
-        "cpu_baseline": {"value": val, "unit": UNIT, "cores": cores, "kind": kind, "sample": sample},
+        "warmup": args.warmup, "ms_per_step": dt * 1e3, "higher_is_better": True,
+        "scaling": "strong" if args.workload == "sharded" else "weak", "vs_baseline": None,
+        "dtype": "f32", "data": "synthetic", "config": config_dict(args.workload, args.gpus),
+        "cpu_baseline": {"value": val, "unit": UNIT, "cores": cores, "kind": kind, "sample": desc},
         "e2e": {"value": val, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }))
@@ -120,9 +133,7 @@ class ClockSampler:
              "clocks_event_reasons.sw_power_cap")
 
     def __init__(self, index):
-        self.index = index
-        self.rows = []
-        self.proc = None
+        self.index, self.rows, self.proc = index, [], None
 
     def start(self):
         try:
@@ -155,17 +166,86 @@ class ClockSampler:
                         reasons.add(name)
             except (ValueError, IndexError):
                 continue
-        sm.sort()
-        return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": max(mx) if mx else None,
+        busy = sorted(sm[len(sm) // 4:]) if sm else []  # the first samples precede the load
+        return {"sm_mhz": busy[len(busy) // 2] if busy else None, "sm_max_mhz": max(mx) if mx else None,
                 "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def timed_loop(fn, steps, barrier, torch, dist, world, dev):
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    e0.record()
+    for _ in range(steps):
+        fn()
+    e1.record()
+    barrier()
+    ms = e0.elapsed_time(e1)
+    if world > 1:
+        t = torch.tensor([ms], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+    return ms / steps
+
+
+def kernel_time(call, torch, nat, reps=6):
+    """Mean device time of the dominant kernel of `call`, events recorded right around its launch."""
+    L = nat.lib()
+    ks, ke = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    ks.record()
+    ke.record()  # torch creates the underlying CUDA events on first record
+    torch.cuda.synchronize()
+    out = []
+    for _ in range(reps):
+        nat.check(L.nmg_profile_next(ks.cuda_event, ke.cuda_event))
+        call()
+        torch.cuda.synchronize()
+        out.append(ks.elapsed_time(ke))
+    out = out[2:] if len(out) > 3 else out
+    return sum(out) / len(out)
+
+
+def sweep_table(torch, ops, nat, dev, peaks, fma_peak):
+    """4096^2 sweep, fp32 (SIMT) and bf16 (tensor cores), next to cuBLAS on the densified weight."""
+    w = torch.randn(SW_M, SW_K, generator=torch.Generator().manual_seed(0)).to(dev)
+    x = torch.randn(SW_TOK, SW_K, generator=torch.Generator().manual_seed(1)).to(dev)
+    rows = []
+
+    def timed(fn, reps=10):
+        fn()
+        torch.cuda.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for _ in range(reps):
+            fn()
+        b.record()
+        torch.cuda.synchronize()
+        return a.elapsed_time(b) / reps
+
+    for dtype, name in ((torch.float32, "f32"), (torch.bfloat16, "bf16")):
+        xd = x.to(dtype)
+        for (n, m) in SWEEP:
+            val, idx = ops.sparsify(w.to(dtype).unsqueeze(0), n, m, G)
+            dense = ops.densify(val, idx, 1, SW_M, SW_K, n, m, G)[0]
+            packed = ops.pack(val, idx, SW_M, SW_K, n, m, G) if dtype != torch.float32 else None
+            o = torch.empty(SW_TOK, SW_M, device=dev, dtype=dtype)
+            t_nmg = timed(lambda: ops.spmm(val, idx, SW_M, SW_K, n, m, G, xd, out=o, packed=packed))
+            t_dense = timed(lambda: torch.mm(xd, dense.t()))
+            useful = useful_flops(SW_M, SW_K, SW_TOK, n, m) / t_nmg / 1e9  # TFLOP/s
+            peak = fma_peak if dtype == torch.float32 else peaks["bf16_tflops"]
+            rows.append({"nm": f"{n}:{m}", "dtype": name, "ms": t_nmg, "useful_tflops": useful,
+                         "bound": "fma" if dtype == torch.float32 else "tensor", "frac_of_peak_useful": useful / peak,
+                         "frac_of_peak_executed": (useful * m / n / peak) if dtype != torch.float32 else useful / peak,
+                         "cublas_dense_ms": t_dense, "speedup_vs_cublas": t_dense / t_nmg})
+            del val, idx, dense, packed, o
+    return rows
 
 
 def run_ours(args):
     import torch
     import torch.distributed as dist
-    import torch.nn.functional as F
     import sten_b200 as sten
     from sten_b200 import _native as nat, ops
+    from sten_b200.sharded import ShardedGroupedNMLinear, row_shard_bounds
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
@@ -175,144 +255,138 @@ def run_ours(args):
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
     sten.set_dispatch_failure("raise")
-
-    # ---- data: same weight on every rank, a different token shard per rank
-    w = torch.randn(M, K, generator=torch.Generator().manual_seed(0)).to(dev)
-    x_host = torch.randn(TOKENS, K, generator=torch.Generator().manual_seed(1 + rank)).pin_memory()
-    x = x_host.to(dev)
-    packs = {nm: ops.sparsify(w.unsqueeze(0), nm[0], nm[1], G) for nm in SWEEP}
-    outs = {nm: torch.empty(TOKENS, M, device=dev) for nm in SWEEP}
-
-    def step():
-        for (n, m) in SWEEP:
-            val, idx = packs[(n, m)]
-            ops.spmm(val, idx, M, K, n, m, G, x, out=outs[(n, m)])
+    peaks, peaks_src = measured_peaks()
 
     def barrier():
         if world > 1:
             dist.barrier()
         torch.cuda.synchronize()
 
+    if args.workload == "sharded":
+        M, K, TOK, n, m = SH_M, SH_K, SH_TOK, SH_N, SH_MM
+        gen = torch.Generator(device=dev).manual_seed(0)
+        bounds = row_shard_bounds(M, world, m)
+        # the same seeded stream on every rank; only this rank's rows are kept
+        w_rows = None
+        chunk = 2048
+        parts = []
+        for r0 in range(0, M, chunk):
+            blk = (torch.randn(chunk, K, generator=gen, device=dev) * 0.02).bfloat16()
+            lo, hi = max(r0, bounds[rank]), min(r0 + chunk, bounds[rank + 1])
+            if lo < hi:
+                parts.append(blk[lo - r0:hi - r0].clone())
+            del blk
+        w_rows = torch.cat(parts)
+        del parts
+        x = torch.randn(TOK, K, generator=torch.Generator(device=dev).manual_seed(1), device=dev).bfloat16()
+        shard = sten.GroupedNMTensor.from_dense(w_rows, n, m, sparse_dim=0, group_size=G, group_dim=1)
+        shard.packed()
+        layer = ShardedGroupedNMLinear(shard, None, M, panels=(4 if world > 1 else 1))
+        total_flops = useful_flops(M, K, TOK, n, m)
+        launches_per_step = layer.panels if world > 1 else 1
+
+        def step():
+            return layer(x)
+
+        x_host = torch.empty(TOK, K, dtype=torch.bfloat16).pin_memory()
+        x_host.copy_(x)
+        y_host = torch.empty(TOK, M, dtype=torch.bfloat16).pin_memory()
+
+        def e2e_step():
+            xd = x_host.to(dev, non_blocking=True)
+            y_host.copy_(layer(xd), non_blocking=True)
+
+        h2d, d2h = x_host.numel() * 2, y_host.numel() * 2
+        dtype_name, scaling = "bf16", "strong"
+    else:
+        M, K, TOK = SW_M, SW_K, SW_TOK
+        w = torch.randn(M, K, generator=torch.Generator().manual_seed(0)).to(dev)
+        x_host = torch.randn(TOK, K, generator=torch.Generator().manual_seed(1 + rank)).pin_memory()
+        x = x_host.to(dev)
+        packs = {nm: ops.sparsify(w.unsqueeze(0), nm[0], nm[1], G) for nm in SWEEP}
+        outs = {nm: torch.empty(TOK, M, device=dev) for nm in SWEEP}
+        total_flops = world * sum(useful_flops(M, K, TOK, n, m) for n, m in SWEEP)
+        launches_per_step = 2 * len(SWEEP)  # activation re-layout + matmul kernel per call
+
+        def step():
+            for (n, m) in SWEEP:
+                val, idx = packs[(n, m)]
+                ops.spmm(val, idx, M, K, n, m, G, x, out=outs[(n, m)])
+
+        sb = sten.SparsityBuilder()
+        layers = torch.nn.ModuleList([torch.nn.Linear(K, M, bias=False, device=dev) for _ in SWEEP])
+        for i, (n, m) in enumerate(SWEEP):
+            layers[i].weight.data.copy_(w)
+            sb.set_weight(f"{i}.weight", initial_sparsifier=sten.GroupedNMSparsifier(n, m, G), out_format=sten.GroupedNMTensor)
+        sparse_layers = sb.sparsify_model_inplace(layers)
+        y_hosts = [torch.empty(TOK, M).pin_memory() for _ in SWEEP]
+
+        def e2e_step():
+            xd = x_host.to(dev, non_blocking=True)
+            with torch.no_grad():
+                for lyr, yh in zip(sparse_layers, y_hosts):
+                    yh.copy_(lyr(xd), non_blocking=True)
+
+        h2d, d2h = x_host.numel() * 4, sum(y.numel() * 4 for y in y_hosts)
+        dtype_name, scaling = "f32", "weak"
+
     for _ in range(args.warmup):
         step()
     sampler = ClockSampler(local)
     if rank == 0:
         sampler.start()
-    barrier()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record()
-    for _ in range(args.steps):
-        step()
-    e1.record()
-    barrier()
-    ms = e0.elapsed_time(e1)
-    if world > 1:
-        t = torch.tensor([ms], device=dev)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        ms = float(t.item())
-    ms_per_step = ms / args.steps
-    value = world * step_flops() / (ms_per_step * 1e-3) / 1e9
-    launches = args.steps * len(SWEEP) * 2  # activation re-layout + matmul kernel per call
+    ms_per_step = timed_loop(step, args.steps, barrier, torch, dist, world, dev)
+    value = total_flops / (ms_per_step * 1e-3) / 1e9
 
-    # ---- end to end through the plugin API with host buffers (weights are model state and stay resident)
-    sb = sten.SparsityBuilder()
-    layers = torch.nn.ModuleList([torch.nn.Linear(K, M, bias=False, device=dev) for _ in SWEEP])
-    for i, (n, m) in enumerate(SWEEP):
-        layers[i].weight.data.copy_(w)
-        sb.set_weight(f"{i}.weight", initial_sparsifier=sten.GroupedNMSparsifier(n, m, G), out_format=sten.GroupedNMTensor)
-    sparse_layers = sb.sparsify_model_inplace(layers)
-    y_host = [torch.empty(TOKENS, M).pin_memory() for _ in SWEEP]
-
-    def e2e_step():
-        xd = x_host.to(dev, non_blocking=True)
-        with torch.no_grad():
-            for layer, yh in zip(sparse_layers, y_host):
-                yh.copy_(layer(xd), non_blocking=True)
-
-    for _ in range(max(1, args.warmup // 2)):
+    for _ in range(2):
         e2e_step()
-    barrier()
-    k_e2e = max(1, args.steps // 2)
-    e0.record()
-    for _ in range(k_e2e):
-        e2e_step()
-    e1.record()
-    barrier()
-    ms_e2e = e0.elapsed_time(e1)
-    if world > 1:
-        t = torch.tensor([ms_e2e], device=dev)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        ms_e2e = float(t.item())
+    k_e2e = max(2, args.steps // 2)
+    ms_e2e = timed_loop(e2e_step, k_e2e, barrier, torch, dist, world, dev)
     clocks = sampler.stop() if rank == 0 else None
-    e2e_value = world * step_flops() / (ms_e2e / k_e2e * 1e-3) / 1e9
-    h2d = x_host.numel() * 4
-    d2h = sum(y.numel() * 4 for y in y_host)
+    e2e_value = total_flops / (ms_e2e * 1e-3) / 1e9
 
     result = None
     if rank == 0:
-        # ---- roofline of the dominant kernel (2:4 SIMT forward), timed alone with events around its launch
-        import ctypes
         L = nat.lib()
-        peak = ctypes.c_double(0.0)
-        nat.check(L.nmg_measure_fma_peak(ctypes.byref(peak), torch.cuda.current_stream().cuda_stream))
-        n, m = 2, 4
-        val, idx = packs[(n, m)]
-        ks, ke = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        ks.record()
-        ke.record()  # torch creates the underlying CUDA events on first record
-        torch.cuda.synchronize()
-        kernel_ms = []
-        for _ in range(8):
-            nat.check(L.nmg_profile_next(ks.cuda_event, ke.cuda_event))
-            ops.spmm(val, idx, M, K, n, m, G, x, out=outs[(n, m)])
-            torch.cuda.synchronize()
-            kernel_ms.append(ks.elapsed_time(ke))
-        kms = sum(kernel_ms[2:]) / len(kernel_ms[2:])
-        achieved = useful_flops(n, m) / (kms * 1e-3) / 1e12
-        roofline = {"bound": "fma", "kernel": "spmm_fwd_simt_kernel<2,4> fp32", "achieved": achieved, "peak": peak.value,
-                    "unit": "TFLOP/s", "frac": achieved / peak.value if peak.value else None,
-                    "peak_source": "fp32 FFMA loop measured in this run (nmg_measure_fma_peak)",
-                    "traffic": None, "ms_per_launch": kms,
-                    "algorithmic_flops_per_launch": useful_flops(n, m)}
-
-        # ---- per-pattern sweep, fp32 and bf16, next to cuBLAS on the densified weight
-        sweep = []
-        for dtype, name in ((torch.float32, "f32"), (torch.bfloat16, "bf16")):
-            xd = x.to(dtype)
-            for (n, m) in SWEEP:
-                v32, i32 = packs[(n, m)]
-                vv = v32.to(dtype)
-                dense = ops.densify(vv, i32, 1, M, K, n, m, G)[0]
-                o = torch.empty(TOKENS, M, device=dev, dtype=dtype)
-
-                def timed(fn, reps=5):
-                    fn()
-                    torch.cuda.synchronize()
-                    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-                    a.record()
-                    for _ in range(reps):
-                        fn()
-                    b.record()
-                    torch.cuda.synchronize()
-                    return a.elapsed_time(b) / reps
-
-                t_nmg = timed(lambda: ops.spmm(vv, i32, M, K, n, m, G, xd, out=o))
-                t_dense = timed(lambda: torch.mm(xd, dense.t()))
-                sweep.append({"nm": f"{n}:{m}", "dtype": name, "ms": t_nmg, "useful_gflops": useful_flops(n, m) / t_nmg / 1e6,
-                              "cublas_dense_ms": t_dense, "speedup_vs_cublas": t_dense / t_nmg})
-
-        # ---- CPU baseline on this host (bounded sample)
-        cpu_tokens = 1024
-        dt, kind, cores = time_cpu(3, 1, cpu_tokens)
-        cpu = {"value": step_flops(cpu_tokens) / dt / 1e9, "unit": UNIT, "cores": cores, "kind": kind,
-               "sample": f"{cpu_tokens} of {TOKENS} tokens, all five patterns, fp32, 3 timed passes"}
-
+        fma = ctypes.c_double(0.0)
+        nat.check(L.nmg_measure_fma_peak(ctypes.byref(fma), torch.cuda.current_stream().cuda_stream))
+        if args.workload == "sharded":
+            rows = bounds[1] - bounds[0]
+            kms = kernel_time(lambda: layer.forward_local(x), torch, nat)
+            alg = useful_flops(rows, K, TOK, n, m)
+            achieved = alg / (kms * 1e-3) / 1e12
+            peak = peaks["bf16_tflops"]
+            roofline = {"bound": "tensor", "kernel": "spmm_tc_kernel<2,8,bf16> (tcgen05, on-the-fly weight expansion)",
+                        "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak,
+                        "peak_source": f"{peaks_src} bf16_tflops (burst: the kernel is timed alone), of measured",
+                        "traffic": None, "ms_per_launch": kms, "algorithmic_flops_per_launch": alg,
+                        "executed_tflops": achieved * m / n, "executed_frac": achieved * m / n / peak,
+                        "note": "algorithmic = useful (non-zero) flops; the tensor cores execute the dense tile, m/n times as many"}
+        else:
+            n, m = 2, 4
+            val, idx = packs[(n, m)]
+            kms = kernel_time(lambda: ops.spmm(val, idx, M, K, n, m, G, x, out=outs[(n, m)]), torch, nat)
+            alg = useful_flops(M, K, TOK, n, m)
+            achieved = alg / (kms * 1e-3) / 1e12
+            roofline = {"bound": "fma", "kernel": "spmm_fwd_simt_kernel<2,4> fp32", "achieved": achieved, "peak": fma.value,
+                        "unit": "TFLOP/s", "frac": achieved / fma.value if fma.value else None,
+                        "peak_source": "fp32 FFMA loop measured in this run (nmg_measure_fma_peak)", "traffic": None,
+                        "ms_per_launch": kms, "algorithmic_flops_per_launch": alg}
+        sweep = None
+        if world == 1 and not args.no_sweep:
+            if args.workload == "sharded":
+                del layer, shard, x, w_rows
+                torch.cuda.empty_cache()
+            sweep = sweep_table(torch, ops, nat, dev, peaks, fma.value)
+        dt, flops, kind, cores, desc = time_cpu(args.workload, 3, 1)
+        cpu = {"value": flops / dt / 1e9, "unit": UNIT, "cores": cores, "kind": kind, "sample": desc + ", 3 timed passes"}
         result = {
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
-            "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
-            "dtype": "f32", "data": "synthetic", "config": config_dict(world),
+            "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": scaling, "vs_baseline": None,
+            "dtype": dtype_name, "data": "synthetic", "config": config_dict(args.workload, world),
             "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
-            "gpu_launches": launches, "clocks": clocks, "roofline": roofline, "cpu_baseline": cpu, "sweep": sweep,
+            "gpu_launches": args.steps * launches_per_step, "clocks": clocks, "roofline": roofline, "cpu_baseline": cpu,
+            "fp32_fma_peak_tflops": fma.value, "sweep": sweep,
         }
     if world > 1:
         dist.barrier()
@@ -328,10 +402,12 @@ def main():
     ap.add_argument("--steps", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="sharded", choices=["sharded", "sweep"])
+    ap.add_argument("--no-sweep", action="store_true", help="skip the per-pattern 4096^2 table")
     args = ap.parse_args()
-    args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
     if args.impl == "reference":
         return run_reference(args)
+    args.warmup = max(args.warmup, 3)
     return run_ours(args)
 
 

@@ -133,3 +133,28 @@ def test_fp16_encoder_layer_shapes_run_through_the_kernels():
         dense = _densified_copy(sparse, block)
         yd = dense.float()(x.float())
     assert rel_fro(np_of(y), np_of(yd)) <= 1e-2
+
+
+def test_row_shards_equal_slices_of_the_full_sparsified_weight():
+    """Sparsifying a row slice gives exactly the tiles of that slice in the full result (tiles never interact), which is
+    what makes row-sharding across GPUs exact; and the sharded layer on one rank is the plain kernel."""
+    import sten_b200 as sten
+    from sten_b200 import ops
+    from sten_b200.sharded import ShardedGroupedNMLinear, row_shard_bounds
+    M, K, n, m, g, R = 256, 1000, 2, 8, 16, 4
+    w = seeded_normal((M, K), 21).to(cuda())
+    full_val, full_idx = ops.sparsify(w.unsqueeze(0), n, m, g)
+    C, cc, nb, nc = ops.geometry(M, K, n, m, g)
+    fv = full_val.view(nc, nb, C, g, n)
+    fi = full_idx.view(nc, nb, C, g, 1)
+    bounds = row_shard_bounds(M, R, m)
+    assert bounds == [0, 64, 128, 192, 256]
+    for r in range(R):
+        val, idx = ops.sparsify(w[bounds[r]:bounds[r + 1]].unsqueeze(0), n, m, g)
+        lo, hi = bounds[r] // m, bounds[r + 1] // m
+        assert torch.equal(val.view(nc, hi - lo, C, g, n), fv[:, lo:hi])
+        assert torch.equal(idx.view(nc, hi - lo, C, g, 1), fi[:, lo:hi])
+    x = seeded_normal((70, K), 22).to(cuda())
+    shard = sten.GroupedNMTensor.from_dense(w, n, m, sparse_dim=0, group_size=g, group_dim=1)
+    layer = ShardedGroupedNMLinear(shard, None, M)
+    assert torch.equal(layer(x), ops.spmm(full_val, full_idx, M, K, n, m, g, x))
