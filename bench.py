@@ -6,8 +6,9 @@
 
 Workload "sharded" (default, every N): the large row-sharded matmul.  W 16384 x 16384 ~ N(0, 0.02) (seed 0), rounded
 to bf16, grouped n:m 2:8 with g = 16, split by output rows over the N ranks; activations X 16384 tokens x 16384
-~ N(0, 1) (seed 1) bf16, replicated.  One step computes y = x W^T: every rank multiplies by its row shard and the
-output slices are combined with an NCCL all-gather (overlapped per token panel); with N = 1 there is no collective.
+~ N(0, 1) (seed 1) bf16, replicated.  One step computes C = W X^T: every rank multiplies by its row panels and the
+output row slabs are combined with in-place NCCL all-gathers (one per row panel, overlapped with the next panel's
+matmul; C = W X^T is kept as [M, tokens] so that slabs are contiguous); with N = 1 there is no collective.
 Total work is fixed, so scaling is "strong".  metric = useful (non-zero) GFLOP/s = 2*M*K*tokens*n/m / step time.
 
 Workload "sweep": the 4096 x 4096 density sweep in fp32 (n:m in {1:4, 2:4, 1:8, 2:8, 1:16}, g = 16, 4096 tokens);
@@ -245,7 +246,7 @@ def run_ours(args):
     import torch.distributed as dist
     import sten_b200 as sten
     from sten_b200 import _native as nat, ops
-    from sten_b200.sharded import ShardedGroupedNMLinear, row_shard_bounds
+    from sten_b200.sharded import RowShardedNMMatmul
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
@@ -265,36 +266,37 @@ def run_ours(args):
     if args.workload == "sharded":
         M, K, TOK, n, m = SH_M, SH_K, SH_TOK, SH_N, SH_MM
         gen = torch.Generator(device=dev).manual_seed(0)
-        bounds = row_shard_bounds(M, world, m)
-        # the same seeded stream on every rank; only this rank's rows are kept
-        w_rows = None
-        chunk = 2048
-        parts = []
-        for r0 in range(0, M, chunk):
-            blk = (torch.randn(chunk, K, generator=gen, device=dev) * 0.02).bfloat16()
-            lo, hi = max(r0, bounds[rank]), min(r0 + chunk, bounds[rank + 1])
-            if lo < hi:
-                parts.append(blk[lo - r0:hi - r0].clone())
-            del blk
-        w_rows = torch.cat(parts)
-        del parts
+        rounds = args.rounds if world > 1 else 1
+        rp = RowShardedNMMatmul.panel_rows(M, world, rounds, m)
+        owned = {(p * world + rank): p for p in range(rounds)}  # global panel index -> local round
+        # the same seeded stream on every rank; only this rank's row panels are kept (block-cyclic over ranks)
+        panels_dense = [None] * rounds
+        for q in range(world * rounds):
+            blk = (torch.randn(rp, K, generator=gen, device=dev) * 0.02).bfloat16()
+            if q in owned:
+                panels_dense[owned[q]] = blk
+            else:
+                del blk
         x = torch.randn(TOK, K, generator=torch.Generator(device=dev).manual_seed(1), device=dev).bfloat16()
-        shard = sten.GroupedNMTensor.from_dense(w_rows, n, m, sparse_dim=0, group_size=G, group_dim=1)
-        shard.packed()
-        layer = ShardedGroupedNMLinear(shard, None, M, panels=(4 if world > 1 else 1))
+        panels = [sten.GroupedNMTensor.from_dense(wd, n, m, sparse_dim=0, group_size=G, group_dim=1) for wd in panels_dense]
+        del panels_dense
+        for pnl in panels:
+            pnl.packed()
+        layer = RowShardedNMMatmul(panels, M)
+        y_dev = torch.empty(M, TOK, dtype=torch.bfloat16, device=dev)
         total_flops = useful_flops(M, K, TOK, n, m)
-        launches_per_step = layer.panels if world > 1 else 1
+        launches_per_step = rounds
 
         def step():
-            return layer(x)
+            return layer(x, out=y_dev)
 
         x_host = torch.empty(TOK, K, dtype=torch.bfloat16).pin_memory()
         x_host.copy_(x)
-        y_host = torch.empty(TOK, M, dtype=torch.bfloat16).pin_memory()
+        y_host = torch.empty(M, TOK, dtype=torch.bfloat16).pin_memory()
 
         def e2e_step():
             xd = x_host.to(dev, non_blocking=True)
-            y_host.copy_(layer(xd), non_blocking=True)
+            y_host.copy_(layer(xd, out=y_dev), non_blocking=True)
 
         h2d, d2h = x_host.numel() * 2, y_host.numel() * 2
         dtype_name, scaling = "bf16", "strong"
@@ -351,9 +353,9 @@ def run_ours(args):
         fma = ctypes.c_double(0.0)
         nat.check(L.nmg_measure_fma_peak(ctypes.byref(fma), torch.cuda.current_stream().cuda_stream))
         if args.workload == "sharded":
-            rows = bounds[1] - bounds[0]
-            kms = kernel_time(lambda: layer.forward_local(x), torch, nat)
-            alg = useful_flops(rows, K, TOK, n, m)
+            from sten_b200.sharded import _default_matmul_rows
+            kms = kernel_time(lambda: _default_matmul_rows(panels[0], x, y_dev[:rp]), torch, nat)
+            alg = useful_flops(rp, K, TOK, n, m)
             achieved = alg / (kms * 1e-3) / 1e12
             peak = peaks["bf16_tflops"]
             roofline = {"bound": "tensor", "kernel": "spmm_tc_kernel<2,8,bf16> (tcgen05, on-the-fly weight expansion)",
@@ -375,7 +377,7 @@ def run_ours(args):
         sweep = None
         if world == 1 and not args.no_sweep:
             if args.workload == "sharded":
-                del layer, shard, x, w_rows
+                del layer, panels, x, y_dev
                 torch.cuda.empty_cache()
             sweep = sweep_table(torch, ops, nat, dev, peaks, fma.value)
         dt, flops, kind, cores, desc = time_cpu(args.workload, 3, 1)
@@ -403,6 +405,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="sharded", choices=["sharded", "sweep"])
+    ap.add_argument("--rounds", type=int, default=4, help="gather rounds (row panels per rank) when N > 1")
     ap.add_argument("--no-sweep", action="store_true", help="skip the per-pattern 4096^2 table")
     args = ap.parse_args()
     if args.impl == "reference":

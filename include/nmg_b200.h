@@ -43,7 +43,9 @@ typedef enum {
 /* Layout of the dense operand of the matmul. */
 typedef enum {
     NMG_ACT_TOKEN_MAJOR = 0, /* X[tokens][K] -> Y[tokens][M]   (F.linear: y = x W^T + b) */
-    NMG_ACT_K_MAJOR = 1      /* B[K][tokens] -> C[M][tokens]   (torch.mm:  C = W B)       */
+    NMG_ACT_K_MAJOR = 1,     /* B[K][tokens] -> C[M][tokens]   (torch.mm:  C = W B)       */
+    NMG_ACT_TOKEN_MAJOR_OUT_ROWS = 2 /* X[tokens][K] -> C[M][tokens] (C = W X^T: output rows follow weight rows, so a
+                                        row shard of W yields a contiguous row slab of C) */
 } nmg_act_layout;
 
 /* Kernel family for nmg_spmm / nmg_spmm_t (NMG_ALGO_AUTO picks by dtype and shape). */
@@ -89,6 +91,7 @@ int nmg_pack(const void *val, const int16_t *idx, int64_t M, int64_t K, int n, i
  * sparse_torch_nn_functional_linear (sten_impls.py:170-173).
  *   layout NMG_ACT_TOKEN_MAJOR: act = X[tokens][ld_act >= K], out = Y[tokens][ld_out >= M], out = X W^T (+ bias[M])
  *   layout NMG_ACT_K_MAJOR:     act = B[K][ld_act >= tokens], out = C[M][ld_out >= tokens], out = W B (+ bias[M] per row)
+ *   layout NMG_ACT_TOKEN_MAJOR_OUT_ROWS: act as TOKEN_MAJOR, out as K_MAJOR
  * act, out, val and bias share `dtype`; accumulation is fp32.  bias may be NULL.
  * packed: result of nmg_pack for the same weight, or NULL (then it is built in the workspace when the chosen kernel
  * needs it).  have_packed in the workspace query says which of the two the caller will do.

@@ -10,7 +10,7 @@ _HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(_HERE, "libnmg_b200.so")
 
 NMG_F32, NMG_F16, NMG_BF16 = 0, 1, 2
-NMG_ACT_TOKEN_MAJOR, NMG_ACT_K_MAJOR = 0, 1
+NMG_ACT_TOKEN_MAJOR, NMG_ACT_K_MAJOR, NMG_ACT_TOKEN_MAJOR_OUT_ROWS = 0, 1, 2
 NMG_ALGO_AUTO, NMG_ALGO_SIMT, NMG_ALGO_TENSOR = 0, 1, 2
 NMG_NOALLOC_SCRATCH_BYTES = 32 << 20
 

@@ -66,7 +66,7 @@ extern "C" size_t nmg_spmm_workspace_bytes(int64_t M, int64_t K, int64_t tokens,
     if (make_geo(M, K, n, m, g, &geo) || tokens < 1 || n < 1) return 0;
     size_t simt = simt_fwd_workspace_bytes(geo, tokens, dtype, layout);
     size_t tensor = 0;
-    if (algo != NMG_ALGO_SIMT && tc_supported(geo, dtype) && layout == NMG_ACT_TOKEN_MAJOR && !have_packed)
+    if (algo != NMG_ALGO_SIMT && tc_supported(geo, dtype) && layout != NMG_ACT_K_MAJOR && !have_packed)
         tensor = natural_bytes(geo, dtype, nullptr) + 512;
     if (algo == NMG_ALGO_TENSOR) return tensor;
     return simt > tensor ? simt : tensor;  // AUTO may take either path depending on operand alignment
@@ -80,10 +80,12 @@ extern "C" int nmg_spmm(const void *val, const int16_t *idx, const void *packed,
     if (rc) return rc;
     if ((rc = check_common(dtype, tokens, val, idx, act, out))) return rc;
     if (n < 1) NMG_FAIL(NMG_ERR_INVALID, "n must be >= 1");
-    if (layout != NMG_ACT_TOKEN_MAJOR && layout != NMG_ACT_K_MAJOR) NMG_FAIL(NMG_ERR_INVALID, "unknown activation layout %d", layout);
-    const bool tm = layout == NMG_ACT_TOKEN_MAJOR;
+    if (layout != NMG_ACT_TOKEN_MAJOR && layout != NMG_ACT_K_MAJOR && layout != NMG_ACT_TOKEN_MAJOR_OUT_ROWS)
+        NMG_FAIL(NMG_ERR_INVALID, "unknown activation layout %d", layout);
+    const bool tm = layout != NMG_ACT_K_MAJOR;               // activation rows are tokens
+    const bool out_tm = layout == NMG_ACT_TOKEN_MAJOR;       // output rows are tokens
     if (ld_act < (tm ? K : tokens)) NMG_FAIL(NMG_ERR_INVALID, "ld_act=%lld is smaller than the activation row", (long long)ld_act);
-    if (ld_out < (tm ? M : tokens)) NMG_FAIL(NMG_ERR_INVALID, "ld_out=%lld is smaller than the output row", (long long)ld_out);
+    if (ld_out < (out_tm ? M : tokens)) NMG_FAIL(NMG_ERR_INVALID, "ld_out=%lld is smaller than the output row", (long long)ld_out);
     if (algo != NMG_ALGO_AUTO && algo != NMG_ALGO_SIMT && algo != NMG_ALGO_TENSOR) NMG_FAIL(NMG_ERR_INVALID, "unknown algo %d", algo);
     cudaStream_t st = (cudaStream_t)stream;
     const bool can_tensor = tm && tensor_ok(geo, dtype, act, ld_act);
@@ -95,7 +97,7 @@ extern "C" int nmg_spmm(const void *val, const int16_t *idx, const void *packed,
         const uint16_t *pat = nullptr;
         const void *nval = nullptr;
         if ((rc = resolve_packed(geo, dtype, val, idx, packed, &ws, &left, &pat, &nval, st))) return rc;
-        return tc_matmul(geo, dtype, false, pat, nval, act, ld_act, tokens, bias, out, ld_out, 1, st);
+        return tc_matmul(geo, dtype, false, pat, nval, act, ld_act, tokens, bias, out, ld_out, out_tm ? 1 : 0, st);
     }
     return simt_fwd(geo, dtype, val, idx, act, ld_act, tokens, bias, out, ld_out, layout, workspace, workspace_bytes, st);
 }

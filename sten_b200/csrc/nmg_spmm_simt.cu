@@ -69,7 +69,7 @@ int launch_widen_to_f32(const void *src, int dtype, int64_t rows, int64_t cols, 
 struct GenFwdParams {
     const void *val; const int16_t *idx; const void *act; const void *bias; void *out; const int8_t *order;
     int64_t M, K, ntok, ld_act, ld_out, nb, nc;
-    int n, m, g, C, cc, token_major;
+    int n, m, g, C, cc, token_major, out_token_major;
 };
 template <typename T>
 __global__ void spmm_fwd_generic_kernel(const GenFwdParams prm) {
@@ -99,7 +99,7 @@ __global__ void spmm_fwd_generic_kernel(const GenFwdParams prm) {
         const int64_t row = mb * prm.m + r;
         if (row >= prm.M) break;
         const float o = acc[r] + (bias ? DT<T>::to_f32(bias[row]) : 0.f);
-        if (prm.token_major) out[tok * prm.ld_out + row] = DT<T>::from_f32(o);
+        if (prm.out_token_major) out[tok * prm.ld_out + row] = DT<T>::from_f32(o);
         else out[row * prm.ld_out + tok] = DT<T>::from_f32(o);
     }
 }
@@ -137,7 +137,8 @@ size_t simt_fwd_workspace_bytes(const Geo &geo, int64_t tokens, int dtype, int l
 int simt_fwd(const Geo &geo, int dtype, const void *val, const int16_t *idx, const void *act, int64_t ld_act,
              int64_t tokens, const void *bias, void *out, int64_t ld_out, int layout, void *ws, size_t ws_bytes,
              cudaStream_t st) {
-    const bool token_major = layout == NMG_ACT_TOKEN_MAJOR;
+    const bool token_major = layout != NMG_ACT_K_MAJOR;      // activation rows are tokens
+    const bool out_token_major = layout == NMG_ACT_TOKEN_MAJOR;
     FwdChoice ch; int box_rows, nbox;
     const bool fast = simt_fwd_specialised(geo.n, geo.m) && choose_fwd(geo, dtype_size(dtype), &ch, &box_rows, &nbox);
     if (!fast) {
@@ -145,7 +146,7 @@ int simt_fwd(const Geo &geo, int dtype, const void *val, const int16_t *idx, con
         int rc = get_pattern_table(geo.n, geo.m, &tab);
         if (rc) return rc;
         GenFwdParams p{val, idx, act, bias, out, tab.order, geo.M, geo.K, tokens, ld_act, ld_out, geo.nb, geo.nc,
-                       geo.n, geo.m, geo.g, geo.C, geo.cc, token_major ? 1 : 0};
+                       geo.n, geo.m, geo.g, geo.C, geo.cc, token_major ? 1 : 0, out_token_major ? 1 : 0};
         if (geo.nb > 65535) NMG_FAIL(NMG_ERR_UNSUPPORTED, "weight has too many row-blocks for one launch");
         dim3 grid((unsigned)((tokens + 127) / 128), (unsigned)geo.nb);
         const ProfileEvents pe = take_profile_events();
@@ -176,7 +177,7 @@ int simt_fwd(const Geo &geo, int dtype, const void *val, const int16_t *idx, con
     if (pe.start) NMG_CUDA(cudaEventRecord(pe.start, st));
 #define NMG_FWD_CASE(N_, M_)                                                                                     \
     if (geo.n == N_ && geo.m == M_) {                                                                            \
-        rc = simt_fwd_launch<N_, M_>(dtype, ch.tt, p, tm, rbc, smem, token_major, tokens, st);                    \
+        rc = simt_fwd_launch<N_, M_>(dtype, ch.tt, p, tm, rbc, smem, out_token_major, tokens, st);                    \
         if (rc == NMG_OK && pe.stop) NMG_CUDA(cudaEventRecord(pe.stop, st));                                      \
         return rc;                                                                                               \
     }

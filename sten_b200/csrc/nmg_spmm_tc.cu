@@ -371,13 +371,31 @@ spmm_tc_kernel(const TcParams prm, const __grid_constant__ CUtensorMap tmap) {
                     tmem_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(c * 32), r);
                     if (tok0 + c * 32 >= prm.ntok) continue;  // warp-uniform
                     if (feat_ok) {
+                        const int64_t tokc = tok0 + c * 32;
+                        const bool vec = !prm.out_token_major && tokc + 32 <= prm.ntok && (prm.ld_out & 7) == 0 &&
+                                         (reinterpret_cast<uintptr_t>(out) & 15) == 0;
+                        if (vec) {  // 32 consecutive tokens of this feature: four 16-byte stores
+                            uint4 *dst = reinterpret_cast<uint4 *>(out + feat * prm.ld_out + tokc);
 #pragma unroll
-                        for (int j = 0; j < 32; j++) {
-                            const int64_t tok = tok0 + c * 32 + j;
-                            if (tok < prm.ntok) {
-                                const T o = DT<T>::from_f32(__uint_as_float(r[j]) + b);
-                                if (prm.out_token_major) out[tok * prm.ld_out + feat] = o;
-                                else out[feat * prm.ld_out + tok] = o;
+                            for (int v = 0; v < 4; v++) {
+                                uint32_t w[4];
+#pragma unroll
+                                for (int h = 0; h < 4; h++) {
+                                    const T lo = DT<T>::from_f32(__uint_as_float(r[8 * v + 2 * h]) + b);
+                                    const T hi = DT<T>::from_f32(__uint_as_float(r[8 * v + 2 * h + 1]) + b);
+                                    w[h] = (uint32_t)bits16<T>(lo) | ((uint32_t)bits16<T>(hi) << 16);
+                                }
+                                dst[v] = make_uint4(w[0], w[1], w[2], w[3]);
+                            }
+                        } else {
+#pragma unroll
+                            for (int j = 0; j < 32; j++) {
+                                const int64_t tok = tokc + j;
+                                if (tok < prm.ntok) {
+                                    const T o = DT<T>::from_f32(__uint_as_float(r[j]) + b);
+                                    if (prm.out_token_major) out[tok * prm.ld_out + feat] = o;
+                                    else out[feat * prm.ld_out + tok] = o;
+                                }
                             }
                         }
                     }

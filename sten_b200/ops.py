@@ -108,19 +108,20 @@ def pack(val, idx, M, K, n, m, g):
 
 def spmm(val, idx, M, K, n, m, g, act, bias=None, layout=nat.NMG_ACT_TOKEN_MAJOR, algo=nat.NMG_ALGO_AUTO, out=None,
          packed=None):
-    """layout TOKEN_MAJOR: act [tokens, K] -> out [tokens, M] = act @ W^T (+ bias)
-       layout K_MAJOR:     act [K, tokens] -> out [M, tokens] = W @ act   (+ bias per row)"""
+    """layout TOKEN_MAJOR:          act [tokens, K] -> out [tokens, M] = act @ W^T (+ bias)
+       layout K_MAJOR:              act [K, tokens] -> out [M, tokens] = W @ act   (+ bias per row)
+       layout TOKEN_MAJOR_OUT_ROWS: act [tokens, K] -> out [M, tokens] = W @ act^T (+ bias per row)"""
     dev = _require_cuda(val, idx, act, bias)
     code = _dtype_code(val)
     if act.dtype != val.dtype or (bias is not None and bias.dtype != val.dtype):
         raise TypeError(f"activation / bias dtype must match the weight dtype {val.dtype}")
     act, ld_act = _row_major_2d(act)
-    token_major = layout == nat.NMG_ACT_TOKEN_MAJOR
+    token_major = layout != nat.NMG_ACT_K_MAJOR
     tokens = act.shape[0] if token_major else act.shape[1]
     if (act.shape[1] if token_major else act.shape[0]) != K:
         raise ValueError(f"activation shape {tuple(act.shape)} does not match K={K}")
     if out is None:
-        out = torch.empty((tokens, M) if token_major else (M, tokens), dtype=val.dtype, device=dev)
+        out = torch.empty((tokens, M) if layout == nat.NMG_ACT_TOKEN_MAJOR else (M, tokens), dtype=val.dtype, device=dev)
     if tokens == 0:
         return out
     val, idx = val.contiguous(), idx.contiguous()

@@ -123,3 +123,79 @@ class ShardedGroupedNMLinear:
         return out.reshape(*x.shape[:-1], self.M_total)
 
     __call__ = forward
+
+
+class RowShardedNMMatmul:
+    """``C[M, tokens] = W @ X^T`` (the ``torch.mm`` orientation) with ``W`` row-sharded block-cyclically.
+
+    The rows are cut into ``R * P`` panels of ``rows_per_panel`` rows; rank ``r`` owns panels ``p * R + r``.  In this
+    orientation a panel of ``W`` produces a contiguous slab of rows of ``C``, and the ``R`` slabs of one round ``p`` are
+    adjacent in rank order, so every round is one *in-place* all-gather straight into the final buffer: no staging
+    buffer and no re-layout copy.  The gather of round ``p`` overlaps the matmul of round ``p + 1``.
+
+    ``panels``: this rank's panels as ``GroupedNMTensor`` objects, in round order."""
+
+    def __init__(self, panels, M_total, group=None, matmul=None):
+        self.group = group
+        self.world = dist.get_world_size(group) if dist.is_initialized() else 1
+        self.rank = dist.get_rank(group) if dist.is_initialized() else 0
+        self.panels = list(panels)
+        self.M_total = int(M_total)
+        self.matmul = matmul or _default_matmul_rows
+        if not self.panels:
+            raise ValueError("at least one panel is required")
+        rows, K = self.panels[0].nm_strides["dense_shape"]
+        self.rows_per_panel, self.K = int(rows), int(K)
+        if any(tuple(p.nm_strides["dense_shape"]) != (rows, K) for p in self.panels):
+            raise ValueError("all panels of a rank must have the same shape")
+        if self.rows_per_panel * self.world * len(self.panels) != self.M_total:
+            raise ValueError(f"{len(self.panels)} panels of {self.rows_per_panel} rows on {self.world} ranks do not tile M={self.M_total}")
+        s = self.panels[0].nm_strides
+        ShardedGroupedNMLinear._check_agreement(self, (self.M_total, self.K, s["n"], s["m"], s["group_size"], len(self.panels)))
+
+    @staticmethod
+    def panel_rows(M, world, rounds, m):
+        """Rows per panel for a block-cyclic split, or raise when ``M`` is not a multiple of ``world * rounds * m``."""
+        if M % (world * rounds * m) != 0:
+            raise ValueError(f"M={M} is not a multiple of world*rounds*m = {world * rounds * m}")
+        return M // (world * rounds)
+
+    @classmethod
+    def from_full_weight(cls, weight, n, m, g, rounds=4, group=None, matmul=None, sparsify=None):
+        world = dist.get_world_size(group) if dist.is_initialized() else 1
+        rank = dist.get_rank(group) if dist.is_initialized() else 0
+        M = weight.shape[0]
+        rp = cls.panel_rows(M, world, rounds, m)
+        make = sparsify or (lambda w: GroupedNMTensor.from_dense(w, n, m, sparse_dim=0, group_size=g, group_dim=1))
+        panels = [make(weight[(p * world + rank) * rp:(p * world + rank + 1) * rp]) for p in range(rounds)]
+        return cls(panels, M, group, matmul)
+
+    def forward(self, x2d, out=None):
+        """``x2d``: [tokens, K] (replicated).  Returns ``C`` [M, tokens] complete on every rank."""
+        if x2d.dim() != 2 or x2d.shape[1] != self.K:
+            raise ValueError(f"activation must be [tokens, {self.K}]")
+        tokens = x2d.shape[0]
+        rp, R = self.rows_per_panel, self.world
+        if out is None:
+            out = torch.empty(self.M_total, tokens, dtype=x2d.dtype, device=x2d.device)
+        pending = []
+        for p, panel in enumerate(self.panels):
+            q = p * R + self.rank
+            mine = out[q * rp:(q + 1) * rp]
+            self.matmul(panel, x2d, mine)
+            if R > 1:
+                pending.append(dist.all_gather_into_tensor(out[p * R * rp:(p + 1) * R * rp], mine, group=self.group, async_op=True))
+        for work in pending:
+            work.wait()
+        return out
+
+    __call__ = forward
+
+
+def _default_matmul_rows(gnm, x2d, out_rows):
+    from . import _native as nat
+    s = gnm.nm_strides
+    M, K = s["dense_shape"]
+    packed = gnm.packed() if gnm.val.dtype in (torch.float16, torch.bfloat16) else None
+    ops.spmm(gnm.val, gnm.idx, int(M), int(K), s["n"], s["m"], s["group_size"], x2d, packed=packed,
+             layout=nat.NMG_ACT_TOKEN_MAJOR_OUT_ROWS, out=out_rows)

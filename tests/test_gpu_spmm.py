@@ -127,6 +127,24 @@ def test_tensor_core_forward_and_transposed(dtype, n, m, g, M, K, tokens):
     assert ops.read_status() == 0
 
 
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_token_major_input_with_row_major_output(dtype):
+    """C = W X^T written as [M, tokens] (what a row shard needs for an in-place gather), into a slab of a larger buffer."""
+    from sten_b200 import _native as nat, ops
+    M, K, n, m, g, tokens = 256, 520, 2, 8, 16, 200
+    val, idx, x, dense = _problem(M, K, n, m, g, tokens, 61, dtype)
+    full = torch.zeros(3 * M, tokens, dtype=dtype, device=cuda())
+    ops.spmm(val, idx, M, K, n, m, g, x, layout=nat.NMG_ACT_TOKEN_MAJOR_OUT_ROWS, out=full[M:2 * M])
+    ref64 = np_of(dense).astype(np.float64) @ np_of(x).astype(np.float64).T
+    assert rel_fro(np_of(full[M:2 * M]), ref64) <= (TOL_F32 if dtype == torch.float32 else TOL_HALF)
+    assert float(full[:M].abs().max()) == 0 and float(full[2 * M:].abs().max()) == 0
+    # aligned case takes the vectorised stores: 256 tokens, ld multiple of 8
+    x2 = seeded_normal((256, K), 62).to(dtype).to(cuda())
+    c2 = ops.spmm(val, idx, M, K, n, m, g, x2, layout=nat.NMG_ACT_TOKEN_MAJOR_OUT_ROWS)
+    y2 = ops.spmm(val, idx, M, K, n, m, g, x2)
+    assert torch.equal(c2, y2.t())
+
+
 def test_tensor_core_is_the_default_for_half_precision_and_rejects_fp32():
     from sten_b200 import _native as nat, ops
     M, K, n, m, g, tokens = 256, 512, 2, 4, 16, 256

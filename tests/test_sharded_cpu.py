@@ -10,7 +10,7 @@ import torch
 import torch.distributed as dist
 import torch.multiprocessing as mp
 
-from sten_b200.sharded import ShardedGroupedNMLinear, row_shard_bounds
+from sten_b200.sharded import RowShardedNMMatmul, ShardedGroupedNMLinear, row_shard_bounds
 
 
 class FakeGNM:
@@ -52,6 +52,18 @@ def _worker_ok(rank, world, port, result_q):
         ok = ok and torch.allclose(y, x @ w.t() + b, atol=1e-5) and y.shape == (3, 5, M)
         local = layer.forward_local(x.reshape(-1, 24))
         ok = ok and local.shape[1] == layer.bounds[rank + 1] - layer.bounds[rank]
+    # torch.mm orientation, block-cyclic panels, in-place gathers
+    w = torch.randn(32, 24)
+    x = torch.randn(7, 24)
+    mm = RowShardedNMMatmul.from_full_weight(w, 2, 4, 2, rounds=2, sparsify=lambda rows: FakeGNM(rows, 2, 4, 2),
+                                             matmul=lambda gnm, x2d, out: out.copy_(gnm.dense @ x2d.t()))
+    c = mm(x)
+    ok = ok and c.shape == (32, 7) and torch.allclose(c, w @ x.t(), atol=1e-5)
+    try:
+        RowShardedNMMatmul.from_full_weight(torch.randn(20, 24), 2, 4, 2, rounds=2, sparsify=lambda r: FakeGNM(r, 2, 4, 2))
+        ok = False
+    except ValueError:
+        pass
     result_q.put((rank, bool(ok)))
     dist.destroy_process_group()
 
