@@ -11,6 +11,9 @@ output row slabs are combined with in-place NCCL all-gathers (one per row panel,
 matmul; C = W X^T is kept as [M, tokens] so that slabs are contiguous); with N = 1 there is no collective.
 Total work is fixed, so scaling is "strong".  metric = useful (non-zero) GFLOP/s = 2*M*K*tokens*n/m / step time.
 
+Workload "encoder": BERT-large-shaped fp16 encoder with all encoder linears at nmg 2:4 through SparsityBuilder, batch
+32 x seq 384 split over the ranks; tokens/s eager, as a CUDA graph, and for the dense fp16 model.
+
 Workload "sweep": the 4096 x 4096 density sweep in fp32 (n:m in {1:4, 2:4, 1:8, 2:8, 1:16}, g = 16, 4096 tokens);
 one step is the five matmuls; with N > 1 every rank runs it on its own token shard (weak scaling, no collective).
 
@@ -222,20 +225,25 @@ def sweep_table(torch, ops, nat, dev, peaks, fma_peak):
         torch.cuda.synchronize()
         return a.elapsed_time(b) / reps
 
-    for dtype, name in ((torch.float32, "f32"), (torch.bfloat16, "bf16")):
+    variants = ((torch.float32, "f32", nat.NMG_ALGO_SIMT, "simt fp32 FMA"),
+                (torch.float32, "f32", nat.NMG_ALGO_TENSOR, "tensor cores, 6 bf16 split products"),
+                (torch.bfloat16, "bf16", nat.NMG_ALGO_TENSOR, "tensor cores"))
+    for dtype, name, algo, how in variants:
         xd = x.to(dtype)
         for (n, m) in SWEEP:
             val, idx = ops.sparsify(w.to(dtype).unsqueeze(0), n, m, G)
             dense = ops.densify(val, idx, 1, SW_M, SW_K, n, m, G)[0]
-            packed = ops.pack(val, idx, SW_M, SW_K, n, m, G) if dtype != torch.float32 else None
+            packed = ops.pack(val, idx, SW_M, SW_K, n, m, G) if algo == nat.NMG_ALGO_TENSOR else None
             o = torch.empty(SW_TOK, SW_M, device=dev, dtype=dtype)
-            t_nmg = timed(lambda: ops.spmm(val, idx, SW_M, SW_K, n, m, G, xd, out=o, packed=packed))
+            t_nmg = timed(lambda: ops.spmm(val, idx, SW_M, SW_K, n, m, G, xd, out=o, packed=packed, algo=algo))
             t_dense = timed(lambda: torch.mm(xd, dense.t()))
             useful = useful_flops(SW_M, SW_K, SW_TOK, n, m) / t_nmg / 1e9  # TFLOP/s
-            peak = fma_peak if dtype == torch.float32 else peaks["bf16_tflops"]
-            rows.append({"nm": f"{n}:{m}", "dtype": name, "ms": t_nmg, "useful_tflops": useful,
-                         "bound": "fma" if dtype == torch.float32 else "tensor", "frac_of_peak_useful": useful / peak,
-                         "frac_of_peak_executed": (useful * m / n / peak) if dtype != torch.float32 else useful / peak,
+            tensor = algo == nat.NMG_ALGO_TENSOR
+            peak = peaks["bf16_tflops"] if tensor else fma_peak
+            executed = useful * m / n * (6 if (tensor and dtype == torch.float32) else 1) if tensor else useful
+            rows.append({"nm": f"{n}:{m}", "dtype": name, "kernel": how, "ms": t_nmg, "useful_tflops": useful,
+                         "bound": "tensor" if tensor else "fma", "frac_of_peak_useful": useful / peak,
+                         "frac_of_peak_executed": executed / peak,
                          "cublas_dense_ms": t_dense, "speedup_vs_cublas": t_dense / t_nmg})
             del val, idx, dense, packed, o
     return rows
@@ -398,16 +406,104 @@ def run_ours(args):
     return 0
 
 
+def run_encoder(args):
+    """BERT-large-shaped encoder (24 layers, hidden 1024, FFN 4096, 16 heads, random init, fp16) with every encoder
+    Linear weight at nmg 2:4 (g = 16) through SparsityBuilder; attention stays dense.  Inference on 32 x 384 random token
+    ids, the batch split evenly over the ranks (no collective).  Reports tokens/s eager and as a replayed CUDA graph."""
+    import torch
+    import torch.distributed as dist
+    import sten_b200 as sten
+    from transformers import BertConfig, BertModel
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    sten.set_dispatch_failure("raise")
+    BATCH, SEQ = 32, 384
+    cfg = BertConfig(hidden_size=1024, num_hidden_layers=24, num_attention_heads=16, intermediate_size=4096,
+                     vocab_size=30522, max_position_embeddings=512)
+    torch.manual_seed(0)
+    model = BertModel(cfg, add_pooling_layer=False).half().to(dev).eval()
+    names = [n + ".weight" for n, mod in model.named_modules() if isinstance(mod, torch.nn.Linear) and "encoder.layer" in n]
+    sb = sten.SparsityBuilder()
+    for w in names:
+        sb.set_weight(name=w, initial_sparsifier=sten.GroupedNMSparsifier(n=2, m=4, g=G), out_format=sten.GroupedNMTensor)
+    dense_model = model
+    import copy
+    sparse_model = sb.sparsify_model_inplace(copy.deepcopy(model))
+    per_rank = BATCH // world
+    ids_all = torch.randint(0, 30522, (BATCH, SEQ), generator=torch.Generator().manual_seed(1))
+    ids = ids_all[rank * per_rank:(rank + 1) * per_rank].to(dev)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def fwd(m):
+        with torch.no_grad():
+            return m(input_ids=ids).last_hidden_state
+
+    for _ in range(max(args.warmup, 3)):
+        out = fwd(sparse_model)
+    ms_eager = timed_loop(lambda: fwd(sparse_model), args.steps, barrier, torch, dist, world, dev)
+    for _ in range(3):
+        fwd(dense_model)
+    ms_dense = timed_loop(lambda: fwd(dense_model), args.steps, barrier, torch, dist, world, dev)
+    # CUDA graph of the sparse forward: removes the host-side dispatch cost of the 144 sparse linears
+    ms_graph = None
+    try:
+        g = torch.cuda.CUDAGraph()
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            fwd(sparse_model)
+        torch.cuda.current_stream().wait_stream(side)
+        with torch.cuda.graph(g):
+            static_out = fwd(sparse_model)
+        ms_graph = timed_loop(g.replay, args.steps, barrier, torch, dist, world, dev)
+    except Exception as e:  # graph capture is an optimisation of the host path, not part of the result's validity
+        ms_graph = None
+        graph_err = f"{type(e).__name__}: {e}"[:200]
+    toks = BATCH * SEQ
+    if rank == 0:
+        print(json.dumps({
+            "metric": "sparse_encoder_tokens_per_s", "value": toks / (ms_eager * 1e-3), "unit": "tokens/s", "n_gpus": world,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_eager, "higher_is_better": True, "scaling": "strong",
+            "vs_baseline": None, "dtype": "f16", "data": "synthetic",
+            "config": {"workload": "BERT-large-shaped encoder, 24 layers, all encoder linears nmg 2:4 g=16, batch 32 x seq 384",
+                       "parallelism": f"batch split over {world} rank(s), no collective"},
+            "cuda_graph_tokens_per_s": (toks / (ms_graph * 1e-3)) if ms_graph else None,
+            "dense_fp16_tokens_per_s": toks / (ms_dense * 1e-3), "sparse_linears_per_forward": len(names),
+            "output_finite": bool(torch.isfinite(out.float()).all()),
+        }))
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+    return 0
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="sharded", choices=["sharded", "sweep"])
+    ap.add_argument("--workload", default="sharded", choices=["sharded", "sweep", "encoder"])
     ap.add_argument("--rounds", type=int, default=4, help="gather rounds (row panels per rank) when N > 1")
     ap.add_argument("--no-sweep", action="store_true", help="skip the per-pattern 4096^2 table")
     args = ap.parse_args()
+    if args.workload == "encoder":
+        if args.impl == "reference":
+            if int(os.environ.get("RANK", "0")) == 0:
+                print(json.dumps({"impl": "reference", "unavailable": "the reference cannot run this encoder on its CPU path in bounded time; "
+                                  "its per-layer matmul is what the default workload's reference arm times"}))
+            return 0
+        return run_encoder(args)
     if args.impl == "reference":
         return run_reference(args)
     args.warmup = max(args.warmup, 3)

@@ -97,8 +97,10 @@ int nmg_pack(const void *val, const int16_t *idx, int64_t M, int64_t K, int n, i
  * needs it).  have_packed in the workspace query says which of the two the caller will do.
  * workspace: device scratch of at least nmg_spmm_workspace_bytes(...) bytes, 256-byte aligned, owned by the
  * caller for the duration of the call (may be NULL when the query returns 0).
- * algo: NMG_ALGO_AUTO uses the tensor-core kernel for fp16 / bf16 weights with m in {4, 8, 16} and token-major
- * activations whose rows are 16-byte aligned, the SIMT kernels otherwise. */
+ * algo: NMG_ALGO_AUTO uses the tensor-core kernel for m in {4, 8, 16}, n <= 2, token-major activations (16-bit
+ * rows must be 16-byte aligned) and at least 64 tokens and 64 rows; the SIMT kernels otherwise.  fp32 operands go through
+ * the tensor cores as exact three-way bf16 splits with promoted fp32 accumulation (relative error ~3.5e-6, independent
+ * of K); NMG_ALGO_SIMT forces plain fp32 FMA arithmetic. */
 size_t nmg_spmm_workspace_bytes(int64_t M, int64_t K, int64_t tokens, int n, int m, int g, int dtype,
                                 int layout, int algo, int have_packed);
 int nmg_spmm(const void *val, const int16_t *idx, const void *packed, int64_t M, int64_t K, int n, int m, int g,

@@ -15,6 +15,8 @@ int launch_widen_to_f32(const void *src, int dtype, int64_t rows, int64_t cols, 
 
 // Column-order ("natural") copy of a weight: for every row-block mb and column k of the padded width Kp,
 // pat[mb][k] = pattern of that column, nval[mb][k][s] = its n kept values.
+struct NaturalLayout { size_t pat_bytes, val_bytes, plane_bytes, total; };
+NaturalLayout natural_layout(const Geo &geo, int dtype);
 int64_t natural_width(const Geo &geo);
 size_t natural_bytes(const Geo &geo, int dtype, size_t *pat_bytes_out);
 int launch_build_natural(const Geo &geo, int dtype, const void *val, const int16_t *idx, uint16_t *pat, void *nval,
@@ -30,11 +32,13 @@ size_t simt_bwd_workspace_bytes(const Geo &geo, int64_t tokens, int dtype);
 int simt_bwd(const Geo &geo, int dtype, const uint16_t *pat, const void *nval, const void *dy, int64_t ld_dy,
              int64_t tokens, void *dx, int64_t ld_dx, void *ws, size_t ws_bytes, cudaStream_t st);
 
-// Tensor-core kernels (nmg_spmm_tc.cu).  act: [tokens][ld_act] with the reduction axis contiguous.
+// Tensor-core kernels (nmg_spmm_tc.cu).  act: [tokens][ld_act] with the reduction axis contiguous.  fp32 operands are
+// multiplied as sums of bf16 pieces and need `ws` (tc_split_workspace_bytes) for the split activation.
 bool tc_supported(const Geo &geo, int dtype);
+size_t tc_split_workspace_bytes(const Geo &geo, int dtype, bool transposed, int64_t tokens);
 int tc_matmul(const Geo &geo, int dtype, bool transposed, const uint16_t *pat, const void *nval, const void *act,
               int64_t ld_act, int64_t tokens, const void *bias, void *out, int64_t ld_out, int out_token_major,
-              cudaStream_t st);
+              void *ws, size_t ws_bytes, cudaStream_t st);
 
 // ---- specialised forward kernel: parameters, shared-memory plan, per-(n, m) launchers
 struct FwdParams {

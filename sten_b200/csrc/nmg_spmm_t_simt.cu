@@ -15,6 +15,7 @@ namespace nmg {
 // ------------------------------------------------------------------------------------------ column-ordered copy
 struct NaturalParams {
     const void *val; const int16_t *idx; uint16_t *pat; void *nval;
+    __nv_bfloat16 *plane[3];  // fp32 weights only, else NULL
     int64_t nb, nc, Kp;
     int n, g, cc;
 };
@@ -31,7 +32,19 @@ __global__ void build_natural_kernel(const NaturalParams prm) {
         if (c < 0 || c >= prm.cc) continue;  // malformed index: leave the column empty
         const int64_t k = kc * prm.cc + c;
         prm.pat[mb * prm.Kp + k] = (uint16_t)(slot / prm.g);
-        for (int s = 0; s < prm.n; s++) nval[(mb * prm.Kp + k) * prm.n + s] = val[e * prm.n + s];
+        for (int s = 0; s < prm.n; s++) {
+            const T v = val[e * prm.n + s];
+            const int64_t o = (mb * prm.Kp + k) * prm.n + s;
+            nval[o] = v;
+            if (prm.plane[0]) {  // exact three-way split of an fp32 value into bf16 pieces
+                const float f = DT<T>::to_f32(v);
+                const __nv_bfloat16 hi = __float2bfloat16_rn(f);
+                const float r1 = f - __bfloat162float(hi);
+                const __nv_bfloat16 mid = __float2bfloat16_rn(r1);
+                const __nv_bfloat16 lo = __float2bfloat16_rn(r1 - __bfloat162float(mid));
+                prm.plane[0][o] = hi; prm.plane[1][o] = mid; prm.plane[2][o] = lo;
+            }
+        }
     }
 }
 
@@ -39,17 +52,31 @@ __global__ void build_natural_kernel(const NaturalParams prm) {
 // row segment a CTA stages is full-size and 16-byte aligned.
 int64_t natural_width(const Geo &geo) { return round_up(geo.nc * geo.cc, 128); }
 
+// Sections of the copy: pattern ids, values in the weight's dtype, and -- for fp32 weights -- three bf16 planes
+// holding the exact split v = hi + mid + lo that the tensor-core kernel multiplies term by term.
+NaturalLayout natural_layout(const Geo &geo, int dtype) {
+    const size_t entries = (size_t)geo.nb * (size_t)natural_width(geo);
+    NaturalLayout l;
+    l.pat_bytes = (entries * 2 + 255) & ~(size_t)255;
+    l.val_bytes = (entries * geo.n * dtype_size(dtype) + 255) & ~(size_t)255;
+    l.plane_bytes = dtype == NMG_F32 ? ((entries * geo.n * 2 + 255) & ~(size_t)255) : 0;
+    l.total = l.pat_bytes + l.val_bytes + 3 * l.plane_bytes;
+    return l;
+}
+
 size_t natural_bytes(const Geo &geo, int dtype, size_t *pat_bytes_out) {
-    const size_t Kp = (size_t)natural_width(geo);
-    const size_t pat = ((size_t)geo.nb * Kp * 2 + 255) & ~(size_t)255;
-    const size_t vals = ((size_t)geo.nb * Kp * geo.n * dtype_size(dtype) + 255) & ~(size_t)255;
-    if (pat_bytes_out) *pat_bytes_out = pat;
-    return pat + vals;
+    const NaturalLayout l = natural_layout(geo, dtype);
+    if (pat_bytes_out) *pat_bytes_out = l.pat_bytes;
+    return l.total;
 }
 
 int launch_build_natural(const Geo &geo, int dtype, const void *val, const int16_t *idx, uint16_t *pat, void *nval,
                          cudaStream_t st) {
-    NaturalParams p{val, idx, pat, nval, geo.nb, geo.nc, natural_width(geo), geo.n, geo.g, geo.cc};
+    const NaturalLayout lay = natural_layout(geo, dtype);
+    NaturalParams p{val, idx, pat, nval, {nullptr, nullptr, nullptr}, geo.nb, geo.nc, natural_width(geo), geo.n, geo.g, geo.cc};
+    if (lay.plane_bytes)
+        for (int c = 0; c < 3; c++)
+            p.plane[c] = reinterpret_cast<__nv_bfloat16 *>(static_cast<char *>(nval) + lay.val_bytes + c * lay.plane_bytes);
     const int64_t total = geo.nb * geo.nc * geo.cc;
     int64_t blocks = (total + 255) / 256;
     if (blocks > 148 * 64) blocks = 148 * 64;

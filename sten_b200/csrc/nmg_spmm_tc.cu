@@ -23,15 +23,17 @@ constexpr int TC_BM = 128;    // output features per CTA (MMA M)
 constexpr int TC_BN = 256;    // tokens per CTA (MMA N)
 constexpr int TC_BK = 64;     // reduction elements per stage: one 128-byte swizzle span of 16-bit data
 constexpr int TC_STAGES = 4;
-constexpr int TC_GROUPS = 3;  // expansion groups of 4 warps
-constexpr int TC_THREADS = 32 * (2 + 4 * TC_GROUPS);
+constexpr int TC_THREADS = 32 * 14;  // TMA warp, MMA warp, 12 worker warps
+// Worker warps: three expansion groups of 4 warps; group 0 also drains the accumulator (promotion in fp32 mode,
+// epilogue in every mode).
+constexpr int TC_CHUNK_KB = 8;       // fp32 mode: k-blocks (of 64) accumulated in the tensor core before promotion
 constexpr int TC_A_BYTES = TC_BM * TC_BK * 2;  // 16 KB
 constexpr int TC_B_BYTES = TC_BN * TC_BK * 2;  // 32 KB
-constexpr int TC_TMEM_COLS = 256;
+constexpr int TC_ACC_COLS = 256;    // one fp32 accumulator tile: 128 lanes x 256 columns
 
 struct TcParams {
     const uint16_t *pat;  // [nb][Kpn]
-    const void *nval;     // [nb][Kpn][n]
+    const void *nval[3];  // [nb][Kpn][n] 16-bit values; fp32 weights: the hi / mid / lo bf16 planes
     const void *bias;     // [out_feats] or NULL
     void *out;
     int64_t out_feats;    // M (forward) or K (transposed)
@@ -88,6 +90,18 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
         : "memory");
     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
+__device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+        "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
+        "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};"
+        ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]),
+          "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]), "r"(r[16]), "r"(r[17]),
+          "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]), "r"(r[24]), "r"(r[25]), "r"(r[26]),
+          "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
+        : "memory");
+    asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+}
 __device__ __forceinline__ void fence_proxy_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 __device__ __forceinline__ void mbar_arrive(uint64_t *bar) {
     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
@@ -110,6 +124,7 @@ template <typename T> __device__ __forceinline__ uint32_t make_idesc() {
 template <typename T> __device__ __forceinline__ uint16_t bits16(T v);
 template <> __device__ __forceinline__ uint16_t bits16<__half>(__half v) { return __half_as_ushort(v); }
 template <> __device__ __forceinline__ uint16_t bits16<__nv_bfloat16>(__nv_bfloat16 v) { return __bfloat16_as_ushort(v); }
+template <> __device__ __forceinline__ uint16_t bits16<float>(float) { return 0; }  // never used: fp32 outputs are stored as words
 
 // ---- weight-tile expansion ------------------------------------------------------------------------------
 // A column of a row-block is n values plus a pattern id; its dense form (m halfs, n of them non-zero) is a byte
@@ -145,9 +160,10 @@ template <int N_, int M_> struct FwdRegs {
 };
 
 template <int N_, int M_>
-__device__ __forceinline__ void fetch_forward(FwdRegs<N_, M_> &t, const TcParams &prm, int64_t feat0, int64_t kb, int gwarp, int lane) {
+__device__ __forceinline__ void fetch_forward(FwdRegs<N_, M_> &t, const TcParams &prm, const void *plane, int64_t feat0, int64_t kb,
+                                              int gwarp, int lane) {
     constexpr int RBW = FwdRegs<N_, M_>::RBW;
-    const uint32_t *nval = static_cast<const uint32_t *>(prm.nval);
+    const uint32_t *nval = static_cast<const uint32_t *>(plane);
 #pragma unroll
     for (int i = 0; i < RBW; i++) {
         const int64_t mb = feat0 / M_ + gwarp + 4 * i;
@@ -199,10 +215,11 @@ template <int N_, int M_> struct TrRegs {
 };
 
 template <int N_, int M_>
-__device__ __forceinline__ void fetch_transposed(TrRegs<N_, M_> &t, const TcParams &prm, int64_t feat0, int64_t kb, int row) {
+__device__ __forceinline__ void fetch_transposed(TrRegs<N_, M_> &t, const TcParams &prm, const void *plane, int64_t feat0, int64_t kb,
+                                                 int row) {
     constexpr int E = TrRegs<N_, M_>::E;
     const int64_t kg = feat0 + row;
-    const uint16_t *nval = static_cast<const uint16_t *>(prm.nval);
+    const uint16_t *nval = static_cast<const uint16_t *>(plane);
 #pragma unroll
     for (int j = 0; j < E; j++) {
         const int64_t mb = kb * E + j;
@@ -236,33 +253,60 @@ __device__ __forceinline__ void write_transposed(const TrRegs<N_, M_> &t, char *
         *reinterpret_cast<uint4 *>(rowp + (((c ^ row) & 7) << 4)) = make_uint4(w[4 * c], w[4 * c + 1], w[4 * c + 2], w[4 * c + 3]);
 }
 
+// fp32 operands run on the bf16 tensor cores as exact three-way splits x = xh + xm + xl, w = wh + wm + wl.  The
+// product keeps the six terms whose weight is >= 2^-16 of the leading one (wh xh, wm xh, wh xm, wm xm, wl xh, wh xl);
+// the dropped terms are below 2^-24 relative, the size of an fp32 rounding error.  Each term is one more pass
+// over the reduction axis with another pair of planes, accumulated in the same fp32 TMEM tile.
+//
+// The tensor core's fp32 accumulator truncates instead of rounding, which biases long sums: measured relative error
+// grows linearly with the reduction length (3.5e-6 at K = 512, 2.6e-5 at K = 4096).  fp32 mode therefore keeps a
+// second accumulator tile in TMEM: every TC_CHUNK_KB k-blocks the first expansion group adds the tensor core's
+// partial tile into it with round-to-nearest FADDs (tcgen05.ld / tcgen05.st), and the MMAs restart from zero.  The
+// error then no longer depends on K.
+template <typename T> struct TcMode { using elem = T; static constexpr int TERMS = 1; static constexpr int GROUPS = 3; };
+template <> struct TcMode<float> { using elem = __nv_bfloat16; static constexpr int TERMS = 6; static constexpr int GROUPS = 3; };
+__device__ __constant__ int kSplitW[6] = {0, 1, 0, 1, 2, 0};
+__device__ __constant__ int kSplitX[6] = {0, 0, 1, 1, 0, 2};
+
 // ---- the kernel -------------------------------------------------------------------------------------------
 template <int N_, int M_, typename T, bool TRANSPOSED>
 __global__ void __launch_bounds__(TC_THREADS, 1)
-spmm_tc_kernel(const TcParams prm, const __grid_constant__ CUtensorMap tmap) {
-    static_assert((3 * TC_STAGES + 1) * 8 <= 112, "barriers overlap the TMEM slot");
+spmm_tc_kernel(const TcParams prm, const __grid_constant__ CUtensorMap tmap0, const __grid_constant__ CUtensorMap tmap1,
+               const __grid_constant__ CUtensorMap tmap2) {
+    constexpr int TERMS = TcMode<T>::TERMS;
+    using E = typename TcMode<T>::elem;  // element type the tensor cores see
+    static_assert((3 * TC_STAGES + 2) * 8 <= 120, "barriers overlap the TMEM slot");
     static_assert(TC_BM % (4 * M_) == 0 && TC_BK % M_ == 0 && M_ % 4 == 0 && N_ <= 2, "tile must hold whole row-blocks; pattern rows are packed in 32 bits");
     constexpr Order<N_, M_> ORD{};
     constexpr int C = Order<N_, M_>::C;
+
+    constexpr bool SPLIT = TERMS > 1;
+    constexpr int GROUPS = TcMode<T>::GROUPS;
+    constexpr uint32_t TMEM_COLS = SPLIT ? 2 * TC_ACC_COLS : TC_ACC_COLS;
 
     extern __shared__ char smem_raw[];
     char *smem = reinterpret_cast<char *>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     char *a_stages = smem;
     char *b_stages = smem + TC_STAGES * TC_A_BYTES;
-    uint64_t *full_a = reinterpret_cast<uint64_t *>(smem + TC_STAGES * (TC_A_BYTES + TC_B_BYTES));
+    char *misc = smem + TC_STAGES * (TC_A_BYTES + TC_B_BYTES);  // 1024-byte aligned: barriers first
+    uint64_t *full_a = reinterpret_cast<uint64_t *>(misc);
     uint64_t *full_b = full_a + TC_STAGES;
     uint64_t *empty = full_b + TC_STAGES;
-    uint64_t *tmem_full = empty + TC_STAGES;
-    char *misc = smem + TC_STAGES * (TC_A_BYTES + TC_B_BYTES);        // 1024-byte aligned: barriers first
-    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(misc + 112);
-    uint16_t *sel = reinterpret_cast<uint16_t *>(misc + 128);          // [C][M_/2] PRMT selectors, 16-byte aligned
+    uint64_t *chunk_done = empty + TC_STAGES;  // MMA -> promotion / epilogue: the accumulator tile is complete
+    uint64_t *promoted = chunk_done + 1;       // promotion -> MMA: the accumulator tile may be overwritten
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(misc + 120);
+    uint16_t *sel = reinterpret_cast<uint16_t *>(misc + 128);  // [C][M_/2] PRMT selectors, 16-byte aligned
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     int tile_f, tile_t;
     tile_of_cta((int)blockIdx.x, prm.tiles_f, prm.tiles_t, tile_f, tile_t);
     const int64_t tok0 = (int64_t)tile_t * TC_BN;
     const int64_t feat0 = (int64_t)tile_f * TC_BM;
-    const int64_t nkb = (prm.red + TC_BK - 1) / TC_BK;
+    // 32-bit loop arithmetic throughout: the single MMA-issuing thread must stay ahead of the tensor core, and a
+    // 64-bit division per iteration on that thread is enough to make issue the bottleneck.
+    const int nkb = (int)((prm.red + TC_BK - 1) / TC_BK) * TERMS;   // iterations: k-blocks x split terms (term fastest)
+    const int chunk_it = SPLIT ? TC_CHUNK_KB * TERMS : nkb;          // iterations per accumulation chunk
+    const int nchunks = (nkb + chunk_it - 1) / chunk_it;
 
     if (tid == 0) {
         for (int s = 0; s < TC_STAGES; s++) {
@@ -270,7 +314,8 @@ spmm_tc_kernel(const TcParams prm, const __grid_constant__ CUtensorMap tmap) {
             mbar_init(&full_b[s], 1);
             mbar_init(&empty[s], 1);
         }
-        mbar_init(tmem_full, 1);
+        mbar_init(chunk_done, 1);
+        mbar_init(promoted, 128);
         mbar_fence_init();
     }
     for (int e = tid; e < C * (M_ / 2); e += TC_THREADS) {
@@ -285,42 +330,142 @@ spmm_tc_kernel(const TcParams prm, const __grid_constant__ CUtensorMap tmap) {
         }
         sel[e] = (uint16_t)code;
     }
-    if (warp == 1) tmem_alloc(tmem_slot, TC_TMEM_COLS);
+    if (warp == 1) tmem_alloc(tmem_slot, TMEM_COLS);
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
 
+    // Promotion + epilogue, run by four warps that together cover the 128 TMEM lanes.  For every finished chunk the
+    // accumulator tile is added to the running tile (columns 256..511) with round-to-nearest adds; the last chunk is
+    // added, biased, converted and stored to global memory instead.  16-bit mode has a single chunk.
+    // Bias, convert and store one 32-column slice (32 tokens) of this thread's feature row.
+    auto store_slice = [&](const uint32_t (&r)[32], int sl, int64_t feat, float b) {
+        T *out = static_cast<T *>(prm.out);
+        const int64_t tokc = tok0 + sl * 32;
+        const bool vec = !prm.out_token_major && tokc + 32 <= prm.ntok && (prm.ld_out % (16 / (int)sizeof(T))) == 0 &&
+                         (reinterpret_cast<uintptr_t>(out) & 15) == 0;
+        if (vec) {  // 32 consecutive tokens of this feature: 16-byte stores
+            uint4 *dst = reinterpret_cast<uint4 *>(out + feat * prm.ld_out + tokc);
+            if constexpr (sizeof(T) == 4) {
+#pragma unroll
+                for (int v = 0; v < 8; v++)
+                    dst[v] = make_uint4(__float_as_uint(__uint_as_float(r[4 * v]) + b), __float_as_uint(__uint_as_float(r[4 * v + 1]) + b),
+                                        __float_as_uint(__uint_as_float(r[4 * v + 2]) + b), __float_as_uint(__uint_as_float(r[4 * v + 3]) + b));
+            } else {
+#pragma unroll
+                for (int v = 0; v < 4; v++) {
+                    uint32_t w[4];
+#pragma unroll
+                    for (int h = 0; h < 4; h++) {
+                        const T lo = DT<T>::from_f32(__uint_as_float(r[8 * v + 2 * h]) + b);
+                        const T hi = DT<T>::from_f32(__uint_as_float(r[8 * v + 2 * h + 1]) + b);
+                        w[h] = (uint32_t)bits16<T>(lo) | ((uint32_t)bits16<T>(hi) << 16);
+                    }
+                    dst[v] = make_uint4(w[0], w[1], w[2], w[3]);
+                }
+            }
+        } else {
+#pragma unroll
+            for (int j = 0; j < 32; j++) {
+                const int64_t tok = tokc + j;
+                if (tok < prm.ntok) {
+                    const T o = DT<T>::from_f32(__uint_as_float(r[j]) + b);
+                    if (prm.out_token_major) out[tok * prm.ld_out + feat] = o;
+                    else out[feat * prm.ld_out + tok] = o;
+                }
+            }
+        }
+    };
+
+    // 16-bit mode: one accumulation chunk, so the four draining warps only run the epilogue.
+    auto epilogue_once = [&]() {
+        if (!mbar_wait_bounded(chunk_done, 0, prm.status, 15)) return;
+        tc_fence_after();
+        const int q = warp & 3;  // TMEM lane quarter this warp may read
+        const int64_t feat = feat0 + q * 32 + lane;
+        const bool feat_ok = feat < prm.out_feats;
+        const float b = (prm.bias && feat_ok) ? DT<T>::to_f32(static_cast<const T *>(prm.bias)[feat]) : 0.f;
+        for (int sl = 0; sl < TC_BN / 32; sl++) {
+            uint32_t r[32];
+            tmem_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(sl * 32), r);
+            if (tok0 + sl * 32 >= prm.ntok) continue;  // warp-uniform
+            if (feat_ok) store_slice(r, sl, feat, b);
+        }
+        tc_fence_before();
+    };
+
+    // fp32 mode: for every finished chunk the accumulator tile is added to the running tile (columns 256..511) with
+    // round-to-nearest adds; the last chunk is added and stored to global memory instead.
+    auto drain_chunk = [&](int c) -> bool {
+        const int q = warp & 3;
+        const int64_t feat = feat0 + q * 32 + lane;
+        const bool feat_ok = feat < prm.out_feats;
+        const float b = (prm.bias && feat_ok) ? DT<T>::to_f32(static_cast<const T *>(prm.bias)[feat]) : 0.f;
+        const uint32_t lane_base = tmem_base + ((uint32_t)(q * 32) << 16);
+        if (!mbar_wait_bounded(chunk_done, (uint32_t)(c & 1), prm.status, 15)) return false;
+        tc_fence_after();
+        const bool last = c == nchunks - 1;
+        for (int sl = 0; sl < TC_BN / 32; sl++) {
+            uint32_t r[32];
+            tmem_ld32(lane_base + (uint32_t)(sl * 32), r);
+            if (c > 0) {
+                uint32_t run[32];
+                tmem_ld32(lane_base + (uint32_t)(TC_ACC_COLS + sl * 32), run);
+#pragma unroll
+                for (int j = 0; j < 32; j++) r[j] = __float_as_uint(__fadd_rn(__uint_as_float(run[j]), __uint_as_float(r[j])));
+            }
+            if (!last) {
+                tmem_st32(lane_base + (uint32_t)(TC_ACC_COLS + sl * 32), r);
+                continue;
+            }
+            if (tok0 + sl * 32 < prm.ntok && feat_ok) store_slice(r, sl, feat, b);
+        }
+        tc_fence_before();
+        if (!last) mbar_arrive(promoted);
+        return true;
+    };
+
     if (warp == 0) {
         // ------------------------------------------------------------------ TMA producer (one lane)
         if (lane == 0) {
-            for (int64_t kb = 0; kb < nkb; kb++) {
-                const int s = (int)(kb % TC_STAGES);
+            for (int kb = 0; kb < nkb; kb++) {
+                const int s = kb % TC_STAGES;
                 const uint32_t ph = (uint32_t)((kb / TC_STAGES) & 1);
                 if (!mbar_wait_bounded(&empty[s], ph ^ 1, prm.status, 11)) break;
                 mbar_expect_tx(&full_b[s], TC_B_BYTES);
-                tma_load_2d(b_stages + s * TC_B_BYTES, &tmap, (int)(kb * TC_BK), (int)tok0, &full_b[s]);
+                const int xc = TERMS == 1 ? 0 : kSplitX[kb % TERMS];
+                const CUtensorMap *tm = xc == 0 ? &tmap0 : (xc == 1 ? &tmap1 : &tmap2);
+                tma_load_2d(b_stages + s * TC_B_BYTES, tm, (kb / TERMS) * TC_BK, (int)tok0, &full_b[s]);
             }
         }
     } else if (warp == 1) {
         // ------------------------------------------------------------------ MMA issuer (one lane)
         if (lane == 0) {
-            const uint32_t idesc = make_idesc<T>();
+            const uint32_t idesc = make_idesc<E>();
             bool ok = true;
-            for (int64_t kb = 0; kb < nkb && ok; kb++) {
-                const int s = (int)(kb % TC_STAGES);
+            int chunk = 0, in_chunk = 0;  // position inside the accumulation chunk, kept without divisions
+            for (int kb = 0; kb < nkb && ok; kb++) {
+                const int s = kb % TC_STAGES;
                 const uint32_t ph = (uint32_t)((kb / TC_STAGES) & 1);
-                ok = mbar_wait_bounded(&full_a[s], ph, prm.status, 12) && mbar_wait_bounded(&full_b[s], ph, prm.status, 13);
+                const bool first = in_chunk == 0;
+                if (first && chunk > 0) ok = mbar_wait_bounded(promoted, (uint32_t)((chunk - 1) & 1), prm.status, 16);
+                ok = ok && mbar_wait_bounded(&full_a[s], ph, prm.status, 12) && mbar_wait_bounded(&full_b[s], ph, prm.status, 13);
                 if (!ok) break;
                 tc_fence_after();
                 const uint64_t adesc = make_sw128_desc(smem_u32(a_stages + s * TC_A_BYTES));
                 const uint64_t bdesc = make_sw128_desc(smem_u32(b_stages + s * TC_B_BYTES));
 #pragma unroll
                 for (int k = 0; k < TC_BK / 16; k++)  // 16 elements = 32 bytes = 2 descriptor units per step
-                    tc_mma_f16(tmem_base, adesc + 2 * k, bdesc + 2 * k, idesc, (kb | k) != 0 ? 1u : 0u);
+                    tc_mma_f16(tmem_base, adesc + 2 * k, bdesc + 2 * k, idesc, (first && k == 0) ? 0u : 1u);
                 tc_commit(&empty[s]);  // arrives when the MMAs above have read the stage
+                if (++in_chunk == chunk_it || kb + 1 == nkb) {
+                    tc_commit(chunk_done);
+                    in_chunk = 0;
+                    chunk++;
+                }
             }
-            tc_commit(tmem_full);      // arrives when every MMA has written TMEM (also on the error path)
+            if (!ok) tc_commit(chunk_done);  // error path: let the drain warps fall through their bounded wait sooner
         }
     } else {
         // ------------------------------------------------------------------ expansion groups
@@ -329,91 +474,66 @@ spmm_tc_kernel(const TcParams prm, const __grid_constant__ CUtensorMap tmap) {
         const int gtid = tid - 64 - group * 128;
         // Two register buffers in ping-pong: the global loads of the group's next tile are in flight while the
         // current one is written, and nothing is copied between the buffers.
+        int drained = 0;  // group 0: accumulation chunks already promoted
         auto run_group = [&](auto fetch, auto write, auto &buf_a, auto &buf_b) {
-            auto publish = [&](int64_t kb, auto &buf) -> bool {
-                const int s = (int)(kb % TC_STAGES);
+            auto publish = [&](int kb, auto &buf) -> bool {
+                const int s = kb % TC_STAGES;
                 const uint32_t ph = (uint32_t)((kb / TC_STAGES) & 1);
+                if (SPLIT && group == 0) {
+                    // Before feeding a later chunk, promote the finished ones: the MMAs of a chunk depend only on
+                    // tiles that are already published, so this wait cannot deadlock, and the MMA issuer needs
+                    // the promotion before it may restart the accumulator.
+                    while (drained < kb / chunk_it) {
+                        if (!drain_chunk(drained)) return false;
+                        drained++;
+                    }
+                }
                 if (!mbar_wait_bounded(&empty[s], ph ^ 1, prm.status, 14)) return false;
                 write(buf, a_stages + s * TC_A_BYTES);
                 fence_proxy_async_smem();  // generic-proxy stores -> visible to the tensor core's async-proxy reads
                 mbar_arrive(&full_a[s]);
                 return true;
             };
-            if (group < nkb) fetch(buf_a, (int64_t)group);
-            for (int64_t kb = group; kb < nkb; kb += 2 * TC_GROUPS) {
-                if (kb + TC_GROUPS < nkb) fetch(buf_b, kb + TC_GROUPS);
+            if (group < nkb) fetch(buf_a, group);
+            for (int kb = group; kb < nkb; kb += 2 * GROUPS) {
+                if (kb + GROUPS < nkb) fetch(buf_b, kb + GROUPS);
                 if (!publish(kb, buf_a)) break;
-                if (kb + TC_GROUPS >= nkb) break;
-                if (kb + 2 * TC_GROUPS < nkb) fetch(buf_a, kb + 2 * TC_GROUPS);
-                if (!publish(kb + TC_GROUPS, buf_b)) break;
+                if (kb + GROUPS >= nkb) break;
+                if (kb + 2 * GROUPS < nkb) fetch(buf_a, kb + 2 * GROUPS);
+                if (!publish(kb + GROUPS, buf_b)) break;
             }
         };
         if (TRANSPOSED) {
             TrRegs<N_, M_> ra, rb;
-            run_group([&](TrRegs<N_, M_> &t, int64_t kb) { fetch_transposed<N_, M_>(t, prm, feat0, kb, gtid); },
+            run_group([&](TrRegs<N_, M_> &t, int it) {
+                          fetch_transposed<N_, M_>(t, prm, prm.nval[TERMS == 1 ? 0 : kSplitW[it % TERMS]], feat0, it / TERMS, gtid);
+                      },
                       [&](const TrRegs<N_, M_> &t, char *tile) { write_transposed<N_, M_>(t, tile, sel, gtid); }, ra, rb);
         } else {
             FwdRegs<N_, M_> ra, rb;
-            run_group([&](FwdRegs<N_, M_> &t, int64_t kb) { fetch_forward<N_, M_>(t, prm, feat0, kb, gwarp, lane); },
+            run_group([&](FwdRegs<N_, M_> &t, int it) {
+                          fetch_forward<N_, M_>(t, prm, prm.nval[TERMS == 1 ? 0 : kSplitW[it % TERMS]], feat0, it / TERMS, gwarp, lane);
+                      },
                       [&](const FwdRegs<N_, M_> &t, char *tile) { write_forward<N_, M_>(t, tile, sel, gwarp, lane); }, ra, rb);
         }
         if (group == 0) {
-            // -------------------------------------------------------------- epilogue
-            if (mbar_wait_bounded(tmem_full, 0, prm.status, 15)) {
-                tc_fence_after();
-                const int q = warp & 3;  // TMEM lane quarter this warp may read
-                const int64_t feat = feat0 + q * 32 + lane;
-                const bool feat_ok = feat < prm.out_feats;
-                T *out = static_cast<T *>(prm.out);
-                const float b = (prm.bias && feat_ok) ? DT<T>::to_f32(static_cast<const T *>(prm.bias)[feat]) : 0.f;
-                for (int c = 0; c < TC_BN / 32; c++) {
-                    uint32_t r[32];
-                    tmem_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(c * 32), r);
-                    if (tok0 + c * 32 >= prm.ntok) continue;  // warp-uniform
-                    if (feat_ok) {
-                        const int64_t tokc = tok0 + c * 32;
-                        const bool vec = !prm.out_token_major && tokc + 32 <= prm.ntok && (prm.ld_out & 7) == 0 &&
-                                         (reinterpret_cast<uintptr_t>(out) & 15) == 0;
-                        if (vec) {  // 32 consecutive tokens of this feature: four 16-byte stores
-                            uint4 *dst = reinterpret_cast<uint4 *>(out + feat * prm.ld_out + tokc);
-#pragma unroll
-                            for (int v = 0; v < 4; v++) {
-                                uint32_t w[4];
-#pragma unroll
-                                for (int h = 0; h < 4; h++) {
-                                    const T lo = DT<T>::from_f32(__uint_as_float(r[8 * v + 2 * h]) + b);
-                                    const T hi = DT<T>::from_f32(__uint_as_float(r[8 * v + 2 * h + 1]) + b);
-                                    w[h] = (uint32_t)bits16<T>(lo) | ((uint32_t)bits16<T>(hi) << 16);
-                                }
-                                dst[v] = make_uint4(w[0], w[1], w[2], w[3]);
-                            }
-                        } else {
-#pragma unroll
-                            for (int j = 0; j < 32; j++) {
-                                const int64_t tok = tokc + j;
-                                if (tok < prm.ntok) {
-                                    const T o = DT<T>::from_f32(__uint_as_float(r[j]) + b);
-                                    if (prm.out_token_major) out[tok * prm.ld_out + feat] = o;
-                                    else out[feat * prm.ld_out + tok] = o;
-                                }
-                            }
-                        }
-                    }
-                }
-                tc_fence_before();
+            if constexpr (SPLIT) {
+                while (drained < nchunks && drain_chunk(drained)) drained++;  // remaining promotions, then the result
+            } else {
+                epilogue_once();
             }
         }
     }
     __syncthreads();
     if (warp == 1) {
         tc_fence_after();
-        tmem_dealloc(tmem_base, TC_TMEM_COLS);
+        tmem_dealloc(tmem_base, TMEM_COLS);
     }
 }
 
 // ------------------------------------------------------------------------------------------------------ host side
 bool tc_supported(const Geo &geo, int dtype) {
-    if (dtype != NMG_F16 && dtype != NMG_BF16) return false;
+    if (dtype != NMG_F16 && dtype != NMG_BF16 && dtype != NMG_F32) return false;
     return (geo.n == 1 && geo.m == 4) || (geo.n == 2 && geo.m == 4) || (geo.n == 1 && geo.m == 8) || (geo.n == 2 && geo.m == 8) ||
            (geo.n == 1 && geo.m == 16);
 }
@@ -422,36 +542,82 @@ static size_t tc_smem_bytes(int C) {
     return (size_t)TC_STAGES * (TC_A_BYTES + TC_B_BYTES) + 128 + (size_t)C * 16 + 1024;
 }
 
+// ---- fp32 activations: three bf16 planes [3][rows][ldp], written by one elementwise pass ---------------------------
+__global__ void split_f32_kernel(const float *__restrict__ src, int64_t rows, int64_t cols, int64_t ld_src,
+                                 __nv_bfloat16 *__restrict__ dst, int64_t ldp, int64_t plane_elems) {
+    const int64_t r = blockIdx.y;
+    for (int64_t c = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; c < ldp; c += (int64_t)gridDim.x * blockDim.x) {
+        const float f = c < cols ? src[r * ld_src + c] : 0.f;
+        const __nv_bfloat16 hi = __float2bfloat16_rn(f);
+        const float r1 = f - __bfloat162float(hi);
+        const __nv_bfloat16 mid = __float2bfloat16_rn(r1);
+        const __nv_bfloat16 lo = __float2bfloat16_rn(r1 - __bfloat162float(mid));
+        const int64_t o = r * ldp + c;
+        dst[o] = hi;
+        dst[plane_elems + o] = mid;
+        dst[2 * plane_elems + o] = lo;
+    }
+}
+
+size_t tc_split_workspace_bytes(const Geo &geo, int dtype, bool transposed, int64_t tokens) {
+    if (dtype != NMG_F32) return 0;
+    const int64_t red = transposed ? geo.M : geo.K;
+    return (size_t)3 * (size_t)tokens * (size_t)round_up(red, 8) * 2 + 512;
+}
+
 template <int N_, int M_, typename T, bool TR>
-static int tc_launch_one(const TcParams &p, const CUtensorMap &tm, cudaStream_t st) {
+static int tc_launch_one(const TcParams &p, const CUtensorMap *tm, cudaStream_t st) {
     const size_t smem = tc_smem_bytes((int)comb(N_, M_));
     const int64_t ctas = (int64_t)p.tiles_f * p.tiles_t;
     if (ctas > 0x7fffffff) NMG_FAIL(NMG_ERR_UNSUPPORTED, "too many output tiles for one launch");
     dim3 grid((unsigned)ctas);
     NMG_CUDA(cudaFuncSetAttribute(spmm_tc_kernel<N_, M_, T, TR>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    spmm_tc_kernel<N_, M_, T, TR><<<grid, TC_THREADS, smem, st>>>(p, tm);
+    spmm_tc_kernel<N_, M_, T, TR><<<grid, TC_THREADS, smem, st>>>(p, tm[0], tm[1], tm[2]);
     NMG_CUDA(cudaGetLastError());
     return NMG_OK;
 }
 
 template <int N_, int M_>
-static int tc_launch_nm(int dtype, bool transposed, const TcParams &p, const CUtensorMap &tm, cudaStream_t st) {
+static int tc_launch_nm(int dtype, bool transposed, const TcParams &p, const CUtensorMap *tm, cudaStream_t st) {
     if (dtype == NMG_F16) return transposed ? tc_launch_one<N_, M_, __half, true>(p, tm, st) : tc_launch_one<N_, M_, __half, false>(p, tm, st);
+    if (dtype == NMG_F32) return transposed ? tc_launch_one<N_, M_, float, true>(p, tm, st) : tc_launch_one<N_, M_, float, false>(p, tm, st);
     return transposed ? tc_launch_one<N_, M_, __nv_bfloat16, true>(p, tm, st) : tc_launch_one<N_, M_, __nv_bfloat16, false>(p, tm, st);
 }
 
 // act: [tokens][ld_act] with the reduction axis contiguous (X for the forward, dY for the transposed product).
 int tc_matmul(const Geo &geo, int dtype, bool transposed, const uint16_t *pat, const void *nval, const void *act,
               int64_t ld_act, int64_t tokens, const void *bias, void *out, int64_t ld_out, int out_token_major,
-              cudaStream_t st) {
+              void *ws, size_t ws_bytes, cudaStream_t st) {
     const int64_t red = transposed ? geo.M : geo.K;
-    CUtensorMap tm;
-    int rc = encode_tmap_2d(&tm, dtype, act, (uint64_t)red, (uint64_t)tokens, (uint64_t)ld_act, TC_BK, TC_BN, 1);
-    if (rc) return rc;
+    CUtensorMap tm[3];
+    int rc;
+    const void *planes[3] = {nval, nval, nval};
+    if (dtype == NMG_F32) {
+        const size_t need = tc_split_workspace_bytes(geo, dtype, transposed, tokens);
+        if (!ws || ws_bytes < need) NMG_FAIL(NMG_ERR_WORKSPACE, "workspace of %zu bytes required for the split activation, got %zu", need, ws_bytes);
+        __nv_bfloat16 *xs = reinterpret_cast<__nv_bfloat16 *>(((uintptr_t)ws + 255) & ~(uintptr_t)255);
+        const int64_t ldp = round_up(red, 8);
+        const int64_t plane_elems = tokens * ldp;
+        if (tokens > 65535 * 16) NMG_FAIL(NMG_ERR_UNSUPPORTED, "too many tokens for the split pre-pass");
+        for (int64_t r0 = 0; r0 < tokens; r0 += 65535) {  // grid.y limit
+            const int64_t nr = tokens - r0 < 65535 ? tokens - r0 : 65535;
+            dim3 grid((unsigned)((ldp + 255) / 256 > 32 ? 32 : (ldp + 255) / 256), (unsigned)nr);
+            split_f32_kernel<<<grid, 256, 0, st>>>(static_cast<const float *>(act) + r0 * ld_act, nr, red, ld_act, xs + r0 * ldp, ldp, plane_elems);
+        }
+        NMG_CUDA(cudaGetLastError());
+        for (int c = 0; c < 3; c++)
+            if ((rc = encode_tmap_2d(&tm[c], NMG_BF16, xs + c * plane_elems, (uint64_t)red, (uint64_t)tokens, (uint64_t)ldp, TC_BK, TC_BN, 1))) return rc;
+        const NaturalLayout lay = natural_layout(geo, dtype);
+        for (int c = 0; c < 3; c++) planes[c] = static_cast<const char *>(nval) + lay.val_bytes + c * lay.plane_bytes;
+    } else {
+        if ((rc = encode_tmap_2d(&tm[0], dtype, act, (uint64_t)red, (uint64_t)tokens, (uint64_t)ld_act, TC_BK, TC_BN, 1))) return rc;
+        tm[1] = tm[0];
+        tm[2] = tm[0];
+    }
     int *status = nullptr;
     if ((rc = get_status_word(&status))) return rc;
     const int64_t feats = transposed ? geo.K : geo.M;
-    TcParams p{pat, nval, bias, out, feats, red, tokens, ld_out, natural_width(geo), geo.nb, out_token_major,
+    TcParams p{pat, {planes[0], planes[1], planes[2]}, bias, out, feats, red, tokens, ld_out, natural_width(geo), geo.nb, out_token_major,
                (int)((feats + TC_BM - 1) / TC_BM), (int)((tokens + TC_BN - 1) / TC_BN), status};
     const ProfileEvents pe = take_profile_events();
     if (pe.start) NMG_CUDA(cudaEventRecord(pe.start, st));

@@ -38,7 +38,7 @@ def main():
     dy = torch.randn(a.tokens, M, generator=torch.Generator().manual_seed(2)).to(dev).to(dtype)
     xt = x.t().contiguous()
     wd = w.to(dtype).unsqueeze(0)
-    packed = None if (a.no_packed or dtype == torch.float32) else ops.pack(val, idx, M, K, n, m, g)
+    packed = None if a.no_packed else ops.pack(val, idx, M, K, n, m, g)
 
     def call():
         if a.op == "fwd":

@@ -145,15 +145,38 @@ def test_token_major_input_with_row_major_output(dtype):
     assert torch.equal(c2, y2.t())
 
 
-def test_tensor_core_is_the_default_for_half_precision_and_rejects_fp32():
+@pytest.mark.parametrize("n,m,g,M,K,tokens", TC_CASES + [(2, 4, 16, 512, 4096, 512)])
+def test_fp32_on_tensor_cores_by_exact_bf16_splitting(n, m, g, M, K, tokens):
+    """fp32 operands as sums of three bf16 pieces, six partial products in the fp32 accumulator: fp32 tolerance holds."""
+    from sten_b200 import _native as nat, ops
+    val, idx, x, dense = _problem(M, K, n, m, g, tokens, 70 * n + m + g)
+    bias = seeded_normal((M,), 8).to(cuda())
+    y = ops.spmm(val, idx, M, K, n, m, g, x, bias=bias, algo=nat.NMG_ALGO_TENSOR)
+    ref64 = np_of(x).astype(np.float64) @ np_of(dense).astype(np.float64).T + np_of(bias).astype(np.float64)
+    err = rel_fro(np_of(y), ref64)
+    print(f"split-bf16 forward {n}:{m} K={K}: rel. Frobenius error {err:.2e}")
+    assert err <= TOL_F32
+    packed = ops.pack(val, idx, M, K, n, m, g)
+    assert torch.equal(ops.spmm(val, idx, M, K, n, m, g, x, bias=bias, algo=nat.NMG_ALGO_TENSOR, packed=packed), y)
+    dy = seeded_normal((tokens, M), 96).to(cuda())
+    dx = ops.spmm_t(val, idx, M, K, n, m, g, dy, algo=nat.NMG_ALGO_TENSOR, packed=packed)
+    assert rel_fro(np_of(dx), np_of(dy).astype(np.float64) @ np_of(dense).astype(np.float64)) <= TOL_F32
+    # the SIMT transposed kernel reads the fp32 section of the same packed copy
+    dx_simt = ops.spmm_t(val, idx, M, K, n, m, g, dy, algo=nat.NMG_ALGO_SIMT, packed=packed)
+    assert rel_fro(np_of(dx_simt), np_of(dx)) <= TOL_F32
+    assert ops.read_status() == 0
+
+
+def test_tensor_core_is_the_default_for_half_precision():
     from sten_b200 import _native as nat, ops
     M, K, n, m, g, tokens = 256, 512, 2, 4, 16, 256
     val, idx, x, dense = _problem(M, K, n, m, g, tokens, 3, torch.bfloat16)
     auto = ops.spmm(val, idx, M, K, n, m, g, x)
     assert torch.equal(auto, ops.spmm(val, idx, M, K, n, m, g, x, algo=nat.NMG_ALGO_TENSOR))
-    val32, idx32, x32, _ = _problem(M, K, n, m, g, tokens, 3)
+    # 3:6 has no tensor-core kernel (6 does not divide the 128-row tile)
+    val36, idx36, x36, _ = _problem(60, 333, 3, 6, 4, 50, 3, torch.bfloat16)
     with pytest.raises(nat.NmgError) as e:
-        ops.spmm(val32, idx32, M, K, n, m, g, x32, algo=nat.NMG_ALGO_TENSOR)
+        ops.spmm(val36, idx36, 60, 333, 3, 6, 4, x36, algo=nat.NMG_ALGO_TENSOR)
     assert e.value.status == 2
 
 
