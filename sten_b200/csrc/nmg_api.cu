@@ -17,7 +17,7 @@ static char *align256(void *p) { return reinterpret_cast<char *>(((uintptr_t)p +
 // The tensor-core kernel reads the activation through a TMA descriptor: 16-bit dtype, reduction axis contiguous,
 // 16-byte aligned base and row pitch.
 static bool tensor_ok(const Geo &geo, int dtype, const void *act, int64_t ld_act) {
-    if (!tc_supported(geo, dtype)) return false;
+    if (!tc_supported(geo, dtype) && !tc_dense_supported(geo, dtype)) return false;
     if (dtype == NMG_F32) return true;  // fp32 activations are re-laid out into aligned bf16 planes first
     return (((uintptr_t)act) & 15) == 0 && (ld_act % 8) == 0;
 }
@@ -68,8 +68,10 @@ extern "C" size_t nmg_spmm_workspace_bytes(int64_t M, int64_t K, int64_t tokens,
     if (make_geo(M, K, n, m, g, &geo) || tokens < 1 || n < 1) return 0;
     size_t simt = simt_fwd_workspace_bytes(geo, tokens, dtype, layout);
     size_t tensor = 0;
-    if (algo != NMG_ALGO_SIMT && tc_supported(geo, dtype) && layout != NMG_ACT_K_MAJOR)
-        tensor = (have_packed ? 0 : natural_bytes(geo, dtype, nullptr) + 512) + tc_split_workspace_bytes(geo, dtype, false, tokens);
+    if (algo != NMG_ALGO_SIMT && (tc_supported(geo, dtype) || tc_dense_supported(geo, dtype)) && layout != NMG_ACT_K_MAJOR)
+        tensor = (tc_use_dense(geo, dtype, tokens) ? tc_dense_workspace_bytes(geo, dtype, false)
+                                                   : (have_packed ? 0 : natural_bytes(geo, dtype, nullptr) + 512)) +
+                 tc_split_workspace_bytes(geo, dtype, false, tokens);
     if (algo == NMG_ALGO_TENSOR) return tensor;
     return simt > tensor ? simt : tensor;  // AUTO may take either path depending on operand alignment
 }
@@ -92,7 +94,7 @@ extern "C" int nmg_spmm(const void *val, const int16_t *idx, const void *packed,
     cudaStream_t st = (cudaStream_t)stream;
     const bool can_tensor = tm && tensor_ok(geo, dtype, act, ld_act);
     if (algo == NMG_ALGO_TENSOR && !can_tensor)
-        NMG_FAIL(NMG_ERR_UNSUPPORTED, "tensor-core path needs fp16/bf16, m in {4,8,16}, token-major activations with 16-byte aligned rows");
+        NMG_FAIL(NMG_ERR_UNSUPPORTED, "tensor-core path needs token-major activations whose rows are 16-byte aligned (16-bit dtypes) and a chunk that fits shared memory");
     // AUTO: tensor cores whenever the problem fills at least one 128 x 256 tile reasonably; small problems and
     // unsupported patterns / layouts stay on the SIMT kernels.  fp32 on tensor cores means exact bf16 splitting with
     // promoted accumulation (measured relative error 3.5e-6, independent of K); NMG_ALGO_SIMT keeps plain fp32 FMAs.
@@ -101,8 +103,9 @@ extern "C" int nmg_spmm(const void *val, const int16_t *idx, const void *packed,
         size_t left = workspace_bytes;
         const uint16_t *pat = nullptr;
         const void *nval = nullptr;
-        if ((rc = resolve_packed(geo, dtype, val, idx, packed, &ws, &left, &pat, &nval, st))) return rc;
-        return tc_matmul(geo, dtype, false, pat, nval, act, ld_act, tokens, bias, out, ld_out, out_tm ? 1 : 0, ws, left, st);
+        const bool dense = tc_use_dense(geo, dtype, tokens);
+        if (!dense && (rc = resolve_packed(geo, dtype, val, idx, packed, &ws, &left, &pat, &nval, st))) return rc;
+        return tc_matmul(geo, dtype, false, dense, val, idx, pat, nval, act, ld_act, tokens, bias, out, ld_out, out_tm ? 1 : 0, ws, left, st);
     }
     return simt_fwd(geo, dtype, val, idx, act, ld_act, tokens, bias, out, ld_out, layout, workspace, workspace_bytes, st);
 }
@@ -111,10 +114,13 @@ extern "C" size_t nmg_spmm_t_workspace_bytes(int64_t M, int64_t K, int64_t token
                                              int algo, int have_packed) {
     Geo geo;
     if (make_geo(M, K, n, m, g, &geo) || tokens < 1 || n < 1) return 0;
-    size_t bytes = have_packed ? 0 : natural_bytes(geo, dtype, nullptr) + 512;
-    const size_t simt = algo != NMG_ALGO_TENSOR ? simt_bwd_workspace_bytes(geo, tokens, dtype) + 256 : 0;
-    const size_t tensor = algo != NMG_ALGO_SIMT ? tc_split_workspace_bytes(geo, dtype, true, tokens) : 0;
-    return bytes + (simt > tensor ? simt : tensor);
+    const size_t pack = have_packed ? 0 : natural_bytes(geo, dtype, nullptr) + 512;
+    const size_t simt = algo != NMG_ALGO_TENSOR ? pack + simt_bwd_workspace_bytes(geo, tokens, dtype) + 256 : 0;
+    size_t tensor = 0;
+    if (algo != NMG_ALGO_SIMT && (tc_supported(geo, dtype) || tc_dense_supported(geo, dtype)))
+        tensor = (tc_use_dense(geo, dtype, tokens) ? tc_dense_workspace_bytes(geo, dtype, true) : pack) +
+                 tc_split_workspace_bytes(geo, dtype, true, tokens);
+    return simt > tensor ? simt : tensor;
 }
 
 extern "C" int nmg_spmm_t(const void *val, const int16_t *idx, const void *packed, int64_t M, int64_t K, int n, int m,
@@ -131,13 +137,14 @@ extern "C" int nmg_spmm_t(const void *val, const int16_t *idx, const void *packe
     cudaStream_t st = (cudaStream_t)stream;
     const bool can_tensor = tensor_ok(geo, dtype, dy, ld_dy);
     if (algo == NMG_ALGO_TENSOR && !can_tensor)
-        NMG_FAIL(NMG_ERR_UNSUPPORTED, "tensor-core path needs fp16/bf16, m in {4,8,16} and 16-byte aligned gradient rows");
+        NMG_FAIL(NMG_ERR_UNSUPPORTED, "tensor-core path needs gradient rows that are 16-byte aligned (16-bit dtypes) and a chunk that fits shared memory");
     char *ws = static_cast<char *>(workspace);
     size_t left = workspace_bytes;
     const uint16_t *pat = nullptr;
     const void *nval = nullptr;
-    if ((rc = resolve_packed(geo, dtype, val, idx, packed, &ws, &left, &pat, &nval, st))) return rc;
-    if (algo == NMG_ALGO_TENSOR || (algo == NMG_ALGO_AUTO && can_tensor && tokens >= 64 && K >= 64))
-        return tc_matmul(geo, dtype, true, pat, nval, dy, ld_dy, tokens, nullptr, dx, ld_dx, 1, ws, left, st);
+    const bool tensor = algo == NMG_ALGO_TENSOR || (algo == NMG_ALGO_AUTO && can_tensor && tokens >= 64 && K >= 64);
+    const bool dense = tensor && tc_use_dense(geo, dtype, tokens);
+    if (!dense && (rc = resolve_packed(geo, dtype, val, idx, packed, &ws, &left, &pat, &nval, st))) return rc;
+    if (tensor) return tc_matmul(geo, dtype, true, dense, val, idx, pat, nval, dy, ld_dy, tokens, nullptr, dx, ld_dx, 1, ws, left, st);
     return simt_bwd(geo, dtype, pat, nval, dy, ld_dy, tokens, dx, ld_dx, ws, left, st);
 }

@@ -32,13 +32,23 @@ size_t simt_bwd_workspace_bytes(const Geo &geo, int64_t tokens, int dtype);
 int simt_bwd(const Geo &geo, int dtype, const uint16_t *pat, const void *nval, const void *dy, int64_t ld_dy,
              int64_t tokens, void *dx, int64_t ld_dx, void *ws, size_t ws_bytes, cudaStream_t st);
 
-// Tensor-core kernels (nmg_spmm_tc.cu).  act: [tokens][ld_act] with the reduction axis contiguous.  fp32 operands are
-// multiplied as sums of bf16 pieces and need `ws` (tc_split_workspace_bytes) for the split activation.
-bool tc_supported(const Geo &geo, int dtype);
+// Tensor-core kernels.  act: [tokens][ld_act] with the reduction axis contiguous.  fp32 operands are multiplied as
+// sums of bf16 pieces and need `ws` (tc_split_workspace_bytes) for the split activation.  Two variants share the
+// entry point tc_matmul: the fused kernel (nmg_spmm_tc.cu) expands the column-ordered copy (pat / nval) tile by tile
+// inside the matmul; the two-pass variant (nmg_gemm_tc.cu, `dense` = true) first expands (val, idx) into a dense 16-bit
+// matrix in `ws` (tc_dense_workspace_bytes, after the split activation) and multiplies that.  tc_use_dense is the
+// policy: two passes from 1024 tokens on, and for every (n, m) the fused kernel has no instantiation for.
+bool tc_supported(const Geo &geo, int dtype);        // fused kernel
+bool tc_dense_supported(const Geo &geo, int dtype);  // two-pass variant
+bool tc_use_dense(const Geo &geo, int dtype, int64_t tokens);
 size_t tc_split_workspace_bytes(const Geo &geo, int dtype, bool transposed, int64_t tokens);
-int tc_matmul(const Geo &geo, int dtype, bool transposed, const uint16_t *pat, const void *nval, const void *act,
-              int64_t ld_act, int64_t tokens, const void *bias, void *out, int64_t ld_out, int out_token_major,
-              void *ws, size_t ws_bytes, cudaStream_t st);
+size_t tc_dense_workspace_bytes(const Geo &geo, int dtype, bool transposed);
+int tc_matmul(const Geo &geo, int dtype, bool transposed, bool dense, const void *val, const int16_t *idx, const uint16_t *pat,
+              const void *nval, const void *act, int64_t ld_act, int64_t tokens, const void *bias, void *out, int64_t ld_out,
+              int out_token_major, void *ws, size_t ws_bytes, cudaStream_t st);
+int tc_dense_matmul(const Geo &geo, int dtype, bool transposed, const void *val, const int16_t *idx, const CUtensorMap *act_maps,
+                    int64_t tokens, const void *bias, void *out, int64_t ld_out, int out_token_major, void *ws, size_t ws_bytes,
+                    cudaStream_t st);
 
 // ---- specialised forward kernel: parameters, shared-memory plan, per-(n, m) launchers
 struct FwdParams {

@@ -36,7 +36,7 @@ CASES = [
     (1, 8, 16, 96, 1024, 128),
     (2, 8, 16, 72, 900, 130),
     (1, 16, 16, 100, 777, 64),
-    (3, 6, 4, 60, 333, 50),
+    (3, 6, 4, 60, 336, 56),
     (2, 4, 64, 64, 2000, 33),
     (4, 8, 1, 16, 150, 40),          # not specialised: generic kernels
     (5, 12, 2, 24, 1600, 9),         # generic, C = 792 patterns
@@ -173,11 +173,51 @@ def test_tensor_core_is_the_default_for_half_precision():
     val, idx, x, dense = _problem(M, K, n, m, g, tokens, 3, torch.bfloat16)
     auto = ops.spmm(val, idx, M, K, n, m, g, x)
     assert torch.equal(auto, ops.spmm(val, idx, M, K, n, m, g, x, algo=nat.NMG_ALGO_TENSOR))
-    # 3:6 has no tensor-core kernel (6 does not divide the 128-row tile)
-    val36, idx36, x36, _ = _problem(60, 333, 3, 6, 4, 50, 3, torch.bfloat16)
+    # 3:6 has no fused tensor-core kernel (6 does not divide the 128-row tile): the two-pass variant takes it
+    val36, idx36, x36, dense36 = _problem(60, 336, 3, 6, 4, 50, 3, torch.bfloat16)
+    y36 = ops.spmm(val36, idx36, 60, 336, 3, 6, 4, x36, algo=nat.NMG_ALGO_TENSOR)
+    assert rel_fro(np_of(y36), np_of(x36).astype(np.float64) @ np_of(dense36).astype(np.float64).T) <= TOL_HALF
+    # 16-bit activation rows that are not 16-byte aligned cannot be read by TMA: the forced tensor path refuses them
+    val_o, idx_o, x_o, _ = _problem(60, 333, 3, 6, 4, 50, 3, torch.bfloat16)
     with pytest.raises(nat.NmgError) as e:
-        ops.spmm(val36, idx36, 60, 333, 3, 6, 4, x36, algo=nat.NMG_ALGO_TENSOR)
+        ops.spmm(val_o, idx_o, 60, 333, 3, 6, 4, x_o, algo=nat.NMG_ALGO_TENSOR)
     assert e.value.status == 2
+
+
+TWO_PASS_CASES = [
+    # n, m, g, M, K, tokens: from 1024 tokens on (and for patterns without a fused kernel) the weight is expanded once
+    # into a dense 16-bit matrix and multiplied by the persistent TMA-fed kernel
+    (2, 4, 16, 256, 512, 1024),
+    (2, 8, 16, 264, 904, 1100),
+    (1, 16, 16, 400, 776, 1030),
+    (1, 4, 16, 128, 520, 1025),
+    (2, 4, 1, 136, 72, 1024),
+    (3, 6, 8, 304, 704, 1200),
+    (3, 6, 4, 64, 336, 56),
+    (1, 8, 3, 1000, 304, 2048),
+    (2, 8, 16, 203, 333, 1029),   # rows of 16-bit operands would not be 16-byte aligned: fp32 only
+    (1, 4, 5, 77, 130, 1500),
+]
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16, torch.float32])
+@pytest.mark.parametrize("n,m,g,M,K,tokens", TWO_PASS_CASES)
+def test_two_pass_tensor_core_forward_and_transposed(dtype, n, m, g, M, K, tokens):
+    from sten_b200 import _native as nat, ops
+    tol = TOL_F32 if dtype == torch.float32 else TOL_HALF
+    if dtype != torch.float32 and (K % 8 or M % 8):
+        pytest.skip("TMA needs 16-byte aligned activation rows")
+    val, idx, x, dense = _problem(M, K, n, m, g, tokens, 90 * n + m + g, dtype)
+    bias = seeded_normal((M,), 16).to(dtype).to(cuda())
+    y = ops.spmm(val, idx, M, K, n, m, g, x, bias=bias, algo=nat.NMG_ALGO_TENSOR)
+    ref64 = np_of(x).astype(np.float64) @ np_of(dense).astype(np.float64).T + np_of(bias).astype(np.float64)
+    assert rel_fro(np_of(y), ref64) <= tol
+    c = ops.spmm(val, idx, M, K, n, m, g, x, bias=bias, algo=nat.NMG_ALGO_TENSOR, layout=nat.NMG_ACT_TOKEN_MAJOR_OUT_ROWS)
+    assert torch.equal(c.t(), y)
+    dy = seeded_normal((tokens, M), 197).to(dtype).to(cuda())
+    dx = ops.spmm_t(val, idx, M, K, n, m, g, dy, algo=nat.NMG_ALGO_TENSOR)
+    assert rel_fro(np_of(dx), np_of(dy).astype(np.float64) @ np_of(dense).astype(np.float64)) <= tol
+    assert ops.read_status() == 0
 
 
 def test_against_stored_reference_microkernel_outputs():
