@@ -97,10 +97,14 @@ int nmg_pack(const void *val, const int16_t *idx, int64_t M, int64_t K, int n, i
  * needs it).  have_packed in the workspace query says which of the two the caller will do.
  * workspace: device scratch of at least nmg_spmm_workspace_bytes(...) bytes, 256-byte aligned, owned by the
  * caller for the duration of the call (may be NULL when the query returns 0).
- * algo: NMG_ALGO_AUTO uses the tensor-core kernel for m in {4, 8, 16}, n <= 2, token-major activations (16-bit
- * rows must be 16-byte aligned) and at least 64 tokens and 64 rows; the SIMT kernels otherwise.  fp32 operands go through
- * the tensor cores as exact three-way bf16 splits with promoted fp32 accumulation (relative error ~3.5e-6, independent
- * of K); NMG_ALGO_SIMT forces plain fp32 FMA arithmetic. */
+ * algo: NMG_ALGO_AUTO uses the tensor cores for token-major activations (16-bit rows must be 16-byte aligned) with at
+ * least 64 tokens and 64 rows; the SIMT kernels otherwise.  Two tensor-core variants exist.  Below 1024 tokens, for
+ * m in {4, 8, 16} and n <= 2, one fused kernel expands tiles of the packed copy inside the matmul.  From 1024 tokens
+ * on, and for every other (n, m), the weight is first expanded into a transient dense 16-bit matrix in the workspace
+ * (M * round_up(K, 8) * 2 bytes; three such planes for fp32) and multiplied by a persistent TMA-fed kernel; that
+ * variant reads val / idx and ignores `packed`.  fp32 operands go through the tensor cores as exact three-way bf16
+ * splits with promoted fp32 accumulation (relative error ~3.5e-6, independent of K); NMG_ALGO_SIMT forces plain fp32
+ * FMA arithmetic. */
 size_t nmg_spmm_workspace_bytes(int64_t M, int64_t K, int64_t tokens, int n, int m, int g, int dtype,
                                 int layout, int algo, int have_packed);
 int nmg_spmm(const void *val, const int16_t *idx, const void *packed, int64_t M, int64_t K, int n, int m, int g,
@@ -115,6 +119,26 @@ size_t nmg_spmm_t_workspace_bytes(int64_t M, int64_t K, int64_t tokens, int n, i
 int nmg_spmm_t(const void *val, const int16_t *idx, const void *packed, int64_t M, int64_t K, int n, int m, int g,
                int dtype, const void *dy, int64_t ld_dy, int64_t tokens, void *dx, int64_t ld_dx, int algo,
                void *workspace, size_t workspace_bytes, void *stream);
+
+/* Whether nmg_spmm (transposed = 0) or nmg_spmm_t (transposed = 1) would read the packed copy for this problem under
+ * `algo`, assuming aligned operands: 1 or 0.  Lets a host build and keep packed copies only for the weights and batch
+ * sizes that use them (the two-pass tensor-core variant and the SIMT forward kernel do not).  `layout` is ignored for
+ * transposed = 1.  No counterpart in the reference. */
+int nmg_spmm_uses_packed(int64_t M, int64_t K, int64_t tokens, int n, int m, int g, int dtype, int layout, int algo,
+                         int transposed);
+
+/* Row-shard matmul fused with the exchange of its result: C = W X^T (+ bias per row), C[M][ld_out >= tokens], written
+ * by the matmul kernel's epilogue into EVERY buffer of outs[0 .. n_outs) with 128-byte coalesced stores.  outs[0] is
+ * the caller's own buffer; the others are the same location of the same buffer on peer GPUs, mapped into this
+ * process (CUDA IPC or a symmetric-memory allocation), so that a row-sharded layer needs no all-gather: when every
+ * rank's call has completed, every GPU holds the full C.  The caller synchronises the ranks afterwards (any
+ * stream-ordered collective or barrier).  Operand conventions as nmg_spmm with NMG_ACT_TOKEN_MAJOR_OUT_ROWS; workspace
+ * as nmg_spmm_workspace_bytes(..., NMG_ACT_TOKEN_MAJOR_OUT_ROWS, NMG_ALGO_TENSOR, 0).  Runs on the two-pass tensor-core
+ * variant only: NMG_ERR_UNSUPPORTED below 1024 tokens or for unaligned 16-bit activation rows.  At most 8 buffers.
+ * No counterpart in the reference, which has no multi-GPU path for this format. */
+int nmg_spmm_replicated(const void *val, const int16_t *idx, int64_t M, int64_t K, int n, int m, int g, int dtype,
+                        const void *act, int64_t ld_act, int64_t tokens, const void *bias, void *const *outs, int n_outs,
+                        int64_t ld_out, void *workspace, size_t workspace_bytes, void *stream);
 
 /* Matmul for callers that cannot allocate device memory (no counterpart in the reference, whose host code allocates
  * every buffer with torch: src/sten/grouped_nm/grouped_nm_tensor.py:652-672, sten_impls.py:127).

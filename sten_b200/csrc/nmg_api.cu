@@ -76,12 +76,13 @@ extern "C" size_t nmg_spmm_workspace_bytes(int64_t M, int64_t K, int64_t tokens,
     return simt > tensor ? simt : tensor;  // AUTO may take either path depending on operand alignment
 }
 
-extern "C" int nmg_spmm(const void *val, const int16_t *idx, const void *packed, int64_t M, int64_t K, int n, int m,
-                        int g, int dtype, const void *act, int64_t ld_act, int64_t tokens, const void *bias, void *out,
-                        int64_t ld_out, int layout, int algo, void *workspace, size_t workspace_bytes, void *stream) {
+static int spmm_impl(const void *val, const int16_t *idx, const void *packed, int64_t M, int64_t K, int n, int m, int g, int dtype,
+                     const void *act, int64_t ld_act, int64_t tokens, const void *bias, void *const *outs, int n_outs, int64_t ld_out,
+                     int layout, int algo, void *workspace, size_t workspace_bytes, void *stream) {
     Geo geo;
     int rc = make_geo(M, K, n, m, g, &geo);
     if (rc) return rc;
+    void *out = outs[0];
     if ((rc = check_common(dtype, tokens, val, idx, act, out))) return rc;
     if (n < 1) NMG_FAIL(NMG_ERR_INVALID, "n must be >= 1");
     if (layout != NMG_ACT_TOKEN_MAJOR && layout != NMG_ACT_K_MAJOR && layout != NMG_ACT_TOKEN_MAJOR_OUT_ROWS)
@@ -105,9 +106,44 @@ extern "C" int nmg_spmm(const void *val, const int16_t *idx, const void *packed,
         const void *nval = nullptr;
         const bool dense = tc_use_dense(geo, dtype, tokens);
         if (!dense && (rc = resolve_packed(geo, dtype, val, idx, packed, &ws, &left, &pat, &nval, st))) return rc;
-        return tc_matmul(geo, dtype, false, dense, val, idx, pat, nval, act, ld_act, tokens, bias, out, ld_out, out_tm ? 1 : 0, ws, left, st);
+        return tc_matmul(geo, dtype, false, dense, val, idx, pat, nval, act, ld_act, tokens, bias, outs, n_outs, ld_out, out_tm ? 1 : 0, ws, left, st);
     }
+    if (n_outs > 1) NMG_FAIL(NMG_ERR_UNSUPPORTED, "several output buffers need the tensor-core path (aligned token-major activations, >= 64 tokens and rows)");
     return simt_fwd(geo, dtype, val, idx, act, ld_act, tokens, bias, out, ld_out, layout, workspace, workspace_bytes, st);
+}
+
+extern "C" int nmg_spmm(const void *val, const int16_t *idx, const void *packed, int64_t M, int64_t K, int n, int m,
+                        int g, int dtype, const void *act, int64_t ld_act, int64_t tokens, const void *bias, void *out,
+                        int64_t ld_out, int layout, int algo, void *workspace, size_t workspace_bytes, void *stream) {
+    void *outs[1] = {out};
+    return spmm_impl(val, idx, packed, M, K, n, m, g, dtype, act, ld_act, tokens, bias, outs, 1, ld_out, layout, algo, workspace,
+                     workspace_bytes, stream);
+}
+
+extern "C" int nmg_spmm_replicated(const void *val, const int16_t *idx, int64_t M, int64_t K, int n, int m, int g, int dtype,
+                                   const void *act, int64_t ld_act, int64_t tokens, const void *bias, void *const *outs, int n_outs,
+                                   int64_t ld_out, void *workspace, size_t workspace_bytes, void *stream) {
+    if (!outs || n_outs < 1 || n_outs > 8) NMG_FAIL(NMG_ERR_INVALID, "between 1 and 8 output buffers, got %d", n_outs);
+    for (int d = 0; d < n_outs; d++)
+        if (!outs[d]) NMG_FAIL(NMG_ERR_INVALID, "output buffer %d is NULL", d);
+    Geo geo;
+    int rc = make_geo(M, K, n, m, g, &geo);
+    if (rc) return rc;
+    if (!tc_dense_supported(geo, dtype) || !tc_use_dense(geo, dtype, tokens))
+        NMG_FAIL(NMG_ERR_UNSUPPORTED, "the replicated-output matmul runs on the two-pass tensor-core variant only (>= 1024 tokens)");
+    return spmm_impl(val, idx, nullptr, M, K, n, m, g, dtype, act, ld_act, tokens, bias, outs, n_outs, ld_out, NMG_ACT_TOKEN_MAJOR_OUT_ROWS,
+                     NMG_ALGO_TENSOR, workspace, workspace_bytes, stream);
+}
+
+extern "C" int nmg_spmm_uses_packed(int64_t M, int64_t K, int64_t tokens, int n, int m, int g, int dtype, int layout,
+                                    int algo, int transposed) {
+    Geo geo;
+    if (make_geo(M, K, n, m, g, &geo) || tokens < 1 || n < 1) return 0;
+    const bool any_tc = tc_supported(geo, dtype) || tc_dense_supported(geo, dtype);
+    const bool wants = algo == NMG_ALGO_TENSOR || (algo == NMG_ALGO_AUTO && tokens >= 64 && (transposed ? K : M) >= 64);
+    const bool tensor = any_tc && wants && (transposed || layout != NMG_ACT_K_MAJOR);
+    if (tensor) return tc_use_dense(geo, dtype, tokens) ? 0 : 1;
+    return transposed ? 1 : 0;  // SIMT: the transposed kernel reads the packed copy, the forward kernel val / idx
 }
 
 extern "C" size_t nmg_spmm_t_workspace_bytes(int64_t M, int64_t K, int64_t tokens, int n, int m, int g, int dtype,
@@ -145,6 +181,7 @@ extern "C" int nmg_spmm_t(const void *val, const int16_t *idx, const void *packe
     const bool tensor = algo == NMG_ALGO_TENSOR || (algo == NMG_ALGO_AUTO && can_tensor && tokens >= 64 && K >= 64);
     const bool dense = tensor && tc_use_dense(geo, dtype, tokens);
     if (!dense && (rc = resolve_packed(geo, dtype, val, idx, packed, &ws, &left, &pat, &nval, st))) return rc;
-    if (tensor) return tc_matmul(geo, dtype, true, dense, val, idx, pat, nval, dy, ld_dy, tokens, nullptr, dx, ld_dx, 1, ws, left, st);
+    void *dxs[1] = {dx};
+    if (tensor) return tc_matmul(geo, dtype, true, dense, val, idx, pat, nval, dy, ld_dy, tokens, nullptr, dxs, 1, ld_dx, 1, ws, left, st);
     return simt_bwd(geo, dtype, pat, nval, dy, ld_dy, tokens, dx, ld_dx, ws, left, st);
 }

@@ -28,14 +28,15 @@ namespace nmg {
 // Expansion pass
 // =========================================================================================================
 struct ExpandParams {
-    const void *val;            // [tiles][C][g][n]
-    const int16_t *idx;         // [tiles][C][g]
-    const int8_t *slot_of_row;  // [C][m]: slot that holds row r under pattern p, or -1
-    void *dst;                  // [planes][rows][ld] 16-bit
+    const void *val;        // [tiles][C][g][n]
+    const int16_t *idx;     // [tiles][C][g]
+    const int8_t *order;    // [C][n]: row of slot t under pattern p
+    void *dst;              // [planes][rows][ld] 16-bit
     int64_t ld, plane_elems;
     int64_t M, K, nb, nc;
     int n, m, g, C, cc;
-    int R;                      // row-blocks per work item
+    int R;                  // row-blocks per work item
+    int pitch;              // elements per line of the shared-memory tile
 };
 
 constexpr int EXPAND_THREADS = 256;
@@ -47,119 +48,130 @@ __device__ __forceinline__ void split3(float f, __nv_bfloat16 &hi, __nv_bfloat16
     lo = __float2bfloat16_rn(r1 - __bfloat162float(mid));
 }
 
-// One element (PAIR = false) or two adjacent elements starting at an even offset (PAIR = true).
-template <typename T, bool PAIR> __device__ __forceinline__ void expand_store(const ExpandParams &p, int64_t off, T a, T b) {
+// Move `cnt` (1..8) consecutive elements of a shared-memory line to the destination planes and clear them in shared
+// memory.  VEC: cnt == 8 and both sides are 16-byte aligned.
+template <typename T, bool VEC> __device__ __forceinline__ void expand_flush(const ExpandParams &p, T *line, int64_t off, int cnt) {
     if constexpr (sizeof(T) == 2) {
         T *d = static_cast<T *>(p.dst) + off;
-        if (PAIR) *reinterpret_cast<uint32_t *>(d) = (uint32_t)bits16<T>(a) | ((uint32_t)bits16<T>(b) << 16);
-        else *d = a;
+        if (VEC) {
+            *reinterpret_cast<uint4 *>(d) = *reinterpret_cast<const uint4 *>(line);
+            *reinterpret_cast<uint4 *>(line) = make_uint4(0, 0, 0, 0);
+        } else {
+            for (int i = 0; i < cnt; i++) { d[i] = line[i]; line[i] = DT<T>::from_f32(0.f); }
+        }
     } else {
-        __nv_bfloat16 pa[3], pb[3];
-        split3(a, pa[0], pa[1], pa[2]);
-        split3(b, pb[0], pb[1], pb[2]);
+        __nv_bfloat16 *d = static_cast<__nv_bfloat16 *>(p.dst) + off;
+        if (VEC) {
+            const float4 a = *reinterpret_cast<const float4 *>(line), b = *reinterpret_cast<const float4 *>(line + 4);
+            *reinterpret_cast<float4 *>(line) = make_float4(0.f, 0.f, 0.f, 0.f);
+            *reinterpret_cast<float4 *>(line + 4) = make_float4(0.f, 0.f, 0.f, 0.f);
+            const float f[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
+            uint32_t w[3][4];
 #pragma unroll
-        for (int c = 0; c < 3; c++) {
-            __nv_bfloat16 *d = static_cast<__nv_bfloat16 *>(p.dst) + c * p.plane_elems + off;
-            if (PAIR) *reinterpret_cast<uint32_t *>(d) = (uint32_t)__bfloat16_as_ushort(pa[c]) | ((uint32_t)__bfloat16_as_ushort(pb[c]) << 16);
-            else *d = pa[c];
+            for (int i = 0; i < 4; i++) {
+                __nv_bfloat16 x[3], y[3];
+                split3(f[2 * i], x[0], x[1], x[2]);
+                split3(f[2 * i + 1], y[0], y[1], y[2]);
+#pragma unroll
+                for (int c = 0; c < 3; c++) w[c][i] = (uint32_t)__bfloat16_as_ushort(x[c]) | ((uint32_t)__bfloat16_as_ushort(y[c]) << 16);
+            }
+#pragma unroll
+            for (int c = 0; c < 3; c++) *reinterpret_cast<uint4 *>(d + c * p.plane_elems) = make_uint4(w[c][0], w[c][1], w[c][2], w[c][3]);
+        } else {
+            for (int i = 0; i < cnt; i++) {
+                __nv_bfloat16 x[3];
+                split3(line[i], x[0], x[1], x[2]);
+                line[i] = 0.f;
+                for (int c = 0; c < 3; c++) d[c * p.plane_elems + i] = x[c];
+            }
         }
     }
 }
 
-// Work item = (column chunk kc, R consecutive row-blocks).  The item's values and an inverse index (column -> slot,
-// pattern) are staged in shared memory; then every output element is looked up and written in the orientation the
-// matmul wants, lanes along the contiguous axis of the destination.
+// Work item = (column chunk kc, R consecutive row-blocks).  The item's dense tile lives in shared memory, in the
+// orientation of the destination (TR = false: lines are weight rows, cc columns long; TR = true: lines are weight
+// columns, R * m rows long).  It starts as zeros; the item's non-zeros are scattered into it straight from global
+// memory (coalesced reads of val and idx, one thread per slot), and the tile is then moved out with 16-byte accesses
+// that also restore the zeros.
 template <typename T, bool TR>
 __global__ void __launch_bounds__(EXPAND_THREADS) expand_dense_kernel(const ExpandParams prm) {
     extern __shared__ __align__(16) char smem[];
-    const int n = prm.n, m = prm.m, g = prm.g, cc = prm.cc, R = prm.R;
-    T *sval = reinterpret_cast<T *>(smem);                                                            // [R][cc * n]
-    uint32_t *code = reinterpret_cast<uint32_t *>(smem + (((size_t)R * cc * n * sizeof(T) + 15) & ~(size_t)15));  // [R][cc]: pattern << 16 | slot
-    int8_t *sor = reinterpret_cast<int8_t *>(code + (size_t)R * cc);                                  // [C][m]
-    for (int i = threadIdx.x; i < prm.C * m; i += EXPAND_THREADS) sor[i] = prm.slot_of_row[i];
+    const int n = prm.n, m = prm.m, g = prm.g, cc = prm.cc, R = prm.R, pitch = prm.pitch;
+    const int lines = TR ? cc : R * m;
+    T *tile = reinterpret_cast<T *>(smem);                                  // [lines][pitch]
+    int8_t *ord = reinterpret_cast<int8_t *>(tile + (size_t)lines * pitch);  // [C][n]
+    for (int i = threadIdx.x; i < prm.C * n; i += EXPAND_THREADS) ord[i] = prm.order[i];
+    for (int i = threadIdx.x; i < lines * pitch; i += EXPAND_THREADS) tile[i] = DT<T>::from_f32(0.f);
 
     const T *val = static_cast<const T *>(prm.val);
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    constexpr int NW = EXPAND_THREADS / 32;
     const int64_t groups = (prm.nb + R - 1) / R;
     const int64_t items = groups * prm.nc;
-    const T zero = DT<T>::from_f32(0.f);
-
-    auto value = [&](int j, int r, int c) -> T {
-        const uint32_t cd = code[j * cc + c];
-        if (cd == 0xffffffffu) return zero;
-        const int t = sor[(cd >> 16) * m + r];
-        return t >= 0 ? sval[(size_t)j * cc * n + (cd & 0xffffu) * n + t] : zero;
-    };
+    const int vec_per_line = pitch / 8;  // pitch is a multiple of 8
 
     for (int64_t item = blockIdx.x; item < items; item += gridDim.x) {
         const int64_t kc = item / groups, mb0 = (item - kc * groups) * R;
         const int rj = (int)(prm.nb - mb0 < R ? prm.nb - mb0 : R);  // row-blocks in this item
-        __syncthreads();  // previous item fully written out
-        for (int e = threadIdx.x; e < rj * cc; e += EXPAND_THREADS) code[e] = 0xffffffffu;
+        __syncthreads();  // the tile is all zeros again
         // tiles of consecutive row-blocks of one chunk are consecutive in memory
-        const T *vsrc = val + (kc * prm.nb + mb0) * (int64_t)cc * n;
-        for (int e = threadIdx.x; e < rj * cc * n; e += EXPAND_THREADS) sval[e] = vsrc[e];
-        __syncthreads();
-        const int16_t *isrc = prm.idx + (kc * prm.nb + mb0) * (int64_t)cc;
+        const int64_t t0 = kc * prm.nb + mb0;
+        const int16_t *isrc = prm.idx + t0 * cc;
+        const T *vsrc = val + t0 * (int64_t)cc * n;
         for (int e = threadIdx.x; e < rj * cc; e += EXPAND_THREADS) {
             const int c = isrc[e];
+            if (c < 0 || c >= cc) continue;  // a malformed index is ignored, never dereferenced
             const int j = e / cc, s = e - j * cc;
-            if (c >= 0 && c < cc) code[j * cc + c] = ((uint32_t)(s / g) << 16) | (uint32_t)s;  // a malformed index is ignored
+            const int8_t *o = ord + (s / g) * n;
+            const T *v = vsrc + (int64_t)e * n;
+            T *base = TR ? tile + c * pitch + j * m : tile + (j * m) * pitch + c;
+            if (sizeof(T) == 2 && n == 2) {  // both values with one 32-bit load
+                const uint32_t vv = *reinterpret_cast<const uint32_t *>(v);
+                const uint16_t lo = (uint16_t)(vv & 0xffffu), hi = (uint16_t)(vv >> 16);
+                *reinterpret_cast<uint16_t *>(base + (TR ? o[0] : o[0] * pitch)) = lo;
+                *reinterpret_cast<uint16_t *>(base + (TR ? o[1] : o[1] * pitch)) = hi;
+            } else {
+                for (int t = 0; t < n; t++) base[TR ? o[t] : o[t] * pitch] = v[t];
+            }
         }
         __syncthreads();
-        const int64_t col0 = kc * cc;
-        const int ncol = (int)(prm.K - col0 < cc ? prm.K - col0 : cc);  // columns of this chunk inside the weight
-        if (!TR) {
-            // dst[row][col0 + c]: a warp per output row, lanes along columns
-            const bool pairs = ((cc & 1) == 0);
-            for (int rr = warp; rr < rj * m; rr += NW) {
-                const int j = rr / m, r = rr - j * m;
-                const int64_t row = (mb0 + j) * m + r;
-                if (row >= prm.M) continue;
-                const int64_t base = row * prm.ld + col0;
-                if (pairs) {
-                    for (int c = 2 * lane; c < ncol; c += 64) {
-                        if (c + 1 < ncol) expand_store<T, true>(prm, base + c, value(j, r, c), value(j, r, c + 1));
-                        else expand_store<T, false>(prm, base + c, value(j, r, c), zero);
-                    }
-                } else {
-                    for (int c = lane; c < ncol; c += 32) expand_store<T, false>(prm, base + c, value(j, r, c), zero);
-                }
+        const int64_t col0 = kc * cc, r0 = mb0 * m;
+        // line l, elements e .. e+7 -> dst[(TR ? col0 + l : r0 + l)][(TR ? r0 : col0) + e]
+        const int64_t line_lim = TR ? prm.K - col0 : prm.M - r0;   // lines inside the weight
+        const int64_t elem_lim = TR ? prm.M - r0 : prm.K - col0;   // elements of a line inside the weight
+        const int ne = TR ? rj * m : cc;                            // elements of a line this item owns
+        const bool aligned = ((TR ? r0 : col0) % 8) == 0;           // ld is a multiple of 8, the workspace is 256-byte aligned
+        for (int v = threadIdx.x; v < lines * vec_per_line; v += EXPAND_THREADS) {
+            const int l = v / vec_per_line, e = (v - l * vec_per_line) * 8;
+            T *line = tile + l * pitch + e;
+            if (l >= line_lim || e >= ne || e >= elem_lim) {  // outside the weight: nothing to store, but keep the tile clean
+                if constexpr (sizeof(T) == 2) *reinterpret_cast<uint4 *>(line) = make_uint4(0, 0, 0, 0);
+                else { *reinterpret_cast<float4 *>(line) = make_float4(0.f, 0.f, 0.f, 0.f); *reinterpret_cast<float4 *>(line + 4) = make_float4(0.f, 0.f, 0.f, 0.f); }
+                continue;
             }
-        } else {
-            // dst[col0 + c][mb0 * m + e]: a warp per weight column, lanes along the rj * m weight rows of the item
-            const bool pairs = ((m & 1) == 0);
-            const int seg = rj * m;
-            const int64_t r0 = mb0 * m;
-            for (int c = warp; c < ncol; c += NW) {
-                const int64_t base = (col0 + c) * prm.ld + r0;
-                if (pairs) {
-                    for (int e = 2 * lane; e < seg; e += 64) {
-                        if (r0 + e >= prm.M) break;
-                        const int j = e / m, r = e - j * m;
-                        if (r0 + e + 1 < prm.M) expand_store<T, true>(prm, base + e, value(j, r, c), value(j, r + 1, c));
-                        else expand_store<T, false>(prm, base + e, value(j, r, c), zero);
-                    }
-                } else {
-                    for (int e = lane; e < seg; e += 32) {
-                        if (r0 + e >= prm.M) break;
-                        const int j = e / m, r = e - j * m;
-                        expand_store<T, false>(prm, base + e, value(j, r, c), zero);
-                    }
-                }
+            const int64_t off = ((TR ? col0 : r0) + l) * prm.ld + (TR ? r0 : col0) + e;
+            // A full vector may run past the item's elements only into the row's padding (last chunk / last group:
+            // ld = round_up(extent, 8)), never into elements another item owns.
+            if (aligned && (e + 8 <= ne || ne >= elem_lim)) {
+                expand_flush<T, true>(prm, line, off, 8);
+            } else {
+                int cnt = ne - e < 8 ? ne - e : 8;
+                if (elem_lim - e < cnt) cnt = (int)(elem_lim - e);
+                expand_flush<T, false>(prm, line, off, cnt);
+                // elements of the vector past cnt were never written by this item's valid slots; clear them anyway
+                for (int i = cnt; i < 8; i++) line[i] = DT<T>::from_f32(0.f);
             }
         }
     }
 }
 
-static size_t expand_smem_bytes(const Geo &geo, size_t es, int R) {
-    return (((size_t)R * geo.cc * geo.n * es + 15) & ~(size_t)15) + (size_t)R * geo.cc * 4 + (size_t)geo.C * geo.m + 16;
+static int expand_pitch(const Geo &geo, bool tr, int R) { return (int)round_up(tr ? (int64_t)R * geo.m : (int64_t)geo.cc, 8) + 8; }
+static size_t expand_smem_bytes(const Geo &geo, size_t es, bool tr, int R) {
+    const size_t lines = tr ? (size_t)geo.cc : (size_t)R * geo.m;
+    return lines * expand_pitch(geo, tr, R) * es + (size_t)geo.C * geo.n + 16;
 }
-static int expand_rows_per_item(const Geo &geo, size_t es) {
+static int expand_rows_per_item(const Geo &geo, size_t es, bool tr) {
     int R = 64 / geo.m;
     if (R < 1) R = 1;
-    while (R > 1 && expand_smem_bytes(geo, es, R) > 96 * 1024) R >>= 1;
+    while (R > 1 && expand_smem_bytes(geo, es, tr, R) > 64 * 1024) R >>= 1;
     return R;
 }
 
@@ -169,14 +181,18 @@ static int expand_rows_per_item(const Geo &geo, size_t es) {
 constexpr int GEMM_THREADS = 32 * 6;  // TMA warp, MMA warp, four drain warps (one per TMEM lane quarter)
 constexpr int GEMM_STAGE_BYTES = TC_A_BYTES + TC_B_BYTES;
 
+constexpr int GEMM_MAX_OUTS = 8;
 struct GemmParams {
     const void *bias;  // [out_feats] or NULL
-    void *out;
+    void *outs[GEMM_MAX_OUTS];  // the result is written to every one of these (same shape and pitch): outs[0] is the
+    int n_out;                  // caller's buffer, the others are typically the same buffer on peer GPUs
     int64_t out_feats, red, ntok, ld_out;
     int out_token_major;
+    int out_staged;    // feature-major output whose rows are 16-byte aligned: go through the staging tile
     int tiles_f, tiles_t;
     int *status;
 };
+constexpr int GEMM_STAGING_BYTES = 4 * 4096;  // per drain warp: 32 feature rows x 128 bytes
 
 struct GemmMaps {
     CUtensorMap a[3];  // weight planes, box 64 x 128, 128-byte swizzle
@@ -193,7 +209,8 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_tc_kernel(const GemmPara
 
     extern __shared__ char smem_raw[];
     char *smem = reinterpret_cast<char *>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
-    char *misc = smem + TC_STAGES * GEMM_STAGE_BYTES;
+    char *staging = smem + TC_STAGES * GEMM_STAGE_BYTES;
+    char *misc = staging + GEMM_STAGING_BYTES;
     uint64_t *full = reinterpret_cast<uint64_t *>(misc);
     uint64_t *empty = full + TC_STAGES;
     uint64_t *acc_full = empty + TC_STAGES;  // [2] MMA issuer -> drain warps: unit complete in accumulator b
@@ -286,9 +303,16 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_tc_kernel(const GemmPara
         }
     } else {
         // ------------------------------------------------------------------ drain warps: promotion and epilogue
+        // Feature-major output (out[feature][token]) leaves through a per-warp staging tile: the warp's 32 features x
+        // 128 bytes of tokens, 16-byte chunks XOR-swizzled by row.  TMEM hands every lane one feature row; the staging
+        // tile turns that into stores whose 8 neighbouring lanes cover 128 contiguous bytes of one output row, which
+        // is what both HBM and NVLink want, and the same registers are stored to every destination buffer.
+        constexpr int CHUNK_TOK = 16 / (int)sizeof(T);         // tokens per 16-byte chunk
+        constexpr int GROUP_TOK = 128 / (int)sizeof(T);        // tokens per staged row: 64 (16-bit) or 32 (fp32)
+        constexpr int GROUP_SLICES = GROUP_TOK / 32;           // 32-column TMEM slices per staged group
         const int q = warp & 3;  // TMEM lane quarter this warp may access
         const uint32_t lane_base = tmem_base + ((uint32_t)(q * 32) << 16);
-        T *out = static_cast<T *>(prm.out);
+        char *stage_w = staging + (warp - 2) * 4096;
         int unit = 0;
         bool ok = true;
         for (int ti = 0; ti < my_tiles && ok; ti++) {
@@ -315,45 +339,76 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_tc_kernel(const GemmPara
                         tmem_st32(lane_base + (uint32_t)(TC_ACC_COLS + sl * 32), r);
                         continue;
                     }
+                    if (sl == TC_BN / 32 - 1) {  // every TMEM read of this unit is done: the issuer may reuse the accumulator
+                        tc_fence_before();
+                        __syncwarp();
+                        if (lane == 0) mbar_arrive(&acc_free[b]);
+                    }
                     const int64_t tokc = (int64_t)tok0 + sl * 32;
-                    if (tokc >= prm.ntok || !feat_ok) continue;
-                    const bool vec = !prm.out_token_major && tokc + 32 <= prm.ntok && (prm.ld_out % (16 / (int)sizeof(T))) == 0 &&
-                                     (reinterpret_cast<uintptr_t>(out) & 15) == 0;
-                    if (vec) {  // 32 consecutive tokens of this feature: 16-byte stores
-                        uint4 *dst = reinterpret_cast<uint4 *>(out + feat * prm.ld_out + tokc);
-                        if constexpr (sizeof(T) == 4) {
+                    if (!prm.out_staged) {
+                        if (tokc >= prm.ntok || !feat_ok) continue;
+                        for (int d = 0; d < prm.n_out; d++) {
+                            T *out = static_cast<T *>(prm.outs[d]);
 #pragma unroll
-                            for (int v = 0; v < 8; v++)
-                                dst[v] = make_uint4(__float_as_uint(__uint_as_float(r[4 * v]) + bias), __float_as_uint(__uint_as_float(r[4 * v + 1]) + bias),
-                                                    __float_as_uint(__uint_as_float(r[4 * v + 2]) + bias), __float_as_uint(__uint_as_float(r[4 * v + 3]) + bias));
-                        } else {
-#pragma unroll
-                            for (int v = 0; v < 4; v++) {
-                                uint32_t w[4];
-#pragma unroll
-                                for (int h = 0; h < 4; h++) {
-                                    const T lo = DT<T>::from_f32(__uint_as_float(r[8 * v + 2 * h]) + bias);
-                                    const T hi = DT<T>::from_f32(__uint_as_float(r[8 * v + 2 * h + 1]) + bias);
-                                    w[h] = (uint32_t)bits16<T>(lo) | ((uint32_t)bits16<T>(hi) << 16);
+                            for (int j = 0; j < 32; j++) {
+                                const int64_t tok = tokc + j;
+                                if (tok < prm.ntok) {
+                                    const T o = DT<T>::from_f32(__uint_as_float(r[j]) + bias);
+                                    if (prm.out_token_major) out[tok * prm.ld_out + feat] = o;
+                                    else out[feat * prm.ld_out + tok] = o;
                                 }
-                                dst[v] = make_uint4(w[0], w[1], w[2], w[3]);
                             }
                         }
-                    } else {
+                        continue;
+                    }
+                    // registers -> staging row `lane`
+                    constexpr int CH = 32 / CHUNK_TOK;  // chunks per slice: 4 (16-bit) or 8 (fp32)
+                    const int ch0 = (sl % GROUP_SLICES) * CH;
 #pragma unroll
-                        for (int j = 0; j < 32; j++) {
-                            const int64_t tok = tokc + j;
-                            if (tok < prm.ntok) {
-                                const T o = DT<T>::from_f32(__uint_as_float(r[j]) + bias);
-                                if (prm.out_token_major) out[tok * prm.ld_out + feat] = o;
-                                else out[feat * prm.ld_out + tok] = o;
+                    for (int v = 0; v < CH; v++) {
+                        uint4 w;
+                        if constexpr (sizeof(T) == 4) {
+                            w = make_uint4(__float_as_uint(__uint_as_float(r[4 * v]) + bias), __float_as_uint(__uint_as_float(r[4 * v + 1]) + bias),
+                                           __float_as_uint(__uint_as_float(r[4 * v + 2]) + bias), __float_as_uint(__uint_as_float(r[4 * v + 3]) + bias));
+                        } else {
+                            uint32_t h[4];
+#pragma unroll
+                            for (int k = 0; k < 4; k++) {
+                                const T lo = DT<T>::from_f32(__uint_as_float(r[8 * v + 2 * k]) + bias);
+                                const T hi = DT<T>::from_f32(__uint_as_float(r[8 * v + 2 * k + 1]) + bias);
+                                h[k] = (uint32_t)bits16<T>(lo) | ((uint32_t)bits16<T>(hi) << 16);
                             }
+                            w = make_uint4(h[0], h[1], h[2], h[3]);
+                        }
+                        *reinterpret_cast<uint4 *>(stage_w + lane * 128 + (((ch0 + v) ^ (lane & 7)) << 4)) = w;
+                    }
+                    if ((sl % GROUP_SLICES) != GROUP_SLICES - 1) continue;
+                    __syncwarp();
+                    // staging -> every destination: lane handles chunk (lane & 7) of rows (lane >> 3) + 4 i
+                    const int64_t tokg = (int64_t)tok0 + (sl / GROUP_SLICES) * GROUP_TOK + (lane & 7) * CHUNK_TOK;
+#pragma unroll
+                    for (int i = 0; i < 8; i++) {
+                        const int row = i * 4 + (lane >> 3);
+                        const int64_t f = (int64_t)feat0 + q * 32 + row;
+                        if (f >= prm.out_feats || tokg >= prm.ntok) continue;
+                        const uint4 w = *reinterpret_cast<const uint4 *>(stage_w + row * 128 + (((lane & 7) ^ (row & 7)) << 4));
+                        if (tokg + CHUNK_TOK <= prm.ntok) {
+                            for (int d = 0; d < prm.n_out; d++)
+                                *reinterpret_cast<uint4 *>(static_cast<T *>(prm.outs[d]) + f * prm.ld_out + tokg) = w;
+                        } else {  // ragged end of the token axis
+                            const T *e = reinterpret_cast<const T *>(&w);
+                            for (int d = 0; d < prm.n_out; d++)
+                                for (int k = 0; k < CHUNK_TOK && tokg + k < prm.ntok; k++)
+                                    (static_cast<T *>(prm.outs[d]) + f * prm.ld_out + tokg)[k] = e[k];
                         }
                     }
+                    __syncwarp();  // the staging rows are free for the next group
                 }
-                tc_fence_before();  // this warp's TMEM reads of the unit are complete (tcgen05.wait::ld in tmem_ld32)
-                __syncwarp();
-                if (lane == 0) mbar_arrive(&acc_free[b]);
+                if (!last) {  // promotion finished: hand the accumulator back
+                    tc_fence_before();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(&acc_free[b]);
+                }
             }
         }
     }
@@ -370,7 +425,7 @@ static int64_t dense_ld(int64_t red) { return round_up(red, 8); }  // row stride
 bool tc_dense_supported(const Geo &geo, int dtype) {
     const size_t es = dtype == NMG_F32 ? 4 : 2;
     if (geo.cc > 32767 || geo.C > 65535) return false;
-    return expand_smem_bytes(geo, es, 1) <= 200 * 1024;
+    return expand_smem_bytes(geo, es, false, 1) <= 200 * 1024 && expand_smem_bytes(geo, es, true, 1) <= 200 * 1024;
 }
 
 size_t tc_dense_workspace_bytes(const Geo &geo, int dtype, bool transposed) {
@@ -391,7 +446,7 @@ template <typename T, bool TR> static int expand_launch(const ExpandParams &p, s
 }
 
 template <typename T> static int gemm_launch(const GemmParams &p, const GemmMaps &maps, cudaStream_t st) {
-    const size_t smem = (size_t)TC_STAGES * GEMM_STAGE_BYTES + 256 + 1024;
+    const size_t smem = (size_t)TC_STAGES * GEMM_STAGE_BYTES + GEMM_STAGING_BYTES + 256 + 1024;
     int dev = 0, sms = 148;
     NMG_CUDA(cudaGetDevice(&dev));
     NMG_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
@@ -406,8 +461,9 @@ template <typename T> static int gemm_launch(const GemmParams &p, const GemmMaps
 // act_maps: tensor maps of the activation planes (box 64 x 256, 128-byte swizzle), one for 16-bit data, three for
 // the fp32 split.  ws holds the expanded weight for the duration of the call.
 int tc_dense_matmul(const Geo &geo, int dtype, bool transposed, const void *val, const int16_t *idx, const CUtensorMap *act_maps,
-                    int64_t tokens, const void *bias, void *out, int64_t ld_out, int out_token_major, void *ws, size_t ws_bytes,
-                    cudaStream_t st) {
+                    int64_t tokens, const void *bias, void *const *outs, int n_outs, int64_t ld_out, int out_token_major, void *ws,
+                    size_t ws_bytes, cudaStream_t st) {
+    if (n_outs < 1 || n_outs > GEMM_MAX_OUTS) NMG_FAIL(NMG_ERR_INVALID, "between 1 and %d output buffers, got %d", GEMM_MAX_OUTS, n_outs);
     const int64_t rows = transposed ? geo.K : geo.M, red = transposed ? geo.M : geo.K;
     const size_t need = tc_dense_workspace_bytes(geo, dtype, transposed);
     if (!ws || ws_bytes < need) NMG_FAIL(NMG_ERR_WORKSPACE, "workspace of %zu bytes required for the expanded weight, got %zu", need, ws_bytes);
@@ -420,12 +476,13 @@ int tc_dense_matmul(const Geo &geo, int dtype, bool transposed, const void *val,
     if ((rc = get_pattern_table(geo.n, geo.m, &tab))) return rc;
 
     ExpandParams ep{};
-    ep.val = val; ep.idx = idx; ep.slot_of_row = tab.slot_of_row; ep.dst = dense;
+    ep.val = val; ep.idx = idx; ep.order = tab.order; ep.dst = dense;
     ep.ld = ld; ep.plane_elems = rows * ld;
     ep.M = geo.M; ep.K = geo.K; ep.nb = geo.nb; ep.nc = geo.nc;
     ep.n = geo.n; ep.m = geo.m; ep.g = geo.g; ep.C = geo.C; ep.cc = geo.cc;
-    ep.R = expand_rows_per_item(geo, es);
-    const size_t esmem = expand_smem_bytes(geo, es, ep.R);
+    ep.R = expand_rows_per_item(geo, es, transposed);
+    ep.pitch = expand_pitch(geo, transposed, ep.R);
+    const size_t esmem = expand_smem_bytes(geo, es, transposed, ep.R);
     if (esmem > 200 * 1024) NMG_FAIL(NMG_ERR_UNSUPPORTED, "chunk of %d columns does not fit the expansion pass", geo.cc);
     const int64_t items = ((geo.nb + ep.R - 1) / ep.R) * geo.nc;
     if (dtype == NMG_F16) rc = transposed ? expand_launch<__half, true>(ep, esmem, items, st) : expand_launch<__half, false>(ep, esmem, items, st);
@@ -442,7 +499,22 @@ int tc_dense_matmul(const Geo &geo, int dtype, bool transposed, const void *val,
     }
     int *status = nullptr;
     if ((rc = get_status_word(&status))) return rc;
-    GemmParams gp{bias, out, rows, red, tokens, ld_out, out_token_major, (int)((rows + TC_BM - 1) / TC_BM), (int)((tokens + TC_BN - 1) / TC_BN), status};
+    GemmParams gp{};
+    gp.bias = bias;
+    gp.n_out = n_outs;
+    const size_t osz = dtype == NMG_F32 ? 4 : 2;
+    bool vec = !out_token_major && (ld_out * osz) % 16 == 0;
+    for (int d = 0; d < n_outs; d++) {
+        if (!outs[d]) NMG_FAIL(NMG_ERR_INVALID, "output buffer %d is NULL", d);
+        gp.outs[d] = outs[d];
+        vec = vec && (reinterpret_cast<uintptr_t>(outs[d]) & 15) == 0;
+    }
+    gp.out_feats = rows; gp.red = red; gp.ntok = tokens; gp.ld_out = ld_out;
+    gp.out_token_major = out_token_major;
+    gp.out_staged = vec ? 1 : 0;
+    gp.tiles_f = (int)((rows + TC_BM - 1) / TC_BM);
+    gp.tiles_t = (int)((tokens + TC_BN - 1) / TC_BN);
+    gp.status = status;
     if (dtype == NMG_F16) return gemm_launch<__half>(gp, maps, st);
     if (dtype == NMG_BF16) return gemm_launch<__nv_bfloat16>(gp, maps, st);
     return gemm_launch<float>(gp, maps, st);

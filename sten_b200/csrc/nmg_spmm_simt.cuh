@@ -43,12 +43,13 @@ bool tc_dense_supported(const Geo &geo, int dtype);  // two-pass variant
 bool tc_use_dense(const Geo &geo, int dtype, int64_t tokens);
 size_t tc_split_workspace_bytes(const Geo &geo, int dtype, bool transposed, int64_t tokens);
 size_t tc_dense_workspace_bytes(const Geo &geo, int dtype, bool transposed);
+// outs / n_outs: the result goes to every listed buffer (same shape and pitch); more than one needs `dense`.
 int tc_matmul(const Geo &geo, int dtype, bool transposed, bool dense, const void *val, const int16_t *idx, const uint16_t *pat,
-              const void *nval, const void *act, int64_t ld_act, int64_t tokens, const void *bias, void *out, int64_t ld_out,
-              int out_token_major, void *ws, size_t ws_bytes, cudaStream_t st);
+              const void *nval, const void *act, int64_t ld_act, int64_t tokens, const void *bias, void *const *outs, int n_outs,
+              int64_t ld_out, int out_token_major, void *ws, size_t ws_bytes, cudaStream_t st);
 int tc_dense_matmul(const Geo &geo, int dtype, bool transposed, const void *val, const int16_t *idx, const CUtensorMap *act_maps,
-                    int64_t tokens, const void *bias, void *out, int64_t ld_out, int out_token_major, void *ws, size_t ws_bytes,
-                    cudaStream_t st);
+                    int64_t tokens, const void *bias, void *const *outs, int n_outs, int64_t ld_out, int out_token_major, void *ws,
+                    size_t ws_bytes, cudaStream_t st);
 
 // ---- specialised forward kernel: parameters, shared-memory plan, per-(n, m) launchers
 struct FwdParams {

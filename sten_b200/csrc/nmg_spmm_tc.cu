@@ -791,19 +791,37 @@ static size_t tc_smem_bytes(int C) {
 }
 
 // ---- fp32 activations: three bf16 planes [3][rows][ldp], written by one elementwise pass ---------------------------
-__global__ void split_f32_kernel(const float *__restrict__ src, int64_t rows, int64_t cols, int64_t ld_src,
-                                 __nv_bfloat16 *__restrict__ dst, int64_t ldp, int64_t plane_elems) {
+__global__ void __launch_bounds__(128) split_f32_kernel(const float *__restrict__ src, int64_t rows, int64_t cols, int64_t ld_src,
+                                                        __nv_bfloat16 *__restrict__ dst, int64_t ldp, int64_t plane_elems) {
     const int64_t r = blockIdx.y;
-    for (int64_t c = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; c < ldp; c += (int64_t)gridDim.x * blockDim.x) {
-        const float f = c < cols ? src[r * ld_src + c] : 0.f;
-        const __nv_bfloat16 hi = __float2bfloat16_rn(f);
-        const float r1 = f - __bfloat162float(hi);
-        const __nv_bfloat16 mid = __float2bfloat16_rn(r1);
-        const __nv_bfloat16 lo = __float2bfloat16_rn(r1 - __bfloat162float(mid));
+    const float *row = src + r * ld_src;
+    const bool vec = (reinterpret_cast<uintptr_t>(row) & 15) == 0;
+    // eight elements per thread: two 16-byte loads, one 16-byte store per plane (ldp is a multiple of 8)
+    for (int64_t c = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) * 8; c < ldp; c += (int64_t)gridDim.x * blockDim.x * 8) {
+        float f[8];
+        if (vec && c + 8 <= cols) {
+            const float4 a = __ldg(reinterpret_cast<const float4 *>(row + c)), b = __ldg(reinterpret_cast<const float4 *>(row + c + 4));
+            f[0] = a.x; f[1] = a.y; f[2] = a.z; f[3] = a.w; f[4] = b.x; f[5] = b.y; f[6] = b.z; f[7] = b.w;
+        } else {
+#pragma unroll
+            for (int i = 0; i < 8; i++) f[i] = c + i < cols ? row[c + i] : 0.f;
+        }
+        uint32_t w[3][4];
+#pragma unroll
+        for (int i = 0; i < 8; i++) {
+            const __nv_bfloat16 hi = __float2bfloat16_rn(f[i]);
+            const float r1 = f[i] - __bfloat162float(hi);
+            const __nv_bfloat16 mid = __float2bfloat16_rn(r1);
+            const __nv_bfloat16 lo = __float2bfloat16_rn(r1 - __bfloat162float(mid));
+            const uint32_t sh = (i & 1) * 16;
+            if (!(i & 1)) { w[0][i >> 1] = 0; w[1][i >> 1] = 0; w[2][i >> 1] = 0; }
+            w[0][i >> 1] |= (uint32_t)__bfloat16_as_ushort(hi) << sh;
+            w[1][i >> 1] |= (uint32_t)__bfloat16_as_ushort(mid) << sh;
+            w[2][i >> 1] |= (uint32_t)__bfloat16_as_ushort(lo) << sh;
+        }
         const int64_t o = r * ldp + c;
-        dst[o] = hi;
-        dst[plane_elems + o] = mid;
-        dst[2 * plane_elems + o] = lo;
+#pragma unroll
+        for (int p = 0; p < 3; p++) *reinterpret_cast<uint4 *>(dst + p * plane_elems + o) = make_uint4(w[p][0], w[p][1], w[p][2], w[p][3]);
     }
 }
 
@@ -877,8 +895,10 @@ bool tc_use_dense(const Geo &geo, int dtype, int64_t tokens) {
 
 // act: [tokens][ld_act] with the reduction axis contiguous (X for the forward, dY for the transposed product).
 int tc_matmul(const Geo &geo, int dtype, bool transposed, bool dense, const void *val, const int16_t *idx, const uint16_t *pat,
-              const void *nval, const void *act, int64_t ld_act, int64_t tokens, const void *bias, void *out, int64_t ld_out,
-              int out_token_major, void *ws, size_t ws_bytes, cudaStream_t st) {
+              const void *nval, const void *act, int64_t ld_act, int64_t tokens, const void *bias, void *const *outs, int n_outs,
+              int64_t ld_out, int out_token_major, void *ws, size_t ws_bytes, cudaStream_t st) {
+    if (n_outs < 1 || (n_outs > 1 && !dense)) NMG_FAIL(NMG_ERR_UNSUPPORTED, "several output buffers need the two-pass tensor-core variant");
+    void *out = outs[0];
     const int64_t red = transposed ? geo.M : geo.K;
     const int64_t feats_all = transposed ? geo.K : geo.M;
     // The CTA-pair kernel is correct but measured slower than the one-CTA kernel (10.3 ms against 8.3 ms on the
@@ -899,8 +919,9 @@ int tc_matmul(const Geo &geo, int dtype, bool transposed, bool dense, const void
         if (tokens > 65535 * 16) NMG_FAIL(NMG_ERR_UNSUPPORTED, "too many tokens for the split pre-pass");
         for (int64_t r0 = 0; r0 < tokens; r0 += 65535) {  // grid.y limit
             const int64_t nr = tokens - r0 < 65535 ? tokens - r0 : 65535;
-            dim3 grid((unsigned)((ldp + 255) / 256 > 32 ? 32 : (ldp + 255) / 256), (unsigned)nr);
-            split_f32_kernel<<<grid, 256, 0, st>>>(static_cast<const float *>(act) + r0 * ld_act, nr, red, ld_act, xs + r0 * ldp, ldp, plane_elems);
+            const int64_t bx = (ldp / 8 + 127) / 128;
+            dim3 grid((unsigned)(bx > 64 ? 64 : bx), (unsigned)nr);
+            split_f32_kernel<<<grid, 128, 0, st>>>(static_cast<const float *>(act) + r0 * ld_act, nr, red, ld_act, xs + r0 * ldp, ldp, plane_elems);
         }
         NMG_CUDA(cudaGetLastError());
         for (int c = 0; c < 3; c++)
@@ -919,7 +940,7 @@ int tc_matmul(const Geo &geo, int dtype, bool transposed, bool dense, const void
     if (dense) {
         const ProfileEvents pe = take_profile_events();
         if (pe.start) NMG_CUDA(cudaEventRecord(pe.start, st));
-        rc = tc_dense_matmul(geo, dtype, transposed, val, idx, tm, tokens, bias, out, ld_out, out_token_major, ws, ws_bytes, st);
+        rc = tc_dense_matmul(geo, dtype, transposed, val, idx, tm, tokens, bias, outs, n_outs, ld_out, out_token_major, ws, ws_bytes, st);
         if (rc == NMG_OK && pe.stop) NMG_CUDA(cudaEventRecord(pe.stop, st));
         return rc;
     }

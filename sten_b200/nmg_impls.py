@@ -55,15 +55,20 @@ def _weight_geometry(weight):
     return gnm, int(M), int(K), s["n"], s["m"], s["group_size"]
 
 
-def _packed_or_none(gnm):
-    """The cached column-ordered copy for 16-bit weights (the tensor-core kernels read it), else None."""
-    return gnm.packed() if gnm.val.dtype in (torch.float16, torch.bfloat16) and gnm.val.is_cuda else None
+def _packed_or_none(gnm, geometry, tokens, layout=nat.NMG_ACT_TOKEN_MAJOR, transposed=False):
+    """The cached column-ordered copy when the kernel that will run reads it, else None (nothing is built)."""
+    M, K, n, m, g = geometry
+    if not gnm.val.is_cuda or not ops.uses_packed(M, K, tokens, n, m, g, gnm.val.dtype, layout, transposed=transposed):
+        return None
+    return gnm.packed()
 
 
 def sparse_dense_mul_dispatch(weight, dense2d, bias, layout):
     """One C-ABI call; replaces the compile-or-load + ctypes call of the reference (sten_impls.py:44-140)."""
     gnm, M, K, n, m, g = _weight_geometry(weight)
-    return ops.spmm(gnm.val, gnm.idx, M, K, n, m, g, dense2d, bias=bias, layout=layout, packed=_packed_or_none(gnm))
+    tokens = dense2d.shape[1] if layout == nat.NMG_ACT_K_MAJOR else dense2d.shape[0]
+    packed = _packed_or_none(gnm, (M, K, n, m, g), tokens, layout) if tokens else None
+    return ops.spmm(gnm.val, gnm.idx, M, K, n, m, g, dense2d, bias=bias, layout=layout, packed=packed)
 
 
 def _linear_fwd(ctx, inputs, output_sparsifiers):
@@ -93,7 +98,8 @@ def _linear_bwd(ctx, grad_outputs, input_sparsifiers):
     dy2d = dy.reshape(-1, M)
     dx = dw = db = None
     if needs[0]:
-        dx = ops.spmm_t(gnm.val, gnm.idx, M, K, n, m, g, dy2d, packed=_packed_or_none(gnm)).reshape(x.shape)
+        dx = ops.spmm_t(gnm.val, gnm.idx, M, K, n, m, g, dy2d,
+                        packed=_packed_or_none(gnm, (M, K, n, m, g), dy2d.shape[0], transposed=True)).reshape(x.shape)
     if needs[1]:
         # dense weight gradient (training of nmg weights is outside the inference hot path): plain GEMM
         dw = dy2d.t().mm(x.reshape(-1, K))
@@ -126,7 +132,9 @@ def _mm_bwd(ctx, grad_outputs, input_sparsifiers):
         dw = dc.mm(b.t())
     if needs[1]:
         # dB = W^T dC : the transposed kernel computes (dC^T W)[N, K]; hand back its transpose
-        db = ops.spmm_t(gnm.val, gnm.idx, M, K, n, m, g, dc.t().contiguous(), packed=_packed_or_none(gnm)).t()
+        dct = dc.t().contiguous()
+        db = ops.spmm_t(gnm.val, gnm.idx, M, K, n, m, g, dct,
+                        packed=_packed_or_none(gnm, (M, K, n, m, g), dct.shape[0], transposed=True)).t()
     return dw, db
 
 

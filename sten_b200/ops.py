@@ -106,6 +106,13 @@ def pack(val, idx, M, K, n, m, g):
     return buf
 
 
+def uses_packed(M, K, tokens, n, m, g, dtype, layout=nat.NMG_ACT_TOKEN_MAJOR, algo=nat.NMG_ALGO_AUTO, transposed=False):
+    """Whether spmm (or spmm_t when `transposed`) would read the packed copy for this problem: the fused tensor-core
+    kernel and the SIMT transposed kernel do; the two-pass tensor-core variant and the SIMT forward kernel do not."""
+    code = {torch.float32: nat.NMG_F32, torch.float16: nat.NMG_F16, torch.bfloat16: nat.NMG_BF16}[dtype]
+    return bool(nat.lib().nmg_spmm_uses_packed(M, K, tokens, n, m, g, code, layout, algo, 1 if transposed else 0))
+
+
 def spmm(val, idx, M, K, n, m, g, act, bias=None, layout=nat.NMG_ACT_TOKEN_MAJOR, algo=nat.NMG_ALGO_AUTO, out=None,
          packed=None):
     """layout TOKEN_MAJOR:          act [tokens, K] -> out [tokens, M] = act @ W^T (+ bias)
@@ -136,6 +143,32 @@ def spmm(val, idx, M, K, n, m, g, act, bias=None, layout=nat.NMG_ACT_TOKEN_MAJOR
                              bias.data_ptr() if bias is not None else None, out.data_ptr(), (out.shape[1] if out.is_contiguous() else out.stride(0)), layout, algo,
                              ws.data_ptr() if ws is not None else None, nbytes, _stream(dev)))
     return out
+
+
+def spmm_replicated(val, idx, M, K, n, m, g, act, out_ptrs, ld_out, bias=None):
+    """C = W @ act^T (+ bias per row) written into every buffer of ``out_ptrs`` (device addresses of [M, ld_out] row
+    panels: this GPU's and the peers' mapped copies) by the matmul kernel itself.  The caller keeps the buffers alive and
+    synchronises the ranks afterwards."""
+    import ctypes
+    dev = _require_cuda(val, idx, act, bias)
+    code = _dtype_code(val)
+    if act.dtype != val.dtype or (bias is not None and bias.dtype != val.dtype):
+        raise TypeError(f"activation / bias dtype must match the weight dtype {val.dtype}")
+    act, ld_act = _row_major_2d(act)
+    tokens = act.shape[0]
+    if act.shape[1] != K:
+        raise ValueError(f"activation shape {tuple(act.shape)} does not match K={K}")
+    val, idx = val.contiguous(), idx.contiguous()
+    if bias is not None:
+        bias = bias.contiguous()
+    L = nat.lib()
+    ptrs = (ctypes.c_void_p * len(out_ptrs))(*[int(p) for p in out_ptrs])
+    with torch.cuda.device(dev):
+        ws, nbytes = _workspace(L.nmg_spmm_workspace_bytes(M, K, tokens, n, m, g, code, nat.NMG_ACT_TOKEN_MAJOR_OUT_ROWS,
+                                                           nat.NMG_ALGO_TENSOR, 0), dev)
+        nat.check(L.nmg_spmm_replicated(val.data_ptr(), idx.data_ptr(), M, K, n, m, g, code, act.data_ptr(), ld_act, tokens,
+                                        bias.data_ptr() if bias is not None else None, ptrs, len(out_ptrs), ld_out,
+                                        ws.data_ptr() if ws is not None else None, nbytes, _stream(dev)))
 
 
 def spmm_t(val, idx, M, K, n, m, g, dy, algo=nat.NMG_ALGO_AUTO, packed=None):

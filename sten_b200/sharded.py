@@ -31,11 +31,23 @@ def row_shard_bounds(M, world_size, m):
     return bounds
 
 
-def _default_matmul(gnm, x2d, bias):
+def _geometry(gnm):
     s = gnm.nm_strides
     M, K = s["dense_shape"]
-    packed = gnm.packed() if gnm.val.dtype in (torch.float16, torch.bfloat16) else None
-    return ops.spmm(gnm.val, gnm.idx, int(M), int(K), s["n"], s["m"], s["group_size"], x2d, bias=bias, packed=packed)
+    return int(M), int(K), s["n"], s["m"], s["group_size"]
+
+
+def _packed_if_used(gnm, tokens, layout):
+    """The cached column-ordered copy when the kernel that will run reads it (few tokens), else None."""
+    M, K, n, m, g = _geometry(gnm)
+    return gnm.packed() if tokens and ops.uses_packed(M, K, tokens, n, m, g, gnm.val.dtype, layout) else None
+
+
+def _default_matmul(gnm, x2d, bias):
+    from . import _native as nat
+    M, K, n, m, g = _geometry(gnm)
+    return ops.spmm(gnm.val, gnm.idx, M, K, n, m, g, x2d, bias=bias,
+                    packed=_packed_if_used(gnm, x2d.shape[0], nat.NMG_ACT_TOKEN_MAJOR))
 
 
 class ShardedGroupedNMLinear:
@@ -194,8 +206,6 @@ class RowShardedNMMatmul:
 
 def _default_matmul_rows(gnm, x2d, out_rows):
     from . import _native as nat
-    s = gnm.nm_strides
-    M, K = s["dense_shape"]
-    packed = gnm.packed() if gnm.val.dtype in (torch.float16, torch.bfloat16) else None
-    ops.spmm(gnm.val, gnm.idx, int(M), int(K), s["n"], s["m"], s["group_size"], x2d, packed=packed,
-             layout=nat.NMG_ACT_TOKEN_MAJOR_OUT_ROWS, out=out_rows)
+    M, K, n, m, g = _geometry(gnm)
+    layout = nat.NMG_ACT_TOKEN_MAJOR_OUT_ROWS
+    ops.spmm(gnm.val, gnm.idx, M, K, n, m, g, x2d, packed=_packed_if_used(gnm, x2d.shape[0], layout), layout=layout, out=out_rows)
