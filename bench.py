@@ -61,10 +61,13 @@ def measured_peaks():
         return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}, "fallback"
 
 
-def config_dict(workload, n_gpus):
+def config_dict(workload, n_gpus, exchange="peer", rounds=1):
     if workload == "sharded":
+        how = ("no exchange" if n_gpus == 1 else
+               "the matmul epilogue stores every output tile into all ranks' buffers over NVLink (peer stores), one 4-byte all-reduce orders the ranks"
+               if exchange == "peer" else f"{rounds} block-cyclic rounds, in-place NCCL all-gather of output slices overlapped with the next round")
         return {"workload": "row-sharded matmul: W 16384x16384 N(0,0.02) seed 0 bf16, nmg 2:8 g=16, X 16384x16384 N(0,1) seed 1 bf16",
-                "group_size": G, "parallelism": f"weight rows split over {n_gpus} rank(s), NCCL all-gather of output slices",
+                "group_size": G, "parallelism": f"weight rows split over {n_gpus} rank(s); {how}",
                 "l2": "operands (0.5 GB activations + 0.5 GB output per step) exceed the 126 MB L2"}
     return {"workload": "density sweep: W 4096x4096 N(0,1) seed 0, nmg {1:4,2:4,1:8,2:8,1:16} g=16, X 4096x4096 fp32 seed 1",
             "tokens_per_gpu": SW_TOK, "group_size": G, "parallelism": f"token-sharded x{n_gpus}, no collective",
@@ -274,7 +277,7 @@ def run_ours(args):
     if args.workload == "sharded":
         M, K, TOK, n, m = SH_M, SH_K, SH_TOK, SH_N, SH_MM
         gen = torch.Generator(device=dev).manual_seed(0)
-        rounds = args.rounds if world > 1 else 1
+        rounds = (args.rounds or (1 if args.exchange == "peer" else 4)) if world > 1 else 1
         rp = RowShardedNMMatmul.panel_rows(M, world, rounds, m)
         owned = {(p * world + rank): p for p in range(rounds)}  # global panel index -> local round
         # the same seeded stream on every rank; only this rank's row panels are kept (block-cyclic over ranks)
@@ -288,13 +291,17 @@ def run_ours(args):
         x = torch.randn(TOK, K, generator=torch.Generator(device=dev).manual_seed(1), device=dev).bfloat16()
         panels = [sten.GroupedNMTensor.from_dense(wd, n, m, sparse_dim=0, group_size=G, group_dim=1) for wd in panels_dense]
         del panels_dense
-        layer = RowShardedNMMatmul(panels, M)
-        y_dev = torch.empty(M, TOK, dtype=torch.bfloat16, device=dev)
+        layer = RowShardedNMMatmul(panels, M, exchange=args.exchange)
+        peer = args.exchange == "peer" and world > 1  # the layer then owns the (peer-mapped) output buffer
+        y_dev = None if peer else torch.empty(M, TOK, dtype=torch.bfloat16, device=dev)
         total_flops = useful_flops(M, K, TOK, n, m)
         launches_per_step = 2 * rounds  # expansion pass + matmul kernel per panel
 
         def step():
             return layer(x, out=y_dev)
+
+        if peer:
+            y_dev = layer(x)  # allocates and maps the output buffers once, outside the timed region
 
         x_host = torch.empty(TOK, K, dtype=torch.bfloat16).pin_memory()
         x_host.copy_(x)
@@ -394,7 +401,7 @@ def run_ours(args):
         result = {
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
             "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": scaling, "vs_baseline": None,
-            "dtype": dtype_name, "data": "synthetic", "config": config_dict(args.workload, world),
+            "dtype": dtype_name, "data": "synthetic", "config": config_dict(args.workload, world, args.exchange, rounds if args.workload == "sharded" else 1),
             "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
             "gpu_launches": args.steps * launches_per_step, "clocks": clocks, "roofline": roofline, "cpu_baseline": cpu,
             "fp32_fma_peak_tflops": fma.value, "sweep": sweep,
@@ -495,7 +502,9 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="sharded", choices=["sharded", "sweep", "encoder"])
-    ap.add_argument("--rounds", type=int, default=4, help="gather rounds (row panels per rank) when N > 1")
+    ap.add_argument("--rounds", type=int, default=0, help="row panels per rank when N > 1 (default: 1 for --exchange peer, 4 for gather)")
+    ap.add_argument("--exchange", default="peer", choices=["peer", "gather"],
+                    help="how row shards combine their output slices when N > 1: stores into every rank's buffer from the matmul epilogue, or NCCL all-gathers")
     ap.add_argument("--no-sweep", action="store_true", help="skip the per-pattern 4096^2 table")
     args = ap.parse_args()
     if args.workload == "encoder":

@@ -137,6 +137,43 @@ class ShardedGroupedNMLinear:
     __call__ = forward
 
 
+class PeerBuffer:
+    """A device buffer of the same shape on every rank, with every rank's copy mapped into this process.
+
+    ``ptrs[r]`` is the device address of rank ``r``'s copy as seen from this process (``ptrs[rank]`` is the local
+    tensor ``local``), so a kernel on this GPU can store into all of them over NVLink.  Uses PyTorch's symmetric-memory
+    allocator; when that is unavailable, CUDA IPC handles of an ordinary allocation are exchanged instead."""
+
+    def __init__(self, shape, dtype, device, group=None):
+        self.group = group if group is not None else dist.group.WORLD
+        self.world, self.rank = dist.get_world_size(self.group), dist.get_rank(self.group)
+        self._keep = []
+        try:
+            import torch.distributed._symmetric_memory as symm
+            self.local = symm.empty(tuple(shape), dtype=dtype, device=device)
+            hdl = symm.rendezvous(self.local, self.group)
+            self._keep.append(hdl)
+            self.ptrs = [int(p) for p in hdl.buffer_ptrs]
+            self.how = "symmetric memory"
+        except Exception as exc:  # noqa: BLE001 - any failure of the optional allocator selects the IPC route
+            self.local = torch.empty(tuple(shape), dtype=dtype, device=device)
+            storage = self.local.untyped_storage()
+            mine = (storage._share_cuda_(), self.local.storage_offset() * self.local.element_size())
+            gathered = [None] * self.world
+            dist.all_gather_object(gathered, mine, group=self.group)
+            self.ptrs = []
+            for r, (handle, offset) in enumerate(gathered):
+                if r == self.rank:
+                    self.ptrs.append(self.local.data_ptr())
+                    continue
+                peer = torch.UntypedStorage._new_shared_cuda(*handle)
+                self._keep.append(peer)
+                self.ptrs.append(peer.data_ptr() + offset)
+            self.how = f"CUDA IPC (symmetric memory unavailable: {type(exc).__name__})"
+        if self.ptrs[self.rank] != self.local.data_ptr():
+            raise RuntimeError("peer buffer table does not list the local copy at this rank's index")
+
+
 class RowShardedNMMatmul:
     """``C[M, tokens] = W @ X^T`` (the ``torch.mm`` orientation) with ``W`` row-sharded block-cyclically.
 
@@ -147,7 +184,12 @@ class RowShardedNMMatmul:
 
     ``panels``: this rank's panels as ``GroupedNMTensor`` objects, in round order."""
 
-    def __init__(self, panels, M_total, group=None, matmul=None):
+    def __init__(self, panels, M_total, group=None, matmul=None, exchange="gather"):
+        if exchange not in ("gather", "peer"):
+            raise ValueError("exchange must be 'gather' (NCCL all-gather per round) or 'peer' (the matmul kernel stores into every rank's buffer)")
+        self.exchange = exchange
+        self._peer_out = None
+        self._flag = None
         self.group = group
         self.world = dist.get_world_size(group) if dist.is_initialized() else 1
         self.rank = dist.get_rank(group) if dist.is_initialized() else 0
@@ -173,19 +215,46 @@ class RowShardedNMMatmul:
         return M // (world * rounds)
 
     @classmethod
-    def from_full_weight(cls, weight, n, m, g, rounds=4, group=None, matmul=None, sparsify=None):
+    def from_full_weight(cls, weight, n, m, g, rounds=4, group=None, matmul=None, sparsify=None, exchange="gather"):
         world = dist.get_world_size(group) if dist.is_initialized() else 1
         rank = dist.get_rank(group) if dist.is_initialized() else 0
         M = weight.shape[0]
         rp = cls.panel_rows(M, world, rounds, m)
         make = sparsify or (lambda w: GroupedNMTensor.from_dense(w, n, m, sparse_dim=0, group_size=g, group_dim=1))
         panels = [make(weight[(p * world + rank) * rp:(p * world + rank + 1) * rp]) for p in range(rounds)]
-        return cls(panels, M, group, matmul)
+        return cls(panels, M, group, matmul, exchange)
+
+    def _forward_peer(self, x2d):
+        """Every panel's matmul writes its rows of ``C`` into all ranks' buffers from its own epilogue (stores over
+        NVLink, overlapped tile by tile with the tensor-core work); one tiny all-reduce orders the ranks afterwards.
+        The returned buffer is reused by the next call: consume or copy it before calling again."""
+        tokens = x2d.shape[0]
+        rp, R = self.rows_per_panel, self.world
+        ld = tokens
+        if self._peer_out is None or tuple(self._peer_out.local.shape) != (self.M_total, ld) or self._peer_out.local.dtype != x2d.dtype:
+            self._peer_out = PeerBuffer((self.M_total, ld), x2d.dtype, x2d.device, self.group)
+            self._flag = torch.zeros(1, device=x2d.device)
+        es = x2d.element_size()
+        for p, panel in enumerate(self.panels):
+            q = p * R + self.rank
+            M, K, n, m, g = _geometry(panel)
+            ptrs = [base + q * rp * ld * es for base in self._peer_out.ptrs]
+            # own copy first: outs[0] is the buffer the bias / alignment checks refer to
+            ptrs = [ptrs[self.rank]] + [a for r, a in enumerate(ptrs) if r != self.rank]
+            ops.spmm_replicated(panel.val, panel.idx, M, K, n, m, g, x2d, ptrs, ld)
+        dist.all_reduce(self._flag, group=self.group)  # stream-ordered: completes when every rank's stores are done
+        return self._peer_out.local
 
     def forward(self, x2d, out=None):
         """``x2d``: [tokens, K] (replicated).  Returns ``C`` [M, tokens] complete on every rank."""
         if x2d.dim() != 2 or x2d.shape[1] != self.K:
             raise ValueError(f"activation must be [tokens, {self.K}]")
+        if self.exchange == "peer" and self.world > 1:
+            res = self._forward_peer(x2d)
+            if out is not None and out.data_ptr() != res.data_ptr():
+                out.copy_(res)
+                return out
+            return res
         tokens = x2d.shape[0]
         rp, R = self.rows_per_panel, self.world
         if out is None:

@@ -1,0 +1,70 @@
+"""Row-sharded matmul on two GPUs: the exchange done by the matmul epilogue (stores into every rank's buffer over
+NVLink) against the NCCL all-gather variant and against a dense product.  Needs two GPUs; skipped otherwise.
+NVLS is switched off for the NCCL calls of this test (plain rings / trees are enough for a 4-byte all-reduce)."""
+import datetime
+import os
+import socket
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def _free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _worker(rank, world, port, result_q):
+    import torch.distributed as dist
+    import sten_b200 as sten
+    from sten_b200.sharded import RowShardedNMMatmul
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    os.environ["NCCL_NVLS_ENABLE"] = "0"
+    torch.cuda.set_device(rank)
+    dev = torch.device("cuda", rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, timeout=datetime.timedelta(seconds=120), device_id=dev)
+    try:
+        M, K, tokens, n, m, g = 1024, 520, 1104, 2, 8, 16
+        gen = torch.Generator().manual_seed(5)
+        w = (torch.randn(M, K, generator=gen) * 0.05).bfloat16().to(dev)
+        x = torch.randn(tokens, K, generator=gen).bfloat16().to(dev)
+        results = {}
+        for exchange, rounds in (("peer", 1), ("peer", 2), ("gather", 2)):
+            layer = RowShardedNMMatmul.from_full_weight(w, n, m, g, rounds=rounds, exchange=exchange)
+            for _ in range(2):  # the peer buffers are reused by the second call
+                c = layer(x)
+            torch.cuda.synchronize()
+            results[(exchange, rounds)] = c.clone()
+        full = sten.GroupedNMTensor.from_dense(w, n, m, sparse_dim=0, group_size=g, group_dim=1).to_dense()
+        ref = full.double() @ x.double().t()
+        errs = {k: float((v.double() - ref).norm() / ref.norm()) for k, v in results.items()}
+        same = all(torch.equal(results[("peer", 1)], v) for v in results.values())
+        result_q.put((rank, errs, same, None))
+    except Exception as exc:  # noqa: BLE001 - reported to the parent, which fails the test
+        result_q.put((rank, None, False, repr(exc)))
+    finally:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_peer_store_exchange_matches_all_gather_and_dense():
+    import torch.multiprocessing as mp
+    world = 2
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_worker, args=(r, world, port, q)) for r in range(world)]
+    for p in procs:
+        p.start()
+    got = [q.get(timeout=300) for _ in range(world)]
+    for p in procs:
+        p.join(timeout=60)
+    for rank, errs, same, exc in got:
+        assert exc is None, f"rank {rank}: {exc}"
+        assert same, f"rank {rank}: exchange variants disagree"
+        assert all(e <= 1e-2 for e in errs.values()), (rank, errs)
