@@ -308,10 +308,11 @@ def run_ours(args):
         y_host = torch.empty(M, TOK, dtype=torch.bfloat16).pin_memory()
 
         def e2e_step():
-            xd = x_host.to(dev, non_blocking=True)
-            y_host.copy_(layer(xd, out=y_dev), non_blocking=True)
+            # pinned host operands in, pinned host result out: chunked 3-stream pipeline on one GPU; on several, every
+            # rank uploads 1/N of X (completed over NVLink) and downloads the rows it computed
+            layer.forward_host(x_host, y_host)
 
-        h2d, d2h = x_host.numel() * 2, y_host.numel() * 2
+        h2d, d2h = x_host.numel() * 2, y_host.numel() * 2  # summed over ranks: every byte of X goes up once, of C comes down once
         dtype_name, scaling = "bf16", "strong"
     else:
         M, K, TOK = SW_M, SW_K, SW_TOK

@@ -168,6 +168,13 @@ int nmg_spmm_noalloc(const void *val, const int16_t *idx, int64_t M, int64_t K, 
 int nmg_profile_next(void *start_event, void *stop_event);
 int nmg_measure_fma_peak(double *tflops_out, void *stream);
 
+/* Pitched asynchronous copy between host and device (or device and device): `rows` rows of `width_bytes` bytes,
+ * row pitches dst_pitch / src_pitch bytes, queued on `stream`.  A host helper for pipelines that move a column block
+ * of a row-major matrix (a token chunk of C[M][tokens]) between pinned host memory and the GPU while other chunks
+ * compute; the direction is inferred from the pointers.  No counterpart in the reference. */
+int nmg_memcpy_2d_async(void *dst, size_t dst_pitch, const void *src, size_t src_pitch, size_t width_bytes, size_t rows,
+                        void *stream);
+
 /* Device-side status word of the last kernels launched by this thread on the current device: 0 when every
  * bounded wait completed.  Synchronises the given stream. */
 int nmg_read_status(void *stream, int *status_out);

@@ -36,6 +36,7 @@ SIGNATURES = {
     "nmg_spmm_noalloc": (_int, [_vp, _vp, _i64, _i64, _int, _int, _int, _int, _vp, _i64, _i64, _vp, _vp, _i64, _int, _vp]),
     "nmg_profile_next": (_int, [_vp, _vp]),
     "nmg_measure_fma_peak": (_int, [ctypes.POINTER(ctypes.c_double), _vp]),
+    "nmg_memcpy_2d_async": (_int, [_vp, _sz, _vp, _sz, _sz, _sz, _vp]),
     "nmg_read_status": (_int, [_vp, ctypes.POINTER(_int)]),
 }
 

@@ -93,10 +93,12 @@ template <typename T, bool VEC> __device__ __forceinline__ void expand_flush(con
 // columns, R * m rows long).  It starts as zeros; the item's non-zeros are scattered into it straight from global
 // memory (coalesced reads of val and idx, one thread per slot), and the tile is then moved out with 16-byte accesses
 // that also restore the zeros.
-template <typename T, bool TR>
+// N_ = n for the vectorised scatter (1 or 2), 0 for the generic one.
+template <typename T, bool TR, int N_>
 __global__ void __launch_bounds__(EXPAND_THREADS) expand_dense_kernel(const ExpandParams prm) {
     extern __shared__ __align__(16) char smem[];
-    const int n = prm.n, m = prm.m, g = prm.g, cc = prm.cc, R = prm.R, pitch = prm.pitch;
+    constexpr bool VEC_OK = N_ > 0;
+    const int n = N_ > 0 ? N_ : prm.n, m = prm.m, g = prm.g, cc = prm.cc, R = prm.R, pitch = prm.pitch;
     const int lines = TR ? cc : R * m;
     T *tile = reinterpret_cast<T *>(smem);                                  // [lines][pitch]
     int8_t *ord = reinterpret_cast<int8_t *>(tile + (size_t)lines * pitch);  // [C][n]
@@ -116,22 +118,33 @@ __global__ void __launch_bounds__(EXPAND_THREADS) expand_dense_kernel(const Expa
         const int64_t t0 = kc * prm.nb + mb0;
         const int16_t *isrc = prm.idx + t0 * cc;
         const T *vsrc = val + t0 * (int64_t)cc * n;
-        for (int e = threadIdx.x; e < rj * cc; e += EXPAND_THREADS) {
-            const int c = isrc[e];
-            if (c < 0 || c >= cc) continue;  // a malformed index is ignored, never dereferenced
+        auto scatter = [&](int e, int c, const T *v) {  // slot e of the item holds column c and the values v[0 .. n)
+            if (c < 0 || c >= cc) return;  // a malformed index is ignored, never dereferenced
             const int j = e / cc, s = e - j * cc;
             const int8_t *o = ord + (s / g) * n;
-            const T *v = vsrc + (int64_t)e * n;
             T *base = TR ? tile + c * pitch + j * m : tile + (j * m) * pitch + c;
-            if (sizeof(T) == 2 && n == 2) {  // both values with one 32-bit load
-                const uint32_t vv = *reinterpret_cast<const uint32_t *>(v);
-                const uint16_t lo = (uint16_t)(vv & 0xffffu), hi = (uint16_t)(vv >> 16);
-                *reinterpret_cast<uint16_t *>(base + (TR ? o[0] : o[0] * pitch)) = lo;
-                *reinterpret_cast<uint16_t *>(base + (TR ? o[1] : o[1] * pitch)) = hi;
-            } else {
-                for (int t = 0; t < n; t++) base[TR ? o[t] : o[t] * pitch] = v[t];
+            for (int t = 0; t < n; t++) base[TR ? o[t] : o[t] * pitch] = v[t];
+        };
+        const int total = rj * cc;
+        bool vectorised = false;
+        if constexpr (VEC_OK) if ((cc & 7) == 0) {
+            vectorised = true;
+            // eight slots per thread: one 16-byte load of indices and N_ 16-byte (16-bit) or 2 N_ (fp32) loads of values,
+            // all issued before the first use, so a whole item's global loads are in flight together
+            constexpr int VL = N_ * (int)sizeof(T) / 2;  // 16-byte loads of values per 8 slots
+            for (int e8 = threadIdx.x * 8; e8 < total; e8 += EXPAND_THREADS * 8) {
+                const uint4 iv = __ldg(reinterpret_cast<const uint4 *>(isrc + e8));
+                uint4 vv[VL];
+#pragma unroll
+                for (int u = 0; u < VL; u++) vv[u] = __ldg(reinterpret_cast<const uint4 *>(vsrc + (int64_t)e8 * N_) + u);
+                const int16_t *ci = reinterpret_cast<const int16_t *>(&iv);
+                const T *vals = reinterpret_cast<const T *>(vv);
+#pragma unroll
+                for (int u = 0; u < 8; u++) scatter(e8 + u, ci[u], vals + u * N_);
             }
         }
+        if (!vectorised)
+            for (int e = threadIdx.x; e < total; e += EXPAND_THREADS) scatter(e, isrc[e], vsrc + (int64_t)e * n);
         __syncthreads();
         const int64_t col0 = kc * cc, r0 = mb0 * m;
         // line l, elements e .. e+7 -> dst[(TR ? col0 + l : r0 + l)][(TR ? r0 : col0) + e]
@@ -434,15 +447,22 @@ size_t tc_dense_workspace_bytes(const Geo &geo, int dtype, bool transposed) {
     return planes * (size_t)rows * (size_t)dense_ld(red) * 2 + 512;
 }
 
-template <typename T, bool TR> static int expand_launch(const ExpandParams &p, size_t smem, int64_t items, cudaStream_t st) {
+template <typename T, bool TR, int N_> static int expand_launch_n(const ExpandParams &p, size_t smem, int64_t items, cudaStream_t st) {
     int dev = 0, sms = 148;
     NMG_CUDA(cudaGetDevice(&dev));
     NMG_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
     const int64_t cap = (int64_t)sms * 16;
-    NMG_CUDA(cudaFuncSetAttribute(expand_dense_kernel<T, TR>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    expand_dense_kernel<T, TR><<<(unsigned)(items < cap ? items : cap), EXPAND_THREADS, smem, st>>>(p);
+    NMG_CUDA(cudaFuncSetAttribute(expand_dense_kernel<T, TR, N_>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    expand_dense_kernel<T, TR, N_><<<(unsigned)(items < cap ? items : cap), EXPAND_THREADS, smem, st>>>(p);
     NMG_CUDA(cudaGetLastError());
     return NMG_OK;
+}
+template <typename T, bool TR> static int expand_launch(const ExpandParams &p, size_t smem, int64_t items, cudaStream_t st) {
+    // the vectorised scatter reads 16-byte pieces of val / idx: tile bases are 16-byte aligned when cc is a multiple of 8
+    const bool aligned = (reinterpret_cast<uintptr_t>(p.val) & 15) == 0 && (reinterpret_cast<uintptr_t>(p.idx) & 15) == 0;
+    if (aligned && p.n == 1) return expand_launch_n<T, TR, 1>(p, smem, items, st);
+    if (aligned && p.n == 2) return expand_launch_n<T, TR, 2>(p, smem, items, st);
+    return expand_launch_n<T, TR, 0>(p, smem, items, st);
 }
 
 template <typename T> static int gemm_launch(const GemmParams &p, const GemmMaps &maps, cudaStream_t st) {

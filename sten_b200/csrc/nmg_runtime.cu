@@ -151,6 +151,15 @@ int nmg_profile_next(void *start_event, void *stop_event) {
     return NMG_OK;
 }
 
+int nmg_memcpy_2d_async(void *dst, size_t dst_pitch, const void *src, size_t src_pitch, size_t width_bytes, size_t rows,
+                        void *stream) {
+    if (!dst || !src) NMG_FAIL(NMG_ERR_INVALID, "NULL pointer");
+    if (width_bytes == 0 || rows == 0) return NMG_OK;
+    if (dst_pitch < width_bytes || src_pitch < width_bytes) NMG_FAIL(NMG_ERR_INVALID, "pitch smaller than the row width");
+    NMG_CUDA(cudaMemcpy2DAsync(dst, dst_pitch, src, src_pitch, width_bytes, rows, cudaMemcpyDefault, (cudaStream_t)stream));
+    return NMG_OK;
+}
+
 int nmg_read_status(void *stream, int *status_out) {
     if (!status_out) NMG_FAIL(NMG_ERR_INVALID, "status_out is NULL");
     int *dev = nullptr;

@@ -9,9 +9,7 @@ constexpr int TC_BM = 128;    // output features per CTA (MMA M)
 constexpr int TC_BN = 256;    // tokens per CTA (MMA N)
 constexpr int TC_BK = 64;     // reduction elements per stage: one 128-byte swizzle span of 16-bit data
 constexpr int TC_STAGES = 4;
-constexpr int TC_THREADS = 32 * 14;  // TMA warp, MMA warp, 12 worker warps
-// Worker warps: three expansion groups of 4 warps; group 0 also drains the accumulator (promotion in fp32 mode,
-// epilogue in every mode).
+constexpr int TC_THREADS = 32 * 14;  // fused kernel: TMA warp, MMA warp, three expansion groups of 4 warps (group 0 also drains)
 constexpr int TC_CHUNK_KB = 8;       // fp32 mode: k-blocks (of 64) accumulated in the tensor core before promotion
 constexpr int TC_A_BYTES = TC_BM * TC_BK * 2;  // 16 KB
 constexpr int TC_B_BYTES = TC_BN * TC_BK * 2;  // 32 KB

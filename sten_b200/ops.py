@@ -196,6 +196,26 @@ def spmm_t(val, idx, M, K, n, m, g, dy, algo=nat.NMG_ALGO_AUTO, packed=None):
     return dx
 
 
+def copy_2d_async(dst, src, stream=None):
+    """Queue a pitched copy between two 2-D tensors of the same shape and dtype whose rows are contiguous (one of them
+    typically a column block of a pinned host matrix).  Unlike ``Tensor.copy_`` it never stages through pageable memory."""
+    if dst.shape != src.shape or dst.dim() != 2 or dst.dtype != src.dtype:
+        raise ValueError("copy_2d_async needs two 2-D tensors of equal shape and dtype")
+    if dst.stride(1) != 1 or src.stride(1) != 1:
+        raise ValueError("rows must be contiguous")
+    es = dst.element_size()
+    cuda_side = dst if dst.is_cuda else src
+    if not cuda_side.is_cuda:
+        raise TypeError("one side must be a CUDA tensor")
+    for t in (dst, src):
+        if not t.is_cuda and not t.is_pinned():
+            raise TypeError("the host side must be pinned memory")
+    st = stream.cuda_stream if stream is not None else _stream(cuda_side.device)
+    with torch.cuda.device(cuda_side.device):
+        nat.check(nat.lib().nmg_memcpy_2d_async(dst.data_ptr(), dst.stride(0) * es, src.data_ptr(), src.stride(0) * es,
+                                                dst.shape[1] * es, dst.shape[0], st))
+
+
 def read_status(dev=None):
     """Synchronise the current stream and raise if any kernel's bounded wait ran out."""
     import ctypes

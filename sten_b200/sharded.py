@@ -272,6 +272,66 @@ class RowShardedNMMatmul:
 
     __call__ = forward
 
+    def forward_host(self, x_host, out_host, chunk_tokens=4096):
+        """The same product with operands in pinned host memory: ``x_host`` [tokens, K] in, ``out_host`` [M, tokens] out.
+
+        One rank: the token axis is cut into chunks and three streams overlap the upload of chunk i+1, the matmul of
+        chunk i and the (pitched) download of chunk i-1, so the step costs about one PCIe direction instead of
+        upload + matmul + download.  Several ranks: every rank uploads 1/R of the tokens and the activation is
+        completed by an all-gather over NVLink (R PCIe links work in parallel), the matmul exchanges its output through
+        peer stores or all-gathers as configured, and every rank downloads only the rows it computed into its
+        ``out_host``.  Returns ``out_host``; the copies are complete when the current stream is."""
+        tokens = x_host.shape[0]
+        dev = self.panels[0].val.device
+        cur = torch.cuda.current_stream(dev)
+        rp, R = self.rows_per_panel, self.world
+        if R > 1:
+            if tokens % R:
+                raise ValueError(f"tokens={tokens} must be a multiple of the world size {R}")
+            tp = tokens // R
+            key = ("multi", tokens, x_host.dtype)
+            if getattr(self, "_host_key", None) != key:
+                self._host_key, self._xd = key, torch.empty(tokens, self.K, dtype=x_host.dtype, device=dev)
+            mine = self._xd[self.rank * tp:(self.rank + 1) * tp]
+            mine.copy_(x_host[self.rank * tp:(self.rank + 1) * tp], non_blocking=True)
+            dist.all_gather_into_tensor(self._xd, mine, group=self.group)
+            c = self.forward(self._xd)
+            for p in range(len(self.panels)):
+                q = p * R + self.rank
+                out_host[q * rp:(q + 1) * rp].copy_(c[q * rp:(q + 1) * rp], non_blocking=True)
+            return out_host
+        key = ("single", tokens, chunk_tokens, x_host.dtype)
+        if getattr(self, "_host_key", None) != key:
+            self._host_key = key
+            self._xd = [torch.empty(min(chunk_tokens, tokens), self.K, dtype=x_host.dtype, device=dev) for _ in range(2)]
+            self._cd = torch.empty(self.M_total, tokens, dtype=x_host.dtype, device=dev)
+            self._s_in, self._s_out = torch.cuda.Stream(dev), torch.cuda.Stream(dev)
+        s_in, s_out = self._s_in, self._s_out
+        s_in.wait_stream(cur)
+        s_out.wait_stream(cur)
+        computed = []
+        for i, t0 in enumerate(range(0, tokens, chunk_tokens)):
+            t1 = min(tokens, t0 + chunk_tokens)
+            xd = self._xd[i % 2][:t1 - t0]
+            with torch.cuda.stream(s_in):
+                if i >= 2:
+                    s_in.wait_event(computed[i - 2])  # the staging buffer's previous chunk has been multiplied
+                xd.copy_(x_host[t0:t1], non_blocking=True)
+                uploaded = torch.cuda.Event()
+                uploaded.record(s_in)
+            cur.wait_event(uploaded)
+            for p, panel in enumerate(self.panels):
+                self.matmul(panel, xd, self._cd[p * rp:(p + 1) * rp, t0:t1])
+            done = torch.cuda.Event()
+            done.record(cur)
+            computed.append(done)
+            with torch.cuda.stream(s_out):
+                s_out.wait_event(done)
+                ops.copy_2d_async(out_host[:, t0:t1], self._cd[:, t0:t1], s_out)
+        cur.wait_stream(s_out)
+        cur.wait_stream(s_in)
+        return out_host
+
 
 def _default_matmul_rows(gnm, x2d, out_rows):
     from . import _native as nat
