@@ -272,7 +272,7 @@ class RowShardedNMMatmul:
 
     __call__ = forward
 
-    def forward_host(self, x_host, out_host, chunk_tokens=4096):
+    def forward_host(self, x_host, out_host, chunk_tokens=2048):
         """The same product with operands in pinned host memory: ``x_host`` [tokens, K] in, ``out_host`` [M, tokens] out.
 
         One rank: the token axis is cut into chunks and three streams overlap the upload of chunk i+1, the matmul of

@@ -69,3 +69,32 @@ def test_cpu_tensors_are_rejected_loudly():
     import sten_b200 as sten
     with pytest.raises(RuntimeError, match="CUDA"):
         sten.GroupedNMTensor.from_dense(torch.randn(8, 12), 2, 4, sparse_dim=0, group_size=2, group_dim=1)
+
+
+def test_kernel_choice_queries_are_pure_host_arithmetic():
+    """Which variant a call takes decides what it reads (packed copy or val / idx) and how much workspace it needs."""
+    L = nat.lib()
+    BF, F32 = nat.NMG_BF16, nat.NMG_F32
+    TM, KM = nat.NMG_ACT_TOKEN_MAJOR, nat.NMG_ACT_K_MAJOR
+    AUTO, SIMT, TENSOR = nat.NMG_ALGO_AUTO, nat.NMG_ALGO_SIMT, nat.NMG_ALGO_TENSOR
+    # fused tensor-core kernel below 1024 tokens reads the packed copy; the two-pass variant above does not
+    assert L.nmg_spmm_uses_packed(4096, 4096, 256, 2, 4, 16, BF, TM, AUTO, 0) == 1
+    assert L.nmg_spmm_uses_packed(4096, 4096, 2048, 2, 4, 16, BF, TM, AUTO, 0) == 0
+    # SIMT forward reads val / idx; SIMT transposed reads the packed copy
+    assert L.nmg_spmm_uses_packed(4096, 4096, 256, 2, 4, 16, BF, TM, SIMT, 0) == 0
+    assert L.nmg_spmm_uses_packed(4096, 4096, 256, 2, 4, 16, BF, KM, AUTO, 0) == 0
+    assert L.nmg_spmm_uses_packed(4096, 4096, 16, 2, 4, 16, F32, TM, AUTO, 1) == 1
+    assert L.nmg_spmm_uses_packed(4096, 4096, 4096, 2, 4, 16, F32, TM, AUTO, 1) == 0
+    # 3:6 has no fused kernel: the tensor-core path is always the two-pass variant
+    assert L.nmg_spmm_uses_packed(600, 600, 512, 3, 6, 4, BF, TM, TENSOR, 0) == 0
+    # the two-pass variant's workspace holds the expanded weight (M * K * 2 bytes; three planes + split activation in fp32)
+    ws = L.nmg_spmm_workspace_bytes(4096, 4096, 4096, 2, 4, 16, BF, TM, TENSOR, 0)
+    assert 4096 * 4096 * 2 <= ws <= 4096 * 4096 * 2 + 4096
+    ws32 = L.nmg_spmm_workspace_bytes(4096, 4096, 4096, 2, 4, 16, F32, TM, TENSOR, 0)
+    assert ws32 >= 6 * 4096 * 4096 * 2
+    # replicated output: argument validation happens before any CUDA call
+    one = ctypes.c_void_p(16)
+    outs = (ctypes.c_void_p * 1)(16)
+    assert L.nmg_spmm_replicated(one, one, 4096, 4096, 2, 4, 16, BF, one, 4096, 2048, None, outs, 0, 2048, None, 0, None) == 1
+    assert L.nmg_spmm_replicated(one, one, 4096, 4096, 2, 4, 16, BF, one, 4096, 100, None, outs, 1, 100, None, 0, None) == 2
+    assert L.nmg_memcpy_2d_async(None, 8, one, 8, 8, 1, None) == 1
