@@ -98,9 +98,9 @@ int nmg_pack(const void *val, const int16_t *idx, int64_t M, int64_t K, int n, i
  * workspace: device scratch of at least nmg_spmm_workspace_bytes(...) bytes, 256-byte aligned, owned by the
  * caller for the duration of the call (may be NULL when the query returns 0).
  * algo: NMG_ALGO_AUTO uses the tensor cores for token-major activations (16-bit rows must be 16-byte aligned) with at
- * least 64 tokens and 64 rows; the SIMT kernels otherwise.  Two tensor-core variants exist.  Below 1024 tokens, for
- * m in {4, 8, 16} and n <= 2, one fused kernel expands tiles of the packed copy inside the matmul.  From 1024 tokens
- * on, and for every other (n, m), the weight is first expanded into a transient dense 16-bit matrix in the workspace
+ * least 64 tokens and 64 rows; the SIMT kernels otherwise.  Two tensor-core variants exist.  Below 1536 tokens (256 for
+ * fp32), for m in {4, 8, 16} and n <= 2, one fused kernel expands tiles of the packed copy inside the matmul.  From
+ * there on, and for every other (n, m), the weight is first expanded into a transient dense 16-bit matrix in the workspace
  * (M * round_up(K, 8) * 2 bytes; three such planes for fp32) and multiplied by a persistent TMA-fed kernel; that
  * variant reads val / idx and ignores `packed`.  fp32 operands go through the tensor cores as exact three-way bf16
  * splits with promoted fp32 accumulation (relative error ~3.5e-6, independent of K); NMG_ALGO_SIMT forces plain fp32
@@ -133,9 +133,9 @@ int nmg_spmm_uses_packed(int64_t M, int64_t K, int64_t tokens, int n, int m, int
  * process (CUDA IPC or a symmetric-memory allocation), so that a row-sharded layer needs no all-gather: when every
  * rank's call has completed, every GPU holds the full C.  The caller synchronises the ranks afterwards (any
  * stream-ordered collective or barrier).  Operand conventions as nmg_spmm with NMG_ACT_TOKEN_MAJOR_OUT_ROWS; workspace
- * as nmg_spmm_workspace_bytes(..., NMG_ACT_TOKEN_MAJOR_OUT_ROWS, NMG_ALGO_TENSOR, 0).  Runs on the two-pass tensor-core
- * variant only: NMG_ERR_UNSUPPORTED below 1024 tokens or for unaligned 16-bit activation rows.  At most 8 buffers.
- * No counterpart in the reference, which has no multi-GPU path for this format. */
+ * of nmg_spmm_replicated_workspace_bytes(...) bytes.  Always runs on the two-pass tensor-core variant:
+ * NMG_ERR_UNSUPPORTED for unaligned 16-bit activation rows or a chunk that does not fit shared memory.  At most 8 buffers.  No counterpart in the reference, which has no multi-GPU path for this format. */
+size_t nmg_spmm_replicated_workspace_bytes(int64_t M, int64_t K, int64_t tokens, int n, int m, int g, int dtype);
 int nmg_spmm_replicated(const void *val, const int16_t *idx, int64_t M, int64_t K, int n, int m, int g, int dtype,
                         const void *act, int64_t ld_act, int64_t tokens, const void *bias, void *const *outs, int n_outs,
                         int64_t ld_out, void *workspace, size_t workspace_bytes, void *stream);

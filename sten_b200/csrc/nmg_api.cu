@@ -78,7 +78,7 @@ extern "C" size_t nmg_spmm_workspace_bytes(int64_t M, int64_t K, int64_t tokens,
 
 static int spmm_impl(const void *val, const int16_t *idx, const void *packed, int64_t M, int64_t K, int n, int m, int g, int dtype,
                      const void *act, int64_t ld_act, int64_t tokens, const void *bias, void *const *outs, int n_outs, int64_t ld_out,
-                     int layout, int algo, void *workspace, size_t workspace_bytes, void *stream) {
+                     int layout, int algo, void *workspace, size_t workspace_bytes, void *stream, bool force_dense = false) {
     Geo geo;
     int rc = make_geo(M, K, n, m, g, &geo);
     if (rc) return rc;
@@ -104,7 +104,7 @@ static int spmm_impl(const void *val, const int16_t *idx, const void *packed, in
         size_t left = workspace_bytes;
         const uint16_t *pat = nullptr;
         const void *nval = nullptr;
-        const bool dense = tc_use_dense(geo, dtype, tokens);
+        const bool dense = force_dense || tc_use_dense(geo, dtype, tokens);
         if (!dense && (rc = resolve_packed(geo, dtype, val, idx, packed, &ws, &left, &pat, &nval, st))) return rc;
         return tc_matmul(geo, dtype, false, dense, val, idx, pat, nval, act, ld_act, tokens, bias, outs, n_outs, ld_out, out_tm ? 1 : 0, ws, left, st);
     }
@@ -129,10 +129,16 @@ extern "C" int nmg_spmm_replicated(const void *val, const int16_t *idx, int64_t 
     Geo geo;
     int rc = make_geo(M, K, n, m, g, &geo);
     if (rc) return rc;
-    if (!tc_dense_supported(geo, dtype) || !tc_use_dense(geo, dtype, tokens))
-        NMG_FAIL(NMG_ERR_UNSUPPORTED, "the replicated-output matmul runs on the two-pass tensor-core variant only (>= 1024 tokens)");
+    if (!tc_dense_supported(geo, dtype))
+        NMG_FAIL(NMG_ERR_UNSUPPORTED, "the replicated-output matmul runs on the two-pass tensor-core variant, which this chunk size does not fit");
     return spmm_impl(val, idx, nullptr, M, K, n, m, g, dtype, act, ld_act, tokens, bias, outs, n_outs, ld_out, NMG_ACT_TOKEN_MAJOR_OUT_ROWS,
-                     NMG_ALGO_TENSOR, workspace, workspace_bytes, stream);
+                     NMG_ALGO_TENSOR, workspace, workspace_bytes, stream, true);
+}
+
+extern "C" size_t nmg_spmm_replicated_workspace_bytes(int64_t M, int64_t K, int64_t tokens, int n, int m, int g, int dtype) {
+    Geo geo;
+    if (make_geo(M, K, n, m, g, &geo) || tokens < 1 || n < 1 || !tc_dense_supported(geo, dtype)) return 0;
+    return tc_dense_workspace_bytes(geo, dtype, false) + tc_split_workspace_bytes(geo, dtype, false, tokens);
 }
 
 extern "C" int nmg_spmm_uses_packed(int64_t M, int64_t K, int64_t tokens, int n, int m, int g, int dtype, int layout,

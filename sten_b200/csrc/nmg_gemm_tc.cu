@@ -132,6 +132,7 @@ __global__ void __launch_bounds__(EXPAND_THREADS) expand_dense_kernel(const Expa
             // eight slots per thread: one 16-byte load of indices and N_ 16-byte (16-bit) or 2 N_ (fp32) loads of values,
             // all issued before the first use, so a whole item's global loads are in flight together
             constexpr int VL = N_ * (int)sizeof(T) / 2;  // 16-byte loads of values per 8 slots
+            const bool same_pattern = (g & 7) == 0;  // 8 consecutive slots then belong to one pattern
             for (int e8 = threadIdx.x * 8; e8 < total; e8 += EXPAND_THREADS * 8) {
                 const uint4 iv = __ldg(reinterpret_cast<const uint4 *>(isrc + e8));
                 uint4 vv[VL];
@@ -139,8 +140,23 @@ __global__ void __launch_bounds__(EXPAND_THREADS) expand_dense_kernel(const Expa
                 for (int u = 0; u < VL; u++) vv[u] = __ldg(reinterpret_cast<const uint4 *>(vsrc + (int64_t)e8 * N_) + u);
                 const int16_t *ci = reinterpret_cast<const int16_t *>(&iv);
                 const T *vals = reinterpret_cast<const T *>(vv);
+                const int j = e8 / cc, s0 = e8 - j * cc;  // cc is a multiple of 8: the 8 slots share the row-block
+                if (same_pattern) {
+                    const int8_t *o = ord + (s0 / g) * N_;
+                    int off[N_];  // element offset of slot value t inside the tile, before the column is added
 #pragma unroll
-                for (int u = 0; u < 8; u++) scatter(e8 + u, ci[u], vals + u * N_);
+                    for (int t = 0; t < N_; t++) off[t] = TR ? j * m + o[t] : (j * m + o[t]) * pitch;
+#pragma unroll
+                    for (int u = 0; u < 8; u++) {
+                        const int c = ci[u];
+                        if ((unsigned)c >= (unsigned)cc) continue;  // a malformed index is ignored, never dereferenced
+#pragma unroll
+                        for (int t = 0; t < N_; t++) tile[off[t] + (TR ? c * pitch : c)] = vals[u * N_ + t];
+                    }
+                } else {
+#pragma unroll
+                    for (int u = 0; u < 8; u++) scatter(e8 + u, ci[u], vals + u * N_);
+                }
             }
         }
         if (!vectorised)

@@ -890,7 +890,9 @@ bool tc_use_dense(const Geo &geo, int dtype, int64_t tokens) {
     if (!dense) return false;
     if (!fused) return true;
     if (forced == 0 || forced == 1) return forced == 1;
-    return tokens >= 1024;
+    // Measured crossover (4096^2 and 16384^2 weights): the fused kernel wins up to 1024 tokens, the two-pass variant
+    // from 2048 on; fp32 (six split products, so six in-kernel expansions per tile) prefers two passes from 256 tokens.
+    return tokens >= (dtype == NMG_F32 ? 256 : 1536);
 }
 
 // act: [tokens][ld_act] with the reduction axis contiguous (X for the forward, dY for the transposed product).

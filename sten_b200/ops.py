@@ -164,8 +164,7 @@ def spmm_replicated(val, idx, M, K, n, m, g, act, out_ptrs, ld_out, bias=None):
     L = nat.lib()
     ptrs = (ctypes.c_void_p * len(out_ptrs))(*[int(p) for p in out_ptrs])
     with torch.cuda.device(dev):
-        ws, nbytes = _workspace(L.nmg_spmm_workspace_bytes(M, K, tokens, n, m, g, code, nat.NMG_ACT_TOKEN_MAJOR_OUT_ROWS,
-                                                           nat.NMG_ALGO_TENSOR, 0), dev)
+        ws, nbytes = _workspace(L.nmg_spmm_replicated_workspace_bytes(M, K, tokens, n, m, g, code), dev)
         nat.check(L.nmg_spmm_replicated(val.data_ptr(), idx.data_ptr(), M, K, n, m, g, code, act.data_ptr(), ld_act, tokens,
                                         bias.data_ptr() if bias is not None else None, ptrs, len(out_ptrs), ld_out,
                                         ws.data_ptr() if ws is not None else None, nbytes, _stream(dev)))

@@ -77,7 +77,7 @@ def test_kernel_choice_queries_are_pure_host_arithmetic():
     BF, F32 = nat.NMG_BF16, nat.NMG_F32
     TM, KM = nat.NMG_ACT_TOKEN_MAJOR, nat.NMG_ACT_K_MAJOR
     AUTO, SIMT, TENSOR = nat.NMG_ALGO_AUTO, nat.NMG_ALGO_SIMT, nat.NMG_ALGO_TENSOR
-    # fused tensor-core kernel below 1024 tokens reads the packed copy; the two-pass variant above does not
+    # fused tensor-core kernel below 1536 tokens reads the packed copy; the two-pass variant above does not
     assert L.nmg_spmm_uses_packed(4096, 4096, 256, 2, 4, 16, BF, TM, AUTO, 0) == 1
     assert L.nmg_spmm_uses_packed(4096, 4096, 2048, 2, 4, 16, BF, TM, AUTO, 0) == 0
     # SIMT forward reads val / idx; SIMT transposed reads the packed copy
@@ -96,5 +96,6 @@ def test_kernel_choice_queries_are_pure_host_arithmetic():
     one = ctypes.c_void_p(16)
     outs = (ctypes.c_void_p * 1)(16)
     assert L.nmg_spmm_replicated(one, one, 4096, 4096, 2, 4, 16, BF, one, 4096, 2048, None, outs, 0, 2048, None, 0, None) == 1
-    assert L.nmg_spmm_replicated(one, one, 4096, 4096, 2, 4, 16, BF, one, 4096, 100, None, outs, 1, 100, None, 0, None) == 2
+    assert L.nmg_spmm_replicated(one, one, 4096, 4096, 2, 4, 16, BF, one, 4090, 32, None, outs, 1, 32, None, 0, None) == 1  # ld_act < K
+    assert L.nmg_spmm_replicated_workspace_bytes(4096, 4096, 100, 2, 4, 16, BF) >= 4096 * 4096 * 2
     assert L.nmg_memcpy_2d_async(None, 8, one, 8, 8, 1, None) == 1
