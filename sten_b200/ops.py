@@ -3,6 +3,7 @@
 torch is used for device memory (caching allocator), the current stream and nothing else; all arithmetic
 happens inside ``libnmg_b200.so``.
 """
+import functools
 import math
 
 import torch
@@ -106,11 +107,17 @@ def pack(val, idx, M, K, n, m, g):
     return buf
 
 
+@functools.lru_cache(maxsize=4096)
 def uses_packed(M, K, tokens, n, m, g, dtype, layout=nat.NMG_ACT_TOKEN_MAJOR, algo=nat.NMG_ALGO_AUTO, transposed=False):
     """Whether spmm (or spmm_t when `transposed`) would read the packed copy for this problem: the fused tensor-core
     kernel and the SIMT transposed kernel do; the two-pass tensor-core variant and the SIMT forward kernel do not."""
     code = {torch.float32: nat.NMG_F32, torch.float16: nat.NMG_F16, torch.bfloat16: nat.NMG_BF16}[dtype]
     return bool(nat.lib().nmg_spmm_uses_packed(M, K, tokens, n, m, g, code, layout, algo, 1 if transposed else 0))
+
+
+@functools.lru_cache(maxsize=4096)
+def _spmm_workspace_bytes(M, K, tokens, n, m, g, code, layout, algo, have_packed):
+    return nat.lib().nmg_spmm_workspace_bytes(M, K, tokens, n, m, g, code, layout, algo, have_packed)
 
 
 def spmm(val, idx, M, K, n, m, g, act, bias=None, layout=nat.NMG_ACT_TOKEN_MAJOR, algo=nat.NMG_ALGO_AUTO, out=None,
@@ -136,8 +143,7 @@ def spmm(val, idx, M, K, n, m, g, act, bias=None, layout=nat.NMG_ACT_TOKEN_MAJOR
         bias = bias.contiguous()
     L = nat.lib()
     with torch.cuda.device(dev):
-        ws, nbytes = _workspace(L.nmg_spmm_workspace_bytes(M, K, tokens, n, m, g, code, layout, algo,
-                                                           1 if packed is not None else 0), dev)
+        ws, nbytes = _workspace(_spmm_workspace_bytes(M, K, tokens, n, m, g, code, layout, algo, 1 if packed is not None else 0), dev)
         nat.check(L.nmg_spmm(val.data_ptr(), idx.data_ptr(), packed.data_ptr() if packed is not None else None, M, K, n,
                              m, g, code, act.data_ptr(), ld_act, tokens,
                              bias.data_ptr() if bias is not None else None, out.data_ptr(), (out.shape[1] if out.is_contiguous() else out.stride(0)), layout, algo,
