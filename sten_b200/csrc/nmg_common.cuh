@@ -136,12 +136,24 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t *bar, uint32_t parity) {
         : "memory");
     return ok != 0;
 }
-// Bounded wait: gives up after `limit` polls (each poll may itself sleep for a hardware-defined slice),
-// records `code` in the status word and reports failure so the caller can leave the kernel.
-constexpr uint32_t kWaitLimit = 1u << 22;
+// Bounded wait: gives up after about two seconds of wall-clock time (%globaltimer, checked every 64 polls; each poll
+// may itself sleep for a hardware-defined slice), records `code` in the status word and reports failure so the caller
+// can leave the kernel.  Two seconds is far above any healthy wait of these kernels and keeps a lost hand-off from
+// occupying the GPU.
+constexpr uint64_t kWaitLimitNs = 2000000000ull;
+__device__ __forceinline__ uint64_t global_timer_ns() {
+    uint64_t t;
+    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+    return t;
+}
 __device__ __forceinline__ bool mbar_wait_bounded(uint64_t *bar, uint32_t parity, int *status, int code) {
-    for (uint32_t i = 0; i < kWaitLimit; i++)
-        if (mbar_try_wait(bar, parity)) return true;
+    if (mbar_try_wait(bar, parity)) return true;
+    const uint64_t t0 = global_timer_ns();
+    for (;;) {
+        for (int i = 0; i < 64; i++)
+            if (mbar_try_wait(bar, parity)) return true;
+        if (global_timer_ns() - t0 > kWaitLimitNs) break;
+    }
     if (status) atomicExch(status, code);
     return false;
 }

@@ -10,7 +10,7 @@
 //   expand_dense_kernel   (val, idx) -> dense W [M][K] (forward) or W^T [K][M] (transposed product), 16-bit; fp32
 //                         weights become three bf16 planes (exact hi / mid / lo split).  Works for every (n, m, g).
 //   gemm_tc_kernel        persistent, one CTA per SM.  Warp 0 issues the TMA loads of both operands, warp 1 the
-//                         MMAs (128 x 256 x 16, fp32 accumulators in TMEM), warps 2..5 drain accumulators.  16-bit
+//                         MMAs (128 x 256 x 16, fp32 accumulators in TMEM), warps 2..9 drain accumulators.  16-bit
 //                         mode double-buffers the accumulator (2 x 256 TMEM columns) so that the drain of one tile
 //                         overlaps the MMAs of the next; fp32 mode uses the second half for the running sum into which
 //                         the tensor core's partial tile is promoted every TC_CHUNK_KB k-blocks.
@@ -207,7 +207,8 @@ static int expand_rows_per_item(const Geo &geo, size_t es, bool tr) {
 // =========================================================================================================
 // Dense-operand matmul
 // =========================================================================================================
-constexpr int GEMM_THREADS = 32 * 6;  // TMA warp, MMA warp, four drain warps (one per TMEM lane quarter)
+constexpr int GEMM_DRAIN_WARPS = 8;   // two per TMEM lane quarter, each takes half of the accumulator's columns
+constexpr int GEMM_THREADS = 32 * (2 + GEMM_DRAIN_WARPS);  // TMA warp, MMA warp, drain warps
 constexpr int GEMM_STAGE_BYTES = TC_A_BYTES + TC_B_BYTES;
 
 constexpr int GEMM_MAX_OUTS = 8;
@@ -219,9 +220,10 @@ struct GemmParams {
     int out_token_major;
     int out_staged;    // feature-major output whose rows are 16-byte aligned: go through the staging tile
     int tiles_f, tiles_t;
+    int debug;         // measurement aid (NMG_TC_DEBUG): bit 0 skips the epilogue's global stores, bit 1 its TMEM reads too; results are garbage
     int *status;
 };
-constexpr int GEMM_STAGING_BYTES = 4 * 4096;  // per drain warp: 32 feature rows x 128 bytes
+constexpr int GEMM_STAGING_BYTES = GEMM_DRAIN_WARPS * 4096;  // per drain warp: 32 feature rows x 128 bytes
 
 struct GemmMaps {
     CUtensorMap a[3];  // weight planes, box 64 x 128, 128-byte swizzle
@@ -261,7 +263,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_tc_kernel(const GemmPara
         }
         for (int b = 0; b < 2; b++) {
             mbar_init(&acc_full[b], 1);
-            mbar_init(&acc_free[b], 4);  // lane 0 of each drain warp
+            mbar_init(&acc_free[b], GEMM_DRAIN_WARPS);  // lane 0 of each drain warp
         }
         mbar_fence_init();
     }
@@ -340,6 +342,8 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_tc_kernel(const GemmPara
         constexpr int GROUP_TOK = 128 / (int)sizeof(T);        // tokens per staged row: 64 (16-bit) or 32 (fp32)
         constexpr int GROUP_SLICES = GROUP_TOK / 32;           // 32-column TMEM slices per staged group
         const int q = warp & 3;  // TMEM lane quarter this warp may access
+        constexpr int SLICES = (TC_BN / 32) / (GEMM_DRAIN_WARPS / 4);  // 32-column slices per warp
+        const int sl0 = ((warp - 2) >> 2) * SLICES;                    // this warp's first slice
         const uint32_t lane_base = tmem_base + ((uint32_t)(q * 32) << 16);
         char *stage_w = staging + (warp - 2) * 4096;
         int unit = 0;
@@ -355,9 +359,16 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_tc_kernel(const GemmPara
                 if (!(ok = mbar_wait_bounded(&acc_full[b], (uint32_t)(use & 1), prm.status, 25))) break;
                 tc_fence_after();
                 const bool last = c == nchunks - 1;
-                for (int sl = 0; sl < TC_BN / 32; sl++) {
-                    uint32_t r[32];
-                    tmem_ld32(lane_base + (uint32_t)(b * TC_ACC_COLS + sl * 32), r);
+                // handle(sl, r): slice sl of the unit is in registers r (this lane's feature row, 32 tokens)
+                auto handle = [&](int sl, uint32_t (&r)[32]) {
+                    if ((prm.debug & 1) && last) {
+                        if (sl == sl0 + SLICES - 1) {
+                            tc_fence_before();
+                            __syncwarp();
+                            if (lane == 0) mbar_arrive(&acc_free[b]);
+                        }
+                        return;
+                    }
                     if (SPLIT && c > 0) {
                         uint32_t run[32];
                         tmem_ld32(lane_base + (uint32_t)(TC_ACC_COLS + sl * 32), run);
@@ -366,16 +377,23 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_tc_kernel(const GemmPara
                     }
                     if (!last) {
                         tmem_st32(lane_base + (uint32_t)(TC_ACC_COLS + sl * 32), r);
-                        continue;
+                        return;
                     }
-                    if (sl == TC_BN / 32 - 1) {  // every TMEM read of this unit is done: the issuer may reuse the accumulator
+                    if (sl == sl0 + SLICES - 1) {  // this warp's TMEM reads of the unit are done: the issuer may reuse the accumulator once all warps say so
                         tc_fence_before();
                         __syncwarp();
                         if (lane == 0) mbar_arrive(&acc_free[b]);
                     }
                     const int64_t tokc = (int64_t)tok0 + sl * 32;
                     if (!prm.out_staged) {
-                        if (tokc >= prm.ntok || !feat_ok) continue;
+                        if (tokc >= prm.ntok || !feat_ok) return;
+                        if (prm.out_token_major && prm.n_out == 1 && tokc + 32 <= prm.ntok) {
+                            // full slice of the F.linear layout: one conversion, one pointer step and one store per element
+                            T *p = static_cast<T *>(prm.outs[0]) + tokc * prm.ld_out + feat;
+#pragma unroll
+                            for (int j = 0; j < 32; j++, p += prm.ld_out) *p = DT<T>::from_f32(__uint_as_float(r[j]) + bias);
+                            return;
+                        }
                         for (int d = 0; d < prm.n_out; d++) {
                             T *out = static_cast<T *>(prm.outs[d]);
 #pragma unroll
@@ -388,7 +406,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_tc_kernel(const GemmPara
                                 }
                             }
                         }
-                        continue;
+                        return;
                     }
                     // registers -> staging row `lane`
                     constexpr int CH = 32 / CHUNK_TOK;  // chunks per slice: 4 (16-bit) or 8 (fp32)
@@ -402,16 +420,13 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_tc_kernel(const GemmPara
                         } else {
                             uint32_t h[4];
 #pragma unroll
-                            for (int k = 0; k < 4; k++) {
-                                const T lo = DT<T>::from_f32(__uint_as_float(r[8 * v + 2 * k]) + bias);
-                                const T hi = DT<T>::from_f32(__uint_as_float(r[8 * v + 2 * k + 1]) + bias);
-                                h[k] = (uint32_t)bits16<T>(lo) | ((uint32_t)bits16<T>(hi) << 16);
-                            }
+                            for (int k = 0; k < 4; k++)  // one packed conversion per pair
+                                h[k] = pack2<T>(__uint_as_float(r[8 * v + 2 * k]) + bias, __uint_as_float(r[8 * v + 2 * k + 1]) + bias);
                             w = make_uint4(h[0], h[1], h[2], h[3]);
                         }
                         *reinterpret_cast<uint4 *>(stage_w + lane * 128 + (((ch0 + v) ^ (lane & 7)) << 4)) = w;
                     }
-                    if ((sl % GROUP_SLICES) != GROUP_SLICES - 1) continue;
+                    if ((sl % GROUP_SLICES) != GROUP_SLICES - 1) return;
                     __syncwarp();
                     // staging -> every destination: lane handles chunk (lane & 7) of rows (lane >> 3) + 4 i
                     const int64_t tokg = (int64_t)tok0 + (sl / GROUP_SLICES) * GROUP_TOK + (lane & 7) * CHUNK_TOK;
@@ -432,6 +447,21 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_tc_kernel(const GemmPara
                         }
                     }
                     __syncwarp();  // the staging rows are free for the next group
+                };
+                // TMEM reads are software-pipelined: the load of the next slice is in flight while this one is converted
+                // and stored; tmem_ld_fence ties the wait to the registers so no use can move above it.
+                uint32_t ra[32], rb[32];
+                const uint32_t acc_addr = lane_base + (uint32_t)(b * TC_ACC_COLS);
+                const bool skip_ld = (prm.debug & 2) != 0;
+                if (!skip_ld) tmem_ld32_issue(acc_addr + (uint32_t)(sl0 * 32), ra);
+#pragma unroll 1
+                for (int sl = sl0; sl < sl0 + SLICES; sl += 2) {
+                    tmem_ld_fence(ra);
+                    if (!skip_ld) tmem_ld32_issue(acc_addr + (uint32_t)((sl + 1) * 32), rb);
+                    handle(sl, ra);
+                    tmem_ld_fence(rb);
+                    if (sl + 2 < sl0 + SLICES && !skip_ld) tmem_ld32_issue(acc_addr + (uint32_t)((sl + 2) * 32), ra);
+                    handle(sl + 1, rb);
                 }
                 if (!last) {  // promotion finished: hand the accumulator back
                     tc_fence_before();
@@ -551,6 +581,8 @@ int tc_dense_matmul(const Geo &geo, int dtype, bool transposed, const void *val,
     gp.tiles_f = (int)((rows + TC_BM - 1) / TC_BM);
     gp.tiles_t = (int)((tokens + TC_BN - 1) / TC_BN);
     gp.status = status;
+    static const int debug_flags = [] { const char *e = getenv("NMG_TC_DEBUG"); return e ? atoi(e) : 0; }();
+    gp.debug = debug_flags;
     if (dtype == NMG_F16) return gemm_launch<__half>(gp, maps, st);
     if (dtype == NMG_BF16) return gemm_launch<__nv_bfloat16>(gp, maps, st);
     return gemm_launch<float>(gp, maps, st);

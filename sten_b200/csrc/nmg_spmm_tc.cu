@@ -506,8 +506,13 @@ __device__ __forceinline__ bool mbar_try_wait_cluster(uint64_t *bar, uint32_t pa
     return ok != 0;
 }
 __device__ __forceinline__ bool mbar_wait_cluster_bounded(uint64_t *bar, uint32_t parity, int *status, int code) {
-    for (uint32_t i = 0; i < kWaitLimit; i++)
-        if (mbar_try_wait_cluster(bar, parity)) return true;
+    if (mbar_try_wait_cluster(bar, parity)) return true;
+    const uint64_t t0 = global_timer_ns();
+    for (;;) {
+        for (int i = 0; i < 64; i++)
+            if (mbar_try_wait_cluster(bar, parity)) return true;
+        if (global_timer_ns() - t0 > kWaitLimitNs) break;
+    }
     if (status) atomicExch(status, code);
     return false;
 }
