@@ -45,6 +45,9 @@ SWEEP = [(1, 4), (2, 4), (1, 8), (2, 8), (1, 16)]
 SW_M = SW_K = SW_TOK = 4096
 SH_M = SH_K = SH_TOK = 16384
 SH_N, SH_MM = 2, 8
+# DRAM traffic of one full-size call of the default workload (expansion pass 0.683 GB + matmul kernel 9.363 GB), from one
+# ncu capture on a B200; reported in roofline.traffic at N = 1
+NCU_DRAM_BYTES_PER_CALL = 10.05e9
 # bounded CPU sample of the sharded workload: one of eight row shards x 1024 tokens
 CPU_ROWS, CPU_TOK = 2048, 1024
 
@@ -376,7 +379,10 @@ def run_ours(args):
                         "kernel": "gemm_tc_kernel<bf16> (persistent TMA-fed tcgen05 matmul) + expand_dense_kernel<bf16> (weight expansion pass), timed together",
                         "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak,
                         "peak_source": f"{peaks_src} bf16_tflops (burst: the call is timed alone), of measured",
-                        "traffic": None, "ms_per_launch": kms, "algorithmic_flops_per_launch": alg,
+                        "traffic": NCU_DRAM_BYTES_PER_CALL if world == 1 else None,
+                        "traffic_source": "ncu dram__bytes_read.sum + dram__bytes_write.sum of both kernels of one full-size call "
+                                          "(profiles/gemm_tc_two_pass_2-8_16384x16384_bf16_launches.txt); operands + result are 1.7 GB",
+                        "ms_per_launch": kms, "algorithmic_flops_per_launch": alg,
                         "executed_tflops": achieved * m / n, "executed_frac": achieved * m / n / peak,
                         "ceiling_frac": n / m, "frac_of_ceiling": achieved * m / n / peak,
                         "note": "algorithmic = useful (non-zero) flops 2*M*K*tokens*n/m; the n:m blocks lie along the output-row axis, "
