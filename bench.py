@@ -138,14 +138,45 @@ def run_reference(args):
 
 # ------------------------------------------------------------------------------------------------ GPU side
 class ClockSampler:
+    """SM clock and clock-event reasons of one GPU, polled through NVML every 5 ms while the timed region runs (read-only
+    queries; falls back to `nvidia-smi -lms 100` when the NVML bindings are missing)."""
     QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
              "clocks_event_reasons.sw_power_cap")
+    REASON_BITS = {"sw_power_cap": 0x4, "hw_slowdown": 0x8, "sw_thermal_slowdown": 0x20, "hw_thermal_slowdown": 0x40}
 
     def __init__(self, index):
         self.index, self.rows, self.proc = index, [], None
+        self.samples, self.reasons, self.max_mhz = [], set(), None
+        self._stop = threading.Event()
+        self._thread = None
+
+    def _poll_nvml(self, nv, handle):
+        get_reasons = getattr(nv, "nvmlDeviceGetCurrentClocksEventReasons", None) or nv.nvmlDeviceGetCurrentClocksThrottleReasons
+        while not self._stop.is_set():
+            try:
+                self.samples.append(float(nv.nvmlDeviceGetClockInfo(handle, nv.NVML_CLOCK_SM)))
+                mask = int(get_reasons(handle))
+                for name, bit in self.REASON_BITS.items():
+                    if mask & bit:
+                        self.reasons.add(name)
+            except Exception:  # noqa: BLE001 - a failed read is a missing sample
+                pass
+            self._stop.wait(0.005)
 
     def start(self):
+        try:
+            import pynvml as nv
+            nv.nvmlInit()
+            visible = os.environ.get("CUDA_VISIBLE_DEVICES")
+            phys = int(visible.split(",")[self.index]) if visible and visible.replace(",", "").isdigit() else self.index
+            handle = nv.nvmlDeviceGetHandleByIndex(phys)
+            self.max_mhz = float(nv.nvmlDeviceGetMaxClockInfo(handle, nv.NVML_CLOCK_SM))
+            self._thread = threading.Thread(target=self._poll_nvml, args=(nv, handle), daemon=True)
+            self._thread.start()
+            return
+        except Exception:  # noqa: BLE001 - any NVML problem selects the nvidia-smi route
+            self._thread = None
         try:
             self.proc = subprocess.Popen(["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.QUERY}",
                                           "--format=csv,noheader,nounits", "-lms", "100"],
@@ -159,6 +190,12 @@ class ClockSampler:
             self.rows.append([c.strip() for c in line.split(",")])
 
     def stop(self):
+        if self._thread is not None:
+            self._stop.set()
+            self._thread.join(timeout=2)
+            busy = sorted(self.samples)
+            return {"sm_mhz": busy[len(busy) // 2] if busy else None, "sm_max_mhz": self.max_mhz,
+                    "reasons": sorted(self.reasons), "samples": len(busy), "source": "NVML, 5 ms period"}
         if self.proc is not None:
             self.proc.terminate()
             try:
@@ -178,7 +215,7 @@ class ClockSampler:
                 continue
         busy = sorted(sm[len(sm) // 4:]) if sm else []  # the first samples precede the load
         return {"sm_mhz": busy[len(busy) // 2] if busy else None, "sm_max_mhz": max(mx) if mx else None,
-                "reasons": sorted(reasons), "samples": len(sm)}
+                "reasons": sorted(reasons), "samples": len(sm), "source": "nvidia-smi -lms 100"}
 
 
 def timed_loop(fn, steps, barrier, torch, dist, world, dev):
@@ -349,11 +386,11 @@ def run_ours(args):
         h2d, d2h = x_host.numel() * 4, sum(y.numel() * 4 for y in y_hosts)
         dtype_name, scaling = "f32", "weak"
 
-    for _ in range(args.warmup):
-        step()
     sampler = ClockSampler(local)
     if rank == 0:
-        sampler.start()
+        sampler.start()  # sampled from the warm-up steps (same kernels, same load) to the end of the end-to-end leg
+    for _ in range(args.warmup):
+        step()
     ms_per_step = timed_loop(step, args.steps, barrier, torch, dist, world, dev)
     value = total_flops / (ms_per_step * 1e-3) / 1e9
 

@@ -277,28 +277,55 @@ class RowShardedNMMatmul:
 
         One rank: the token axis is cut into chunks and three streams overlap the upload of chunk i+1, the matmul of
         chunk i and the (pitched) download of chunk i-1, so the step costs about one PCIe direction instead of
-        upload + matmul + download.  Several ranks: every rank uploads 1/R of the tokens and the activation is
-        completed by an all-gather over NVLink (R PCIe links work in parallel), the matmul exchanges its output through
-        peer stores or all-gathers as configured, and every rank downloads only the rows it computed into its
-        ``out_host``.  Returns ``out_host``; the copies are complete when the current stream is."""
+        upload + matmul + download.  Several ranks: the same pipeline, but every rank uploads 1/R of each chunk's tokens,
+        the chunk is completed by an all-gather over NVLink (R PCIe links work in parallel), and every rank downloads
+        only the rows it computed into its ``out_host`` (no output exchange between GPUs is needed for a host result).
+        Returns ``out_host``; the copies are complete when the current stream is."""
         tokens = x_host.shape[0]
         dev = self.panels[0].val.device
         cur = torch.cuda.current_stream(dev)
         rp, R = self.rows_per_panel, self.world
         if R > 1:
-            if tokens % R:
-                raise ValueError(f"tokens={tokens} must be a multiple of the world size {R}")
-            tp = tokens // R
-            key = ("multi", tokens, x_host.dtype)
+            # Token chunks; per chunk: upload this rank's 1/R of the chunk's tokens, complete the chunk over NVLink
+            # (all-gather), multiply this rank's weight rows with it, download those rows' column block.  The result goes
+            # to the host by rows, so no exchange of output slices between GPUs is needed here.
+            chunk = min(chunk_tokens * 2, tokens)
+            if tokens % R or chunk % R or tokens % chunk:
+                raise ValueError(f"tokens={tokens} and the chunk of {chunk} tokens must be multiples of the world size {R}, and the chunk must divide tokens")
+            key = ("multi", tokens, chunk, x_host.dtype)
             if getattr(self, "_host_key", None) != key:
-                self._host_key, self._xd = key, torch.empty(tokens, self.K, dtype=x_host.dtype, device=dev)
-            mine = self._xd[self.rank * tp:(self.rank + 1) * tp]
-            mine.copy_(x_host[self.rank * tp:(self.rank + 1) * tp], non_blocking=True)
-            dist.all_gather_into_tensor(self._xd, mine, group=self.group)
-            c = self.forward(self._xd)
-            for p in range(len(self.panels)):
-                q = p * R + self.rank
-                out_host[q * rp:(q + 1) * rp].copy_(c[q * rp:(q + 1) * rp], non_blocking=True)
+                self._host_key = key
+                self._xd = [torch.empty(chunk, self.K, dtype=x_host.dtype, device=dev) for _ in range(2)]
+                self._cd = torch.empty(len(self.panels) * rp, tokens, dtype=x_host.dtype, device=dev)  # this rank's rows only
+                self._s_in, self._s_out = torch.cuda.Stream(dev), torch.cuda.Stream(dev)
+            s_in, s_out = self._s_in, self._s_out
+            s_in.wait_stream(cur)
+            s_out.wait_stream(cur)
+            share = chunk // R
+            computed = []
+            for i, t0 in enumerate(range(0, tokens, chunk)):
+                xd = self._xd[i % 2]
+                mine = xd[self.rank * share:(self.rank + 1) * share]
+                with torch.cuda.stream(s_in):
+                    if i >= 2:
+                        s_in.wait_event(computed[i - 2])
+                    mine.copy_(x_host[t0 + self.rank * share:t0 + (self.rank + 1) * share], non_blocking=True)
+                    uploaded = torch.cuda.Event()
+                    uploaded.record(s_in)
+                cur.wait_event(uploaded)
+                dist.all_gather_into_tensor(xd, mine, group=self.group)
+                for p, panel in enumerate(self.panels):
+                    _default_matmul_rows(panel, xd, self._cd[p * rp:(p + 1) * rp, t0:t0 + chunk])
+                done = torch.cuda.Event()
+                done.record(cur)
+                computed.append(done)
+                with torch.cuda.stream(s_out):
+                    s_out.wait_event(done)
+                    for p in range(len(self.panels)):
+                        q = p * R + self.rank
+                        ops.copy_2d_async(out_host[q * rp:(q + 1) * rp, t0:t0 + chunk], self._cd[p * rp:(p + 1) * rp, t0:t0 + chunk], s_out)
+            cur.wait_stream(s_out)
+            cur.wait_stream(s_in)
             return out_host
         key = ("single", tokens, chunk_tokens, x_host.dtype)
         if getattr(self, "_host_key", None) != key:
