@@ -102,6 +102,9 @@ __global__ void __launch_bounds__(EXPAND_THREADS) expand_dense_kernel(const Expa
     const int lines = TR ? cc : R * m;
     T *tile = reinterpret_cast<T *>(smem);                                  // [lines][pitch]
     int8_t *ord = reinterpret_cast<int8_t *>(tile + (size_t)lines * pitch);  // [C][n]
+    // The matmul kernel that follows is launched with programmatic stream serialization: it may become resident and run
+    // its prologue while this grid drains, and reads nothing this grid writes before its griddepcontrol.wait.
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     for (int i = threadIdx.x; i < prm.C * n; i += EXPAND_THREADS) ord[i] = prm.order[i];
     for (int i = threadIdx.x; i < lines * pitch; i += EXPAND_THREADS) tile[i] = DT<T>::from_f32(0.f);
 
@@ -285,6 +288,9 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_tc_kernel(const GemmPara
         if (lane == 0) {
             int it = 0;
             bool ok = true;
+            // Everything this kernel reads that an earlier kernel of the stream wrote (the expanded weight, the
+            // activations) arrives through the loads below: wait here for the preceding grid to complete and flush.
+            asm volatile("griddepcontrol.wait;" ::: "memory");
             for (int ti = 0; ti < my_tiles && ok; ti++) {
                 int feat0, tok0;
                 tile_origin(ti, feat0, tok0);
@@ -519,8 +525,17 @@ template <typename T> static int gemm_launch(const GemmParams &p, const GemmMaps
     const int64_t tiles = (int64_t)p.tiles_f * p.tiles_t;
     if (tiles > 0x3fffffff) NMG_FAIL(NMG_ERR_UNSUPPORTED, "too many output tiles for one launch");
     NMG_CUDA(cudaFuncSetAttribute(gemm_tc_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    gemm_tc_kernel<T><<<(unsigned)(tiles < sms ? tiles : sms), GEMM_THREADS, smem, st>>>(p, maps);  // persistent
-    NMG_CUDA(cudaGetLastError());
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)(tiles < sms ? tiles : sms));  // persistent
+    cfg.blockDim = dim3(GEMM_THREADS);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;  // overlap the prologue with the expansion pass's tail
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    NMG_CUDA(cudaLaunchKernelEx(&cfg, gemm_tc_kernel<T>, p, maps));
     return NMG_OK;
 }
 
