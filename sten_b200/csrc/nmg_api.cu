@@ -70,7 +70,8 @@ extern "C" size_t nmg_spmm_workspace_bytes(int64_t M, int64_t K, int64_t tokens,
     size_t tensor = 0;
     if (algo != NMG_ALGO_SIMT && (tc_supported(geo, dtype) || tc_dense_supported(geo, dtype)) && layout != NMG_ACT_K_MAJOR)
         tensor = (tc_use_dense(geo, dtype, tokens) ? tc_dense_workspace_bytes(geo, dtype, false)
-                                                   : (have_packed ? 0 : natural_bytes(geo, dtype, nullptr) + 512)) +
+                                                   : (have_packed ? 0 : natural_bytes(geo, dtype, nullptr) + 512) +
+                                                         tc_ksplit_workspace_bytes(geo, dtype, false, tokens)) +
                  tc_split_workspace_bytes(geo, dtype, false, tokens);
     if (algo == NMG_ALGO_TENSOR) return tensor;
     return simt > tensor ? simt : tensor;  // AUTO may take either path depending on operand alignment
@@ -161,7 +162,8 @@ extern "C" size_t nmg_spmm_t_workspace_bytes(int64_t M, int64_t K, int64_t token
     const size_t simt = algo != NMG_ALGO_TENSOR ? pack + simt_bwd_workspace_bytes(geo, tokens, dtype) + 256 : 0;
     size_t tensor = 0;
     if (algo != NMG_ALGO_SIMT && (tc_supported(geo, dtype) || tc_dense_supported(geo, dtype)))
-        tensor = (tc_use_dense(geo, dtype, tokens) ? tc_dense_workspace_bytes(geo, dtype, true) : pack) +
+        tensor = (tc_use_dense(geo, dtype, tokens) ? tc_dense_workspace_bytes(geo, dtype, true)
+                                                   : pack + tc_ksplit_workspace_bytes(geo, dtype, true, tokens)) +
                  tc_split_workspace_bytes(geo, dtype, true, tokens);
     return simt > tensor ? simt : tensor;
 }

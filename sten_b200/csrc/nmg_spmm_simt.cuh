@@ -43,6 +43,9 @@ bool tc_dense_supported(const Geo &geo, int dtype);  // two-pass variant
 bool tc_use_dense(const Geo &geo, int dtype, int64_t tokens);
 size_t tc_split_workspace_bytes(const Geo &geo, int dtype, bool transposed, int64_t tokens);
 size_t tc_dense_workspace_bytes(const Geo &geo, int dtype, bool transposed);
+// fused kernel with few output tiles: the reduction axis is cut over tc_ksplit CTAs per tile, fp32 partial tiles in `ws`
+int tc_ksplit(const Geo &geo, int dtype, bool transposed, int64_t tokens);
+size_t tc_ksplit_workspace_bytes(const Geo &geo, int dtype, bool transposed, int64_t tokens);
 // outs / n_outs: the result goes to every listed buffer (same shape and pitch); more than one needs `dense`.
 int tc_matmul(const Geo &geo, int dtype, bool transposed, bool dense, const void *val, const int16_t *idx, const uint16_t *pat,
               const void *nval, const void *act, int64_t ld_act, int64_t tokens, const void *bias, void *const *outs, int n_outs,

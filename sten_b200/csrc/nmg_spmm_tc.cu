@@ -33,6 +33,9 @@ struct TcParams {
     int64_t ntok, ld_out, Kpn, nb;
     int out_token_major;  // 1: out[token][feature], 0: out[feature][token]
     int tiles_f, tiles_t; // output tiles along features / tokens
+    int ksplit;           // > 1: the reduction axis is cut into ksplit ranges, one CTA each; fp32 partial tiles go to `partial`
+    float *partial;       // [ksplit][tiles_f * 128][ld_partial] fp32, feature-major
+    int64_t ld_partial;
     int *status;
     int debug;            // measurement aid (NMG_TC_DEBUG): bit 0 skips the expansion stores, bit 1 the TMA loads; results are garbage
 };
@@ -225,13 +228,20 @@ spmm_tc_kernel(const TcParams prm, const __grid_constant__ CUtensorMap tmap0, co
     uint16_t *sel = reinterpret_cast<uint16_t *>(misc + 128);  // [C][M_/2] PRMT selectors, 16-byte aligned
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    // Few output tiles (few tokens): the grid is ksplit x tiles and every CTA takes one range of the reduction axis, so
+    // that the compressed weight streams from HBM through all SMs; a second kernel adds the partial tiles.
+    const int ntiles = prm.tiles_f * prm.tiles_t;
+    const int split = (int)blockIdx.x / ntiles;
     int tile_f, tile_t;
-    tile_of_cta((int)blockIdx.x, prm.tiles_f, prm.tiles_t, tile_f, tile_t);
+    tile_of_cta((int)blockIdx.x - split * ntiles, prm.tiles_f, prm.tiles_t, tile_f, tile_t);
     const int64_t tok0 = (int64_t)tile_t * TC_BN;
     const int64_t feat0 = (int64_t)tile_f * TC_BM;
     // 32-bit loop arithmetic throughout: the single MMA-issuing thread must stay ahead of the tensor core, and a
     // 64-bit division per iteration on that thread is enough to make issue the bottleneck.
-    const int nkb = (int)((prm.red + TC_BK - 1) / TC_BK) * TERMS;   // iterations: k-blocks x split terms (term fastest)
+    const int nkb_all = (int)((prm.red + TC_BK - 1) / TC_BK) * TERMS;  // iterations: k-blocks x split terms (term fastest)
+    const int kb_per = (nkb_all + prm.ksplit - 1) / prm.ksplit;
+    const int kb_base = split * kb_per;                                 // this CTA's first iteration (0 unless ksplit > 1)
+    const int nkb = (nkb_all < kb_base + kb_per ? nkb_all : kb_base + kb_per) - kb_base;  // >= 1 by the host's choice of ksplit
     const int chunk_it = SPLIT ? TC_CHUNK_KB * TERMS : nkb;          // iterations per accumulation chunk
     const int nchunks = (nkb + chunk_it - 1) / chunk_it;
 
@@ -317,6 +327,12 @@ spmm_tc_kernel(const TcParams prm, const __grid_constant__ CUtensorMap tmap0, co
             uint32_t r[32];
             tmem_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(sl * 32), r);
             if (tok0 + sl * 32 >= prm.ntok) continue;  // warp-uniform
+            if (prm.ksplit > 1) {  // raw fp32 partial sums; rows exist for every feature of the tile, ld_partial covers the slice
+                uint4 *dst = reinterpret_cast<uint4 *>(prm.partial + ((int64_t)split * prm.tiles_f * TC_BM + feat) * prm.ld_partial + tok0 + sl * 32);
+#pragma unroll
+                for (int v = 0; v < 8; v++) dst[v] = make_uint4(r[4 * v], r[4 * v + 1], r[4 * v + 2], r[4 * v + 3]);
+                continue;
+            }
             if (feat_ok) store_slice(r, sl, feat, b);
         }
         tc_fence_before();
@@ -364,7 +380,7 @@ spmm_tc_kernel(const TcParams prm, const __grid_constant__ CUtensorMap tmap0, co
                 mbar_expect_tx(&full_b[s], TC_B_BYTES);
                 const int xc = TERMS == 1 ? 0 : kSplitX[kb % TERMS];
                 const CUtensorMap *tm = xc == 0 ? &tmap0 : (xc == 1 ? &tmap1 : &tmap2);
-                tma_load_2d(b_stages + s * TC_B_BYTES, tm, (kb / TERMS) * TC_BK, (int)tok0, &full_b[s]);
+                tma_load_2d(b_stages + s * TC_B_BYTES, tm, ((kb_base + kb) / TERMS) * TC_BK, (int)tok0, &full_b[s]);
             }
         }
     } else if (warp == 1) {
@@ -435,13 +451,13 @@ spmm_tc_kernel(const TcParams prm, const __grid_constant__ CUtensorMap tmap0, co
         if (TRANSPOSED) {
             TrRegs<N_, M_> ra, rb;
             run_group([&](TrRegs<N_, M_> &t, int it) {
-                          fetch_transposed<N_, M_>(t, prm, prm.nval[TERMS == 1 ? 0 : kSplitW[it % TERMS]], feat0, it / TERMS, gtid);
+                          fetch_transposed<N_, M_>(t, prm, prm.nval[TERMS == 1 ? 0 : kSplitW[it % TERMS]], feat0, (kb_base + it) / TERMS, gtid);
                       },
                       [&](const TrRegs<N_, M_> &t, char *tile) { write_transposed<N_, M_>(t, tile, sel, gtid); }, ra, rb);
         } else {
             FwdRegs<N_, M_> ra, rb;
             run_group([&](FwdRegs<N_, M_> &t, int it) {
-                          fetch_forward<N_, M_>(t, prm, prm.nval[TERMS == 1 ? 0 : kSplitW[it % TERMS]], feat0, it / TERMS, gwarp, lane);
+                          fetch_forward<N_, M_>(t, prm, prm.nval[TERMS == 1 ? 0 : kSplitW[it % TERMS]], feat0, (kb_base + it) / TERMS, gwarp, lane);
                       },
                       [&](const FwdRegs<N_, M_> &t, char *tile) { write_forward<N_, M_>(t, tile, sel, gwarp, lane); }, ra, rb);
         }
@@ -830,6 +846,62 @@ __global__ void __launch_bounds__(128) split_f32_kernel(const float *__restrict_
     }
 }
 
+// ---- split-K of the fused kernel for few output tiles ----------------------------------------------------------------
+// Policy (pure arithmetic, so that workspace queries need no device): with fewer output tiles than half the SMs of a
+// B200 the reduction axis is cut so that about one CTA per SM runs, every range keeping at least four k-blocks.
+constexpr int TC_POLICY_SMS = 148;
+int tc_ksplit(const Geo &geo, int dtype, bool transposed, int64_t tokens) {
+    if (dtype == NMG_F32) return 1;  // fp32 mode accumulates in promoted chunks inside one CTA
+    const int64_t feats = transposed ? geo.K : geo.M, red = transposed ? geo.M : geo.K;
+    const int64_t tiles = ((feats + TC_BM - 1) / TC_BM) * ((tokens + TC_BN - 1) / TC_BN);
+    const int64_t nkb = (red + TC_BK - 1) / TC_BK;
+    if (tiles * 2 > TC_POLICY_SMS || nkb < 8) return 1;
+    int64_t want = TC_POLICY_SMS / tiles;
+    if (want > nkb / 4) want = nkb / 4;
+    if (want > 32) want = 32;
+    if (want < 2) return 1;
+    const int64_t per = (nkb + want - 1) / want;
+    return (int)((nkb + per - 1) / per);  // every range non-empty
+}
+size_t tc_ksplit_workspace_bytes(const Geo &geo, int dtype, bool transposed, int64_t tokens) {
+    const int ks = tc_ksplit(geo, dtype, transposed, tokens);
+    if (ks <= 1) return 0;
+    const int64_t feats = transposed ? geo.K : geo.M;
+    return (size_t)ks * (size_t)round_up(feats, TC_BM) * (size_t)round_up(tokens, TC_BN) * 4 + 512;
+}
+
+// out = sum over the ranges of partial[s] (+ bias), converted; 32 x 32 tiles through shared memory so that both the reads
+// (tokens contiguous) and token-major writes (features contiguous) are coalesced.  Ranges are added in a fixed order.
+template <typename T>
+__global__ void __launch_bounds__(256) splitk_reduce_kernel(const float *__restrict__ partial, int ksplit, int64_t plane, int64_t ldp,
+                                                            int64_t feats, int64_t ntok, const T *__restrict__ bias, T *__restrict__ out,
+                                                            int64_t ld_out, int token_major) {
+    __shared__ float tile[32][33];
+    const int64_t f0 = (int64_t)blockIdx.y * 32, t0 = (int64_t)blockIdx.x * 32;
+    const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
+    for (int r = ty; r < 32; r += 8) {
+        const int64_t f = f0 + r, t = t0 + tx;
+        float acc = 0.f;
+        if (f < feats && t < ntok) {
+            for (int s = 0; s < ksplit; s++) acc += partial[s * plane + f * ldp + t];
+            if (bias) acc += DT<T>::to_f32(bias[f]);
+        }
+        tile[r][tx] = acc;
+    }
+    __syncthreads();
+    if (token_major) {
+        for (int r = ty; r < 32; r += 8) {  // r = token, tx = feature
+            const int64_t t = t0 + r, f = f0 + tx;
+            if (f < feats && t < ntok) out[t * ld_out + f] = DT<T>::from_f32(tile[tx][r]);
+        }
+    } else {
+        for (int r = ty; r < 32; r += 8) {
+            const int64_t f = f0 + r, t = t0 + tx;
+            if (f < feats && t < ntok) out[f * ld_out + t] = DT<T>::from_f32(tile[r][tx]);
+        }
+    }
+}
+
 size_t tc_split_workspace_bytes(const Geo &geo, int dtype, bool transposed, int64_t tokens) {
     if (dtype != NMG_F32) return 0;
     const int64_t red = transposed ? geo.M : geo.K;
@@ -839,7 +911,7 @@ size_t tc_split_workspace_bytes(const Geo &geo, int dtype, bool transposed, int6
 template <int N_, int M_, typename T, bool TR>
 static int tc_launch_one(const TcParams &p, const CUtensorMap *tm, cudaStream_t st) {
     const size_t smem = tc_smem_bytes((int)comb(N_, M_));
-    const int64_t ctas = (int64_t)p.tiles_f * p.tiles_t;
+    const int64_t ctas = (int64_t)p.tiles_f * p.tiles_t * p.ksplit;
     if (ctas > 0x7fffffff) NMG_FAIL(NMG_ERR_UNSUPPORTED, "too many output tiles for one launch");
     dim3 grid((unsigned)ctas);
     NMG_CUDA(cudaFuncSetAttribute(spmm_tc_kernel<N_, M_, T, TR>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
@@ -955,10 +1027,23 @@ int tc_matmul(const Geo &geo, int dtype, bool transposed, bool dense, const void
     if ((rc = get_status_word(&status))) return rc;
     const int64_t feats = transposed ? geo.K : geo.M;
     const int64_t ftile = pair ? 256 : TC_BM;
-    TcParams p{pat, {planes[0], planes[1], planes[2]}, bias, out, feats, red, tokens, ld_out, natural_width(geo), geo.nb, out_token_major,
-               (int)((feats + ftile - 1) / ftile), (int)((tokens + TC_BN - 1) / TC_BN), status, 0};
+    TcParams p{};
+    p.pat = pat;
+    for (int c = 0; c < 3; c++) p.nval[c] = planes[c];
+    p.bias = bias; p.out = out; p.out_feats = feats; p.red = red; p.ntok = tokens; p.ld_out = ld_out;
+    p.Kpn = natural_width(geo); p.nb = geo.nb; p.out_token_major = out_token_major;
+    p.tiles_f = (int)((feats + ftile - 1) / ftile);
+    p.tiles_t = (int)((tokens + TC_BN - 1) / TC_BN);
+    p.status = status;
     static const int debug_flags = [] { const char *e = getenv("NMG_TC_DEBUG"); return e ? atoi(e) : 0; }();
     p.debug = debug_flags;
+    p.ksplit = pair ? 1 : tc_ksplit(geo, dtype, transposed, tokens);
+    if (p.ksplit > 1) {
+        const size_t need = tc_ksplit_workspace_bytes(geo, dtype, transposed, tokens);
+        if (!ws || ws_bytes < need) NMG_FAIL(NMG_ERR_WORKSPACE, "workspace of %zu bytes required for the partial tiles, got %zu", need, ws_bytes);
+        p.partial = reinterpret_cast<float *>(((uintptr_t)ws + 255) & ~(uintptr_t)255);
+        p.ld_partial = (int64_t)p.tiles_t * TC_BN;
+    }
     const ProfileEvents pe = take_profile_events();
     if (pe.start) NMG_CUDA(cudaEventRecord(pe.start, st));
     rc = NMG_ERR_UNSUPPORTED;
@@ -972,6 +1057,19 @@ int tc_matmul(const Geo &geo, int dtype, bool transposed, bool dense, const void
     NMG_TC_CASE(1, 16)
 #undef NMG_TC_CASE
     if (rc == NMG_ERR_UNSUPPORTED) set_error("no tensor-core kernel for %d:%d", geo.n, geo.m);
+    if (rc == NMG_OK && p.ksplit > 1) {
+        const int64_t plane = (int64_t)p.tiles_f * TC_BM * p.ld_partial;
+        dim3 grid((unsigned)((tokens + 31) / 32), (unsigned)((feats + 31) / 32));
+        if (grid.y > 65535) NMG_FAIL(NMG_ERR_UNSUPPORTED, "too many output features for the split-K reduction");
+        if (dtype == NMG_F16)
+            splitk_reduce_kernel<__half><<<grid, 256, 0, st>>>(p.partial, p.ksplit, plane, p.ld_partial, feats, tokens, static_cast<const __half *>(bias),
+                                                                static_cast<__half *>(out), ld_out, out_token_major);
+        else
+            splitk_reduce_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>(p.partial, p.ksplit, plane, p.ld_partial, feats, tokens,
+                                                                       static_cast<const __nv_bfloat16 *>(bias), static_cast<__nv_bfloat16 *>(out), ld_out,
+                                                                       out_token_major);
+        NMG_CUDA(cudaGetLastError());
+    }
     if (rc == NMG_OK && pe.stop) NMG_CUDA(cudaEventRecord(pe.stop, st));
     return rc;
 }

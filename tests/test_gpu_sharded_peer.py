@@ -42,7 +42,10 @@ def _worker(rank, world, port, result_q):
         full = sten.GroupedNMTensor.from_dense(w, n, m, sparse_dim=0, group_size=g, group_dim=1).to_dense()
         ref = full.double() @ x.double().t()
         errs = {k: float((v.double() - ref).norm() / ref.norm()) for k, v in results.items()}
-        same = all(torch.equal(results[("peer", 1)], v) for v in results.values())
+        def close(a, b):  # variants differ in fp32 summation order (fused kernel with a split reduction axis vs two passes)
+            return float((a.double() - b.double()).norm() / b.double().norm()) <= 2e-3
+
+        same = torch.equal(results[("peer", 1)], results[("peer", 2)]) and close(results[("gather", 2)], results[("peer", 1)])
         # host operands: every rank uploads half of X, downloads the rows it computed
         layer = RowShardedNMMatmul.from_full_weight(w, n, m, g, rounds=1, exchange="peer")
         x_host = x.cpu().pin_memory()
@@ -50,7 +53,7 @@ def _worker(rank, world, port, result_q):
         layer.forward_host(x_host, out_host)
         torch.cuda.synchronize()
         rp = M // world
-        same = same and torch.equal(out_host[rank * rp:(rank + 1) * rp], results[("peer", 1)][rank * rp:(rank + 1) * rp].cpu())
+        same = same and close(out_host[rank * rp:(rank + 1) * rp], results[("peer", 1)][rank * rp:(rank + 1) * rp].cpu())
         same = same and float(out_host[(1 - rank) * rp:(2 - rank) * rp].abs().max()) == 0
         result_q.put((rank, errs, same, None))
     except Exception as exc:  # noqa: BLE001 - reported to the parent, which fails the test
@@ -94,7 +97,8 @@ def test_host_operand_pipeline_on_one_gpu():
         layer.forward_host(x_host, out_host, chunk_tokens=1024)
     torch.cuda.synchronize()
     direct = layer(x_host.to(dev))
-    assert torch.equal(out_host, direct.cpu())
+    # chunks of 1024 tokens and the whole batch may take different kernel variants: same numbers up to fp32 summation order
+    assert float((out_host.double() - direct.cpu().double()).norm() / direct.double().norm()) <= 2e-3
     full = sten.GroupedNMTensor.from_dense(w, n, m, sparse_dim=0, group_size=g, group_dim=1).to_dense()
     ref = full.double() @ x_host.to(dev).double().t()
     assert float((direct.double() - ref).norm() / ref.norm()) <= 1e-2

@@ -235,14 +235,18 @@ def test_replicated_output_matches_the_plain_matmul(dtype, M, K, tokens, tight):
     ref64 = np_of(dense).astype(np.float64) @ np_of(x).astype(np.float64).T + np_of(bias).astype(np.float64)[:, None]
     assert rel_fro(np_of(ref), ref64) <= (TOL_F32 if dtype == torch.float32 else TOL_HALF)
     for b in bufs:
-        assert torch.equal(b[1:M + 1, :tokens], ref)
+        # every destination receives the same bits; the plain call may run another variant (fused, split reduction axis),
+        # whose fp32 summation order differs
+        assert torch.equal(b[1:M + 1, :tokens], bufs[0][1:M + 1, :tokens])
+        assert rel_fro(np_of(b[1:M + 1, :tokens]), np_of(ref).astype(np.float64)) <= (1e-6 if dtype == torch.float32 else 2e-3)
+        assert rel_fro(np_of(b[1:M + 1, :tokens]), ref64) <= (TOL_F32 if dtype == torch.float32 else TOL_HALF)
         # nothing outside the panel is touched
         assert float((b[0] - 7).abs().max()) == 0 and float((b[M + 1] - 7).abs().max()) == 0
         assert ld == tokens or float((b[1:M + 1, tokens:] - 7).abs().max()) == 0
     assert ops.read_status() == 0
     # few tokens run on the same variant
     ops.spmm_replicated(val, idx, M, K, n, m, g, x[:32], [bufs[0][1:].data_ptr()], ld, bias=bias)
-    assert torch.equal(bufs[0][1:M + 1, :32], ref[:, :32])
+    assert rel_fro(np_of(bufs[0][1:M + 1, :32]), ref64[:, :32]) <= (TOL_F32 if dtype == torch.float32 else TOL_HALF)
 
 
 def test_against_stored_reference_microkernel_outputs():
