@@ -67,7 +67,8 @@ def measured_peaks():
 def config_dict(workload, n_gpus, exchange="peer", rounds=1):
     if workload == "sharded":
         how = ("no exchange" if n_gpus == 1 else
-               "the matmul epilogue stores every output tile into all ranks' buffers over NVLink (peer stores), one 4-byte all-reduce orders the ranks"
+               "the matmul epilogue stores every output tile into all ranks' buffers over NVLink (multimem.st through the NVSwitch multicast address "
+               "when the allocation has one, else one peer store per rank), one 4-byte all-reduce orders the ranks"
                if exchange == "peer" else f"{exchange}: {rounds} block-cyclic round(s), in-place NCCL all-gather of output slices overlapped with the next round")
         return {"workload": "row-sharded matmul: W 16384x16384 N(0,0.02) seed 0 bf16, nmg 2:8 g=16, X 16384x16384 N(0,1) seed 1 bf16",
                 "group_size": G, "parallelism": f"weight rows split over {n_gpus} rank(s); {how}",
@@ -332,6 +333,7 @@ def run_ours(args):
         panels = [sten.GroupedNMTensor.from_dense(wd, n, m, sparse_dim=0, group_size=G, group_dim=1) for wd in panels_dense]
         del panels_dense
         layer = RowShardedNMMatmul(panels, M, exchange=args.exchange)
+        layer.multicast = not args.no_multicast
         peer = args.exchange == "peer" and world > 1  # the layer then owns the (peer-mapped) output buffer
         y_dev = None if peer else torch.empty(M, TOK, dtype=torch.bfloat16, device=dev)
         total_flops = useful_flops(M, K, TOK, n, m)
@@ -566,6 +568,7 @@ def main():
     ap.add_argument("--rounds", type=int, default=0, help="row panels per rank when N > 1 (default: 1 for --exchange peer, 4 for gather)")
     ap.add_argument("--exchange", default="peer", choices=["peer", "gather"],
                     help="how row shards combine their output slices when N > 1: stores into every rank's buffer from the matmul epilogue, or NCCL all-gathers")
+    ap.add_argument("--no-multicast", action="store_true", help="peer exchange with one store per destination instead of NVSwitch multicast stores")
     ap.add_argument("--no-sweep", action="store_true", help="skip the per-pattern 4096^2 table")
     args = ap.parse_args()
     if args.workload == "encoder":

@@ -138,7 +138,7 @@ int nmg_spmm_uses_packed(int64_t M, int64_t K, int64_t tokens, int n, int m, int
 size_t nmg_spmm_replicated_workspace_bytes(int64_t M, int64_t K, int64_t tokens, int n, int m, int g, int dtype);
 int nmg_spmm_replicated(const void *val, const int16_t *idx, int64_t M, int64_t K, int n, int m, int g, int dtype,
                         const void *act, int64_t ld_act, int64_t tokens, const void *bias, void *const *outs, int n_outs,
-                        int64_t ld_out, void *workspace, size_t workspace_bytes, void *stream);
+                        void *multicast_out, int64_t ld_out, void *workspace, size_t workspace_bytes, void *stream);
 
 /* Matmul for callers that cannot allocate device memory (no counterpart in the reference, whose host code allocates
  * every buffer with torch: src/sten/grouped_nm/grouped_nm_tensor.py:652-672, sten_impls.py:127).

@@ -33,7 +33,7 @@ SIGNATURES = {
                           _vp]),
     "nmg_spmm_uses_packed": (_int, [_i64, _i64, _i64, _int, _int, _int, _int, _int, _int, _int]),
     "nmg_spmm_replicated_workspace_bytes": (_sz, [_i64, _i64, _i64, _int, _int, _int, _int]),
-    "nmg_spmm_replicated": (_int, [_vp, _vp, _i64, _i64, _int, _int, _int, _int, _vp, _i64, _i64, _vp, _vp, _int, _i64, _vp, _sz, _vp]),
+    "nmg_spmm_replicated": (_int, [_vp, _vp, _i64, _i64, _int, _int, _int, _int, _vp, _i64, _i64, _vp, _vp, _int, _vp, _i64, _vp, _sz, _vp]),
     "nmg_spmm_noalloc": (_int, [_vp, _vp, _i64, _i64, _int, _int, _int, _int, _vp, _i64, _i64, _vp, _vp, _i64, _int, _vp]),
     "nmg_profile_next": (_int, [_vp, _vp]),
     "nmg_measure_fma_peak": (_int, [ctypes.POINTER(ctypes.c_double), _vp]),

@@ -79,7 +79,7 @@ extern "C" size_t nmg_spmm_workspace_bytes(int64_t M, int64_t K, int64_t tokens,
 
 static int spmm_impl(const void *val, const int16_t *idx, const void *packed, int64_t M, int64_t K, int n, int m, int g, int dtype,
                      const void *act, int64_t ld_act, int64_t tokens, const void *bias, void *const *outs, int n_outs, int64_t ld_out,
-                     int layout, int algo, void *workspace, size_t workspace_bytes, void *stream, bool force_dense = false) {
+                     int layout, int algo, void *workspace, size_t workspace_bytes, void *stream, bool force_dense = false, void *mc_out = nullptr) {
     Geo geo;
     int rc = make_geo(M, K, n, m, g, &geo);
     if (rc) return rc;
@@ -108,7 +108,7 @@ static int spmm_impl(const void *val, const int16_t *idx, const void *packed, in
         const void *nval = nullptr;
         const bool dense = force_dense || tc_use_dense(geo, dtype, tokens);
         if (!dense && (rc = resolve_packed(geo, dtype, val, idx, packed, &ws, &left, &pat, &nval, st))) return rc;
-        return tc_matmul(geo, dtype, false, dense, val, idx, pat, nval, act, ld_act, tokens, bias, outs, n_outs, ld_out, out_tm ? 1 : 0, ws, left, st);
+        return tc_matmul(geo, dtype, false, dense, val, idx, pat, nval, act, ld_act, tokens, bias, outs, n_outs, mc_out, ld_out, out_tm ? 1 : 0, ws, left, st);
     }
     if (n_outs > 1) NMG_FAIL(NMG_ERR_UNSUPPORTED, "several output buffers need the tensor-core path (aligned token-major activations, >= 64 tokens and rows)");
     return simt_fwd(geo, dtype, val, idx, act, ld_act, tokens, bias, out, ld_out, layout, workspace, workspace_bytes, st);
@@ -124,7 +124,7 @@ extern "C" int nmg_spmm(const void *val, const int16_t *idx, const void *packed,
 
 extern "C" int nmg_spmm_replicated(const void *val, const int16_t *idx, int64_t M, int64_t K, int n, int m, int g, int dtype,
                                    const void *act, int64_t ld_act, int64_t tokens, const void *bias, void *const *outs, int n_outs,
-                                   int64_t ld_out, void *workspace, size_t workspace_bytes, void *stream) {
+                                   void *multicast_out, int64_t ld_out, void *workspace, size_t workspace_bytes, void *stream) {
     if (!outs || n_outs < 1 || n_outs > 8) NMG_FAIL(NMG_ERR_INVALID, "between 1 and 8 output buffers, got %d", n_outs);
     for (int d = 0; d < n_outs; d++)
         if (!outs[d]) NMG_FAIL(NMG_ERR_INVALID, "output buffer %d is NULL", d);
@@ -134,7 +134,7 @@ extern "C" int nmg_spmm_replicated(const void *val, const int16_t *idx, int64_t 
     if (!tc_dense_supported(geo, dtype))
         NMG_FAIL(NMG_ERR_UNSUPPORTED, "the replicated-output matmul runs on the two-pass tensor-core variant, which this chunk size does not fit");
     return spmm_impl(val, idx, nullptr, M, K, n, m, g, dtype, act, ld_act, tokens, bias, outs, n_outs, ld_out, NMG_ACT_TOKEN_MAJOR_OUT_ROWS,
-                     NMG_ALGO_TENSOR, workspace, workspace_bytes, stream, true);
+                     NMG_ALGO_TENSOR, workspace, workspace_bytes, stream, true, multicast_out);
 }
 
 extern "C" size_t nmg_spmm_replicated_workspace_bytes(int64_t M, int64_t K, int64_t tokens, int n, int m, int g, int dtype) {
@@ -191,6 +191,6 @@ extern "C" int nmg_spmm_t(const void *val, const int16_t *idx, const void *packe
     const bool dense = tensor && tc_use_dense(geo, dtype, tokens);
     if (!dense && (rc = resolve_packed(geo, dtype, val, idx, packed, &ws, &left, &pat, &nval, st))) return rc;
     void *dxs[1] = {dx};
-    if (tensor) return tc_matmul(geo, dtype, true, dense, val, idx, pat, nval, dy, ld_dy, tokens, nullptr, dxs, 1, ld_dx, 1, ws, left, st);
+    if (tensor) return tc_matmul(geo, dtype, true, dense, val, idx, pat, nval, dy, ld_dy, tokens, nullptr, dxs, 1, nullptr, ld_dx, 1, ws, left, st);
     return simt_bwd(geo, dtype, pat, nval, dy, ld_dy, tokens, dx, ld_dx, ws, left, st);
 }

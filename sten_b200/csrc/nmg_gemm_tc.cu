@@ -219,6 +219,7 @@ struct GemmParams {
     const void *bias;  // [out_feats] or NULL
     void *outs[GEMM_MAX_OUTS];  // the result is written to every one of these (same shape and pitch): outs[0] is the
     int n_out;                  // caller's buffer, the others are typically the same buffer on peer GPUs
+    void *mc_out;               // NVSwitch multicast address mapping onto all of outs[], or NULL: one multimem.st reaches every GPU
     int64_t out_feats, red, ntok, ld_out;
     int out_token_major;
     int out_staged;    // feature-major output whose rows are 16-byte aligned: go through the staging tile
@@ -443,6 +444,10 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_tc_kernel(const GemmPara
                         if (f >= prm.out_feats || tokg >= prm.ntok) continue;
                         const uint4 w = *reinterpret_cast<const uint4 *>(stage_w + row * 128 + (((lane & 7) ^ (row & 7)) << 4));
                         if (tokg + CHUNK_TOK <= prm.ntok) {
+                            if (prm.mc_out) {  // the switch replicates the 16 bytes to every GPU of the multicast group
+                                multimem_st_v4(static_cast<T *>(prm.mc_out) + f * prm.ld_out + tokg, w);
+                                continue;
+                            }
                             for (int d = 0; d < prm.n_out; d++)
                                 *reinterpret_cast<uint4 *>(static_cast<T *>(prm.outs[d]) + f * prm.ld_out + tokg) = w;
                         } else {  // ragged end of the token axis
@@ -542,8 +547,8 @@ template <typename T> static int gemm_launch(const GemmParams &p, const GemmMaps
 // act_maps: tensor maps of the activation planes (box 64 x 256, 128-byte swizzle), one for 16-bit data, three for
 // the fp32 split.  ws holds the expanded weight for the duration of the call.
 int tc_dense_matmul(const Geo &geo, int dtype, bool transposed, const void *val, const int16_t *idx, const CUtensorMap *act_maps,
-                    int64_t tokens, const void *bias, void *const *outs, int n_outs, int64_t ld_out, int out_token_major, void *ws,
-                    size_t ws_bytes, cudaStream_t st) {
+                    int64_t tokens, const void *bias, void *const *outs, int n_outs, void *mc_out, int64_t ld_out, int out_token_major,
+                    void *ws, size_t ws_bytes, cudaStream_t st) {
     if (n_outs < 1 || n_outs > GEMM_MAX_OUTS) NMG_FAIL(NMG_ERR_INVALID, "between 1 and %d output buffers, got %d", GEMM_MAX_OUTS, n_outs);
     const int64_t rows = transposed ? geo.K : geo.M, red = transposed ? geo.M : geo.K;
     const size_t need = tc_dense_workspace_bytes(geo, dtype, transposed);
@@ -593,6 +598,7 @@ int tc_dense_matmul(const Geo &geo, int dtype, bool transposed, const void *val,
     gp.out_feats = rows; gp.red = red; gp.ntok = tokens; gp.ld_out = ld_out;
     gp.out_token_major = out_token_major;
     gp.out_staged = vec ? 1 : 0;
+    gp.mc_out = (vec && mc_out && (reinterpret_cast<uintptr_t>(mc_out) & 15) == 0) ? mc_out : nullptr;
     gp.tiles_f = (int)((rows + TC_BM - 1) / TC_BM);
     gp.tiles_t = (int)((tokens + TC_BN - 1) / TC_BN);
     gp.status = status;

@@ -46,13 +46,14 @@ size_t tc_dense_workspace_bytes(const Geo &geo, int dtype, bool transposed);
 // fused kernel with few output tiles: the reduction axis is cut over tc_ksplit CTAs per tile, fp32 partial tiles in `ws`
 int tc_ksplit(const Geo &geo, int dtype, bool transposed, int64_t tokens);
 size_t tc_ksplit_workspace_bytes(const Geo &geo, int dtype, bool transposed, int64_t tokens);
-// outs / n_outs: the result goes to every listed buffer (same shape and pitch); more than one needs `dense`.
+// outs / n_outs: the result goes to every listed buffer (same shape and pitch); more than one needs `dense`.  mc_out, when
+// not NULL, is an NVSwitch multicast address that maps onto all of them: full 16-byte chunks are then stored once.
 int tc_matmul(const Geo &geo, int dtype, bool transposed, bool dense, const void *val, const int16_t *idx, const uint16_t *pat,
               const void *nval, const void *act, int64_t ld_act, int64_t tokens, const void *bias, void *const *outs, int n_outs,
-              int64_t ld_out, int out_token_major, void *ws, size_t ws_bytes, cudaStream_t st);
+              void *mc_out, int64_t ld_out, int out_token_major, void *ws, size_t ws_bytes, cudaStream_t st);
 int tc_dense_matmul(const Geo &geo, int dtype, bool transposed, const void *val, const int16_t *idx, const CUtensorMap *act_maps,
-                    int64_t tokens, const void *bias, void *const *outs, int n_outs, int64_t ld_out, int out_token_major, void *ws,
-                    size_t ws_bytes, cudaStream_t st);
+                    int64_t tokens, const void *bias, void *const *outs, int n_outs, void *mc_out, int64_t ld_out, int out_token_major,
+                    void *ws, size_t ws_bytes, cudaStream_t st);
 
 // ---- specialised forward kernel: parameters, shared-memory plan, per-(n, m) launchers
 struct FwdParams {

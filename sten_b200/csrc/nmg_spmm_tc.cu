@@ -975,7 +975,7 @@ bool tc_use_dense(const Geo &geo, int dtype, int64_t tokens) {
 // act: [tokens][ld_act] with the reduction axis contiguous (X for the forward, dY for the transposed product).
 int tc_matmul(const Geo &geo, int dtype, bool transposed, bool dense, const void *val, const int16_t *idx, const uint16_t *pat,
               const void *nval, const void *act, int64_t ld_act, int64_t tokens, const void *bias, void *const *outs, int n_outs,
-              int64_t ld_out, int out_token_major, void *ws, size_t ws_bytes, cudaStream_t st) {
+              void *mc_out, int64_t ld_out, int out_token_major, void *ws, size_t ws_bytes, cudaStream_t st) {
     if (n_outs < 1 || (n_outs > 1 && !dense)) NMG_FAIL(NMG_ERR_UNSUPPORTED, "several output buffers need the two-pass tensor-core variant");
     void *out = outs[0];
     const int64_t red = transposed ? geo.M : geo.K;
@@ -1019,7 +1019,7 @@ int tc_matmul(const Geo &geo, int dtype, bool transposed, bool dense, const void
     if (dense) {
         const ProfileEvents pe = take_profile_events();
         if (pe.start) NMG_CUDA(cudaEventRecord(pe.start, st));
-        rc = tc_dense_matmul(geo, dtype, transposed, val, idx, tm, tokens, bias, outs, n_outs, ld_out, out_token_major, ws, ws_bytes, st);
+        rc = tc_dense_matmul(geo, dtype, transposed, val, idx, tm, tokens, bias, outs, n_outs, mc_out, ld_out, out_token_major, ws, ws_bytes, st);
         if (rc == NMG_OK && pe.stop) NMG_CUDA(cudaEventRecord(pe.stop, st));
         return rc;
     }

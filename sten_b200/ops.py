@@ -151,10 +151,10 @@ def spmm(val, idx, M, K, n, m, g, act, bias=None, layout=nat.NMG_ACT_TOKEN_MAJOR
     return out
 
 
-def spmm_replicated(val, idx, M, K, n, m, g, act, out_ptrs, ld_out, bias=None):
+def spmm_replicated(val, idx, M, K, n, m, g, act, out_ptrs, ld_out, bias=None, multicast_ptr=None):
     """C = W @ act^T (+ bias per row) written into every buffer of ``out_ptrs`` (device addresses of [M, ld_out] row
     panels: this GPU's and the peers' mapped copies) by the matmul kernel itself.  The caller keeps the buffers alive and
-    synchronises the ranks afterwards."""
+    synchronises the ranks afterwards.  ``multicast_ptr``: NVSwitch multicast address of the same location, when there is one."""
     import ctypes
     dev = _require_cuda(val, idx, act, bias)
     code = _dtype_code(val)
@@ -172,7 +172,8 @@ def spmm_replicated(val, idx, M, K, n, m, g, act, out_ptrs, ld_out, bias=None):
     with torch.cuda.device(dev):
         ws, nbytes = _workspace(L.nmg_spmm_replicated_workspace_bytes(M, K, tokens, n, m, g, code), dev)
         nat.check(L.nmg_spmm_replicated(val.data_ptr(), idx.data_ptr(), M, K, n, m, g, code, act.data_ptr(), ld_act, tokens,
-                                        bias.data_ptr() if bias is not None else None, ptrs, len(out_ptrs), ld_out,
+                                        bias.data_ptr() if bias is not None else None, ptrs, len(out_ptrs),
+                                        int(multicast_ptr) if multicast_ptr else None, ld_out,
                                         ws.data_ptr() if ws is not None else None, nbytes, _stream(dev)))
 
 

@@ -148,13 +148,17 @@ class PeerBuffer:
         self.group = group if group is not None else dist.group.WORLD
         self.world, self.rank = dist.get_world_size(self.group), dist.get_rank(self.group)
         self._keep = []
+        self.multicast_ptr = 0
         try:
             import torch.distributed._symmetric_memory as symm
             self.local = symm.empty(tuple(shape), dtype=dtype, device=device)
             hdl = symm.rendezvous(self.local, self.group)
             self._keep.append(hdl)
             self.ptrs = [int(p) for p in hdl.buffer_ptrs]
-            self.how = "symmetric memory"
+            # NVSwitch multicast address of the same allocation (0 / absent when the fabric has none): one store to it
+            # lands in every rank's copy
+            self.multicast_ptr = int(getattr(hdl, "multicast_ptr", 0) or 0)
+            self.how = "symmetric memory" + (" with NVSwitch multicast" if self.multicast_ptr else "")
         except Exception as exc:  # noqa: BLE001 - any failure of the optional allocator selects the IPC route
             self.local = torch.empty(tuple(shape), dtype=dtype, device=device)
             storage = self.local.untyped_storage()
@@ -188,6 +192,7 @@ class RowShardedNMMatmul:
         if exchange not in ("gather", "peer"):
             raise ValueError("exchange must be 'gather' (NCCL all-gather per round) or 'peer' (the matmul kernel stores into every rank's buffer)")
         self.exchange = exchange
+        self.multicast = True  # peer exchange: store through the NVSwitch multicast address when the allocation has one
         self._peer_out = None
         self._flag = None
         self.group = group
@@ -241,7 +246,8 @@ class RowShardedNMMatmul:
             ptrs = [base + q * rp * ld * es for base in self._peer_out.ptrs]
             # own copy first: outs[0] is the buffer the bias / alignment checks refer to
             ptrs = [ptrs[self.rank]] + [a for r, a in enumerate(ptrs) if r != self.rank]
-            ops.spmm_replicated(panel.val, panel.idx, M, K, n, m, g, x2d, ptrs, ld)
+            mc = self._peer_out.multicast_ptr + q * rp * ld * es if (self._peer_out.multicast_ptr and self.multicast) else None
+            ops.spmm_replicated(panel.val, panel.idx, M, K, n, m, g, x2d, ptrs, ld, multicast_ptr=mc)
         dist.all_reduce(self._flag, group=self.group)  # stream-ordered: completes when every rank's stores are done
         return self._peer_out.local
 

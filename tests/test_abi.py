@@ -95,7 +95,7 @@ def test_kernel_choice_queries_are_pure_host_arithmetic():
     # replicated output: argument validation happens before any CUDA call
     one = ctypes.c_void_p(16)
     outs = (ctypes.c_void_p * 1)(16)
-    assert L.nmg_spmm_replicated(one, one, 4096, 4096, 2, 4, 16, BF, one, 4096, 2048, None, outs, 0, 2048, None, 0, None) == 1
-    assert L.nmg_spmm_replicated(one, one, 4096, 4096, 2, 4, 16, BF, one, 4090, 32, None, outs, 1, 32, None, 0, None) == 1  # ld_act < K
+    assert L.nmg_spmm_replicated(one, one, 4096, 4096, 2, 4, 16, BF, one, 4096, 2048, None, outs, 0, None, 2048, None, 0, None) == 1
+    assert L.nmg_spmm_replicated(one, one, 4096, 4096, 2, 4, 16, BF, one, 4090, 32, None, outs, 1, None, 32, None, 0, None) == 1  # ld_act < K
     assert L.nmg_spmm_replicated_workspace_bytes(4096, 4096, 100, 2, 4, 16, BF) >= 4096 * 4096 * 2
     assert L.nmg_memcpy_2d_async(None, 8, one, 8, 8, 1, None) == 1
