@@ -513,8 +513,11 @@ def run_encoder(args):
         torch.cuda.synchronize()
 
     def fwd(m):
+        # embeddings + encoder stack called directly with no attention mask (the batch has no padding): the model's own
+        # mask preparation keeps an all-ones mask while a CUDA graph is being captured, which pushes attention onto a
+        # slow fp32 path in the captured graph only; without a mask eager and captured runs use the same fused attention
         with torch.no_grad():
-            return m(input_ids=ids).last_hidden_state
+            return m.encoder(m.embeddings(input_ids=ids), attention_mask=None).last_hidden_state
 
     for _ in range(max(args.warmup, 3)):
         out = fwd(sparse_model)
@@ -540,10 +543,15 @@ def run_encoder(args):
     ms_graph = graphed(sparse_model)
     ms_graph_dense = graphed(dense_model)
     toks = BATCH * SEQ
+    # headline: the captured graph when capture worked (steady-state serving replays a graph; every replay recomputes the
+    # whole forward through the same plugin calls), else the eager loop
+    ms_best = min(ms_eager, ms_graph) if ms_graph else ms_eager
     if rank == 0:
         print(json.dumps({
-            "metric": "sparse_encoder_tokens_per_s", "value": toks / (ms_eager * 1e-3), "unit": "tokens/s", "n_gpus": world,
-            "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_eager, "higher_is_better": True, "scaling": "strong",
+            "metric": "sparse_encoder_tokens_per_s", "value": toks / (ms_best * 1e-3), "unit": "tokens/s", "n_gpus": world,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_best, "higher_is_better": True, "scaling": "strong",
+            "execution": "cuda graph replay" if ms_graph and ms_graph <= ms_eager else "eager",
+            "eager_tokens_per_s": toks / (ms_eager * 1e-3),
             "vs_baseline": None, "dtype": "f16", "data": "synthetic",
             "config": {"workload": "BERT-large-shaped encoder, 24 layers, all encoder linears nmg 2:4 g=16, batch 32 x seq 384",
                        "parallelism": f"batch split over {world} rank(s), no collective"},

@@ -35,8 +35,31 @@ def _require_cuda(*tensors):
     return dev
 
 
+_raw_stream = getattr(torch._C, "_cuda_getCurrentRawStream", None)
+
+
 def _stream(dev):
+    """Handle of the current stream of ``dev`` (the raw query is several times cheaper than building a Stream object)."""
+    if _raw_stream is not None and dev.index is not None:
+        return _raw_stream(dev.index)
     return torch.cuda.current_stream(dev).cuda_stream
+
+
+class _on_device:
+    """``torch.cuda.device(dev)`` only when ``dev`` is not already current: the common case costs one integer compare."""
+
+    __slots__ = ("ctx",)
+
+    def __init__(self, dev):
+        self.ctx = None if dev.index is None or torch.cuda.current_device() == dev.index else torch.cuda.device(dev)
+
+    def __enter__(self):
+        if self.ctx is not None:
+            self.ctx.__enter__()
+
+    def __exit__(self, *exc):
+        if self.ctx is not None:
+            self.ctx.__exit__(*exc)
 
 
 def _workspace(nbytes, dev):
@@ -142,7 +165,7 @@ def spmm(val, idx, M, K, n, m, g, act, bias=None, layout=nat.NMG_ACT_TOKEN_MAJOR
     if bias is not None:
         bias = bias.contiguous()
     L = nat.lib()
-    with torch.cuda.device(dev):
+    with _on_device(dev):
         ws, nbytes = _workspace(_spmm_workspace_bytes(M, K, tokens, n, m, g, code, layout, algo, 1 if packed is not None else 0), dev)
         nat.check(L.nmg_spmm(val.data_ptr(), idx.data_ptr(), packed.data_ptr() if packed is not None else None, M, K, n,
                              m, g, code, act.data_ptr(), ld_act, tokens,
@@ -192,7 +215,7 @@ def spmm_t(val, idx, M, K, n, m, g, dy, algo=nat.NMG_ALGO_AUTO, packed=None):
         return dx
     val, idx = val.contiguous(), idx.contiguous()
     L = nat.lib()
-    with torch.cuda.device(dev):
+    with _on_device(dev):
         ws, nbytes = _workspace(L.nmg_spmm_t_workspace_bytes(M, K, tokens, n, m, g, code, algo,
                                                              1 if packed is not None else 0), dev)
         nat.check(L.nmg_spmm_t(val.data_ptr(), idx.data_ptr(), packed.data_ptr() if packed is not None else None, M, K,
