@@ -98,7 +98,7 @@ int nmg_pack(const void *val, const int16_t *idx, int64_t M, int64_t K, int n, i
  * workspace: device scratch of at least nmg_spmm_workspace_bytes(...) bytes, 256-byte aligned, owned by the
  * caller for the duration of the call (may be NULL when the query returns 0).
  * algo: NMG_ALGO_AUTO uses the tensor cores for token-major activations (16-bit rows must be 16-byte aligned) and
- * weights of at least 64 rows, at every token count; the SIMT kernels otherwise.  Two tensor-core variants exist.  Below 1536 tokens (256 for
+ * weights of at least 64 rows, at every token count; the SIMT kernels otherwise.  Two tensor-core variants exist.  Below 1280 tokens (256 for
  * fp32), for m in {4, 8, 16} and n <= 2, one fused kernel expands tiles of the packed copy inside the matmul.  From
  * there on, and for every other (n, m), the weight is first expanded into a transient dense 16-bit matrix in the workspace
  * (M * round_up(K, 8) * 2 bytes; three such planes for fp32) and multiplied by a persistent TMA-fed kernel; that

@@ -37,7 +37,7 @@ int simt_bwd(const Geo &geo, int dtype, const uint16_t *pat, const void *nval, c
 // entry point tc_matmul: the fused kernel (nmg_spmm_tc.cu) expands the column-ordered copy (pat / nval) tile by tile
 // inside the matmul; the two-pass variant (nmg_gemm_tc.cu, `dense` = true) first expands (val, idx) into a dense 16-bit
 // matrix in `ws` (tc_dense_workspace_bytes, after the split activation) and multiplies that.  tc_use_dense is the
-// policy: two passes from 1536 tokens on (256 for fp32), and for every (n, m) the fused kernel has no instantiation for.
+// policy: two passes from 1280 tokens on (256 for fp32), and for every (n, m) the fused kernel has no instantiation for.
 bool tc_supported(const Geo &geo, int dtype);        // fused kernel
 bool tc_dense_supported(const Geo &geo, int dtype);  // two-pass variant
 bool tc_use_dense(const Geo &geo, int dtype, int64_t tokens);

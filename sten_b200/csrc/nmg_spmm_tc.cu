@@ -967,9 +967,10 @@ bool tc_use_dense(const Geo &geo, int dtype, int64_t tokens) {
     if (!dense) return false;
     if (!fused) return true;
     if (forced == 0 || forced == 1) return forced == 1;
-    // Measured crossover (4096^2 and 16384^2 weights): the fused kernel wins up to 1024 tokens, the two-pass variant
-    // from 2048 on; fp32 (six split products, so six in-kernel expansions per tile) prefers two passes from 256 tokens.
-    return tokens >= (dtype == NMG_F32 ? 256 : 1536);
+    // Measured crossover (4096^2 and 16384^2 bf16 weights): a tie around 1024 tokens (0.055 / 0.053 ms and 0.567 / 0.598 ms,
+    // fused / two-pass), two passes clearly ahead at 1536 (0.099 / 0.072 ms and 0.836 / 0.799 ms); fp32 (six split products,
+    // so six in-kernel expansions per tile) prefers two passes from 256 tokens.
+    return tokens >= (dtype == NMG_F32 ? 256 : 1280);
 }
 
 // act: [tokens][ld_act] with the reduction axis contiguous (X for the forward, dY for the transposed product).

@@ -77,7 +77,7 @@ def test_kernel_choice_queries_are_pure_host_arithmetic():
     BF, F32 = nat.NMG_BF16, nat.NMG_F32
     TM, KM = nat.NMG_ACT_TOKEN_MAJOR, nat.NMG_ACT_K_MAJOR
     AUTO, SIMT, TENSOR = nat.NMG_ALGO_AUTO, nat.NMG_ALGO_SIMT, nat.NMG_ALGO_TENSOR
-    # fused tensor-core kernel below 1536 tokens reads the packed copy; the two-pass variant above does not
+    # fused tensor-core kernel below 1280 tokens reads the packed copy; the two-pass variant above does not
     assert L.nmg_spmm_uses_packed(4096, 4096, 256, 2, 4, 16, BF, TM, AUTO, 0) == 1
     assert L.nmg_spmm_uses_packed(4096, 4096, 2048, 2, 4, 16, BF, TM, AUTO, 0) == 0
     # SIMT forward reads val / idx; SIMT transposed reads the packed copy

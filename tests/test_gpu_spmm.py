@@ -185,7 +185,7 @@ def test_tensor_core_is_the_default_for_half_precision():
 
 
 TWO_PASS_CASES = [
-    # n, m, g, M, K, tokens: from 1536 tokens on (256 in fp32, and always for patterns without a fused kernel) the weight is
+    # n, m, g, M, K, tokens: from 1280 tokens on (256 in fp32, and always for patterns without a fused kernel) the weight is
     # expanded once into a dense 16-bit matrix and multiplied by the persistent TMA-fed kernel
     (2, 4, 16, 256, 512, 1536),
     (2, 8, 16, 264, 904, 1700),
