@@ -91,7 +91,13 @@ def time_cpu(workload, steps, warmup):
     """Seconds per step of the bounded CPU sample, its useful flops, kind, threads, description."""
     import numpy as np
     import torch
-    from oracle import nmg_oracle
+    from oracle import build_ref, nmg_oracle
+    # every host core this process may use, stated explicitly: launchers (torch.distributed.run) export OMP_NUM_THREADS=1
+    # for their workers, which would otherwise make this a one-thread measurement
+    cores = len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else (os.cpu_count() or 1)
+    nmg_oracle.set_threads(cores)
+    build_ref.set_threads(cores)
+    torch.set_num_threads(cores)
     if workload == "sharded":
         w = (torch.randn(CPU_ROWS, SH_K, generator=torch.Generator().manual_seed(0)) * 0.02).bfloat16().float().numpy()
         x = torch.randn(CPU_TOK, SH_K, generator=torch.Generator().manual_seed(1)).bfloat16().float().numpy()
@@ -117,7 +123,7 @@ def time_cpu(workload, steps, warmup):
     t0 = time.perf_counter()
     for _ in range(steps):
         one_step()
-    return (time.perf_counter() - t0) / steps, flops, kind, nmg_oracle.num_threads(), desc
+    return (time.perf_counter() - t0) / steps, flops, kind, cores, desc
 
 
 def run_reference(args):
@@ -252,6 +258,20 @@ def kernel_time(call, torch, nat, reps=6):
     return sum(out) / len(out)
 
 
+CHECK_ROWS = 64
+TOL = {"bf16": 1e-2, "f16": 1e-2, "f32": 1e-5}
+
+
+def sampled_rows(torch, count, limit, seed, dev):
+    rows = torch.randperm(limit, generator=torch.Generator().manual_seed(seed))[:count - 2]
+    return torch.cat([rows, torch.tensor([0, limit - 1])]).sort().values.to(dev)
+
+
+def rel_fro(got, want):
+    got, want = got.double(), want.double()
+    return float((got - want).norm() / want.norm())
+
+
 def sweep_table(torch, ops, nat, dev, peaks, fma_peak):
     """4096^2 sweep, fp32 (SIMT) and bf16 (tensor cores), next to cuBLAS on the densified weight."""
     w = torch.randn(SW_M, SW_K, generator=torch.Generator().manual_seed(0)).to(dev)
@@ -281,6 +301,8 @@ def sweep_table(torch, ops, nat, dev, peaks, fma_peak):
             o = torch.empty(SW_TOK, SW_M, device=dev, dtype=dtype)
             t_nmg = timed(lambda: ops.spmm(val, idx, SW_M, SW_K, n, m, G, xd, out=o, packed=packed, algo=algo))
             t_dense = timed(lambda: torch.mm(xd, dense.t()))
+            rows_chk = sampled_rows(torch, CHECK_ROWS, SW_M, 11, dev)
+            err = rel_fro(o[:, rows_chk], xd.double() @ dense[rows_chk].double().t())
             useful = useful_flops(SW_M, SW_K, SW_TOK, n, m) / t_nmg / 1e9  # TFLOP/s
             tensor = algo == nat.NMG_ALGO_TENSOR
             peak = peaks["bf16_tflops"] if tensor else fma_peak
@@ -288,7 +310,8 @@ def sweep_table(torch, ops, nat, dev, peaks, fma_peak):
             rows.append({"nm": f"{n}:{m}", "dtype": name, "kernel": how, "ms": t_nmg, "useful_tflops": useful,
                          "bound": "tensor" if tensor else "fma", "frac_of_peak_useful": useful / peak,
                          "frac_of_peak_executed": executed / peak,
-                         "cublas_dense_ms": t_dense, "speedup_vs_cublas": t_dense / t_nmg})
+                         "cublas_dense_ms": t_dense, "speedup_vs_cublas": t_dense / t_nmg,
+                         "rel_fro_vs_float64": err, "tolerance": TOL[name]})
             del val, idx, dense, packed, o
     return rows
 
@@ -323,12 +346,15 @@ def run_ours(args):
         owned = {(p * world + rank): p for p in range(rounds)}  # global panel index -> local round
         # the same seeded stream on every rank; only this rank's row panels are kept (block-cyclic over ranks)
         panels_dense = [None] * rounds
+        check_q = (rank + 1) % world  # global index of a panel ANOTHER rank computes (round 0): the output check below uses it
+        check_dense = None
         for q in range(world * rounds):
             blk = (torch.randn(rp, K, generator=gen, device=dev) * 0.02).bfloat16()
             if q in owned:
                 panels_dense[owned[q]] = blk
-            else:
-                del blk
+            if q == check_q:
+                check_dense = blk
+            del blk
         x = torch.randn(TOK, K, generator=torch.Generator(device=dev).manual_seed(1), device=dev).bfloat16()
         panels = [sten.GroupedNMTensor.from_dense(wd, n, m, sparse_dim=0, group_size=G, group_dim=1) for wd in panels_dense]
         del panels_dense
@@ -340,7 +366,8 @@ def run_ours(args):
         launches_per_step = 2 * rounds  # expansion pass + matmul kernel per panel
 
         def step():
-            return layer(x, out=y_dev)
+            # peer exchange: the layer returns one of its two peer-mapped buffers (they alternate between calls)
+            return layer(x, out=None if peer else y_dev)
 
         exchange_used = args.exchange if world > 1 else "none"
         if peer:
@@ -370,6 +397,24 @@ def run_ours(args):
 
         h2d, d2h = x_host.numel() * 2, y_host.numel() * 2  # summed over ranks: every byte of X goes up once, of C comes down once
         dtype_name, scaling = "bf16", "strong"
+
+        def check_output(y_last):
+            """Sampled parity check of the step's result, after the timed loop: CHECK_ROWS rows of C that ANOTHER rank
+            produced (rank r checks the panel of rank r+1, read from its own copy of C, so the exchange is verified as
+            well) against float64 dot products of the densified weight rows with X.  One rank: its own rows."""
+            val_c, idx_c = ops.sparsify(check_dense.unsqueeze(0), n, m, G)
+            rows = sampled_rows(torch, CHECK_ROWS, rp, 17 + rank, dev)
+            w_rows = ops.densify(val_c, idx_c, 1, rp, K, n, m, G)[0][rows].double()
+            want = w_rows @ x.double().t()
+            return rel_fro(y_last[check_q * rp + rows], want), int(rows.numel())
+
+        def check_e2e(y_last):
+            """The end-to-end leg's host result against the device-resident one, on this rank's rows (the rows it downloads)."""
+            errs = []
+            for p_ in range(rounds):
+                q = p_ * world + rank
+                errs.append(rel_fro(y_host[q * rp:(q + 1) * rp].to(dev), y_last[q * rp:(q + 1) * rp]))
+            return max(errs)
     else:
         M, K, TOK = SW_M, SW_K, SW_TOK
         w = torch.randn(M, K, generator=torch.Generator().manual_seed(0)).to(dev)
@@ -402,6 +447,19 @@ def run_ours(args):
         h2d, d2h = x_host.numel() * 4, sum(y.numel() * 4 for y in y_hosts)
         dtype_name, scaling = "f32", "weak"
 
+        def check_output(_):
+            """Sampled parity check after the timed loop: CHECK_ROWS output features of every pattern against float64."""
+            worst = 0.0
+            for (n_, m_) in SWEEP:
+                val_, idx_ = packs[(n_, m_)]
+                rows = sampled_rows(torch, CHECK_ROWS, M, 17 + rank, dev)
+                w_rows = ops.densify(val_, idx_, 1, M, K, n_, m_, G)[0][rows].double()
+                worst = max(worst, rel_fro(outs[(n_, m_)][:, rows], x.double() @ w_rows.t()))
+            return worst, CHECK_ROWS * len(SWEEP)
+
+        def check_e2e(_):
+            return max(rel_fro(yh.to(dev), outs[nm]) for yh, nm in zip(y_hosts, SWEEP))
+
     sampler = ClockSampler(local)
     if rank == 0:
         sampler.start()  # sampled from the warm-up steps (same kernels, same load) to the end of the end-to-end leg
@@ -409,6 +467,8 @@ def run_ours(args):
         step()
     ms_per_step = timed_loop(step, args.steps, barrier, torch, dist, world, dev)
     value = total_flops / (ms_per_step * 1e-3) / 1e9
+    y_last = step()  # one more (untimed) step whose result is checked; the timed steps computed exactly this
+    chk_err, chk_rows = check_output(y_last)
 
     for _ in range(2):
         e2e_step()
@@ -416,6 +476,18 @@ def run_ours(args):
     ms_e2e = timed_loop(e2e_step, k_e2e, barrier, torch, dist, world, dev)
     clocks = sampler.stop() if rank == 0 else None
     e2e_value = total_flops / (ms_e2e * 1e-3) / 1e9
+    torch.cuda.synchronize()
+    e2e_err = check_e2e(y_last)
+    tol = TOL[dtype_name]
+    if world > 1:
+        t = torch.tensor([chk_err, e2e_err], device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        chk_err, e2e_err = float(t[0].item()), float(t[1].item())
+    check = {"rel_fro": chk_err, "rows": chk_rows * world, "tokens": TOK, "tolerance": tol,
+             "against": "float64 dot products of the densified weight rows; every rank checks rows of C that another rank produced, read from its own buffer"
+                        if world > 1 else "float64 dot products of the densified weight rows",
+             "e2e_rel_fro_vs_device_result": e2e_err, "max_over_ranks": True}
+    failed = not (chk_err <= tol and e2e_err <= tol)
 
     result = None
     if rank == 0:
@@ -456,21 +528,26 @@ def run_ours(args):
                 del layer, panels, x, y_dev
                 torch.cuda.empty_cache()
             sweep = sweep_table(torch, ops, nat, dev, peaks, fma.value)
-        dt, flops, kind, cores, desc = time_cpu(args.workload, 3, 1)
-        cpu = {"value": flops / dt / 1e9, "unit": UNIT, "cores": cores, "kind": kind, "sample": desc + ", 3 timed passes"}
+        cpu = None
+        if world == 1:  # the CPU baseline is reported at N = 1 only; `bench.py --impl reference` times it at every N
+            dt, flops, kind, cores, desc = time_cpu(args.workload, 3, 1)
+            cpu = {"value": flops / dt / 1e9, "unit": UNIT, "cores": cores, "kind": kind, "sample": desc + ", 3 timed passes"}
         result = {
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
             "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": scaling, "vs_baseline": None,
             "dtype": dtype_name, "data": "synthetic", "config": config_dict(args.workload, world, exchange_used if args.workload == "sharded" else "none", rounds if args.workload == "sharded" else 1),
             "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
             "gpu_launches": args.steps * launches_per_step, "clocks": clocks, "roofline": roofline, "cpu_baseline": cpu,
-            "fp32_fma_peak_tflops": fma.value, "sweep": sweep,
+            "fp32_fma_peak_tflops": fma.value, "sweep": sweep, "check": check,
         }
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()
     if result is not None:
         print(json.dumps(result))
+    if failed:
+        print(f"output check failed: rel. Frobenius error {chk_err:.3e} (end to end {e2e_err:.3e}) above {tol}", file=sys.stderr)
+        return 1
     return 0
 
 
@@ -569,7 +646,7 @@ def run_encoder(args):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="sharded", choices=["sharded", "sweep", "encoder"])

@@ -151,7 +151,9 @@ int nmg_spmm_replicated(const void *val, const int16_t *idx, int64_t M, int64_t 
  *   - every GPU that loads the library holds the array until the process exits;
  *   - all calls on a device share it: calls that overlap in time on one GPU race and must be serialised by the caller;
  *   - the first call on a device resolves the array's address and clears its status word (synchronous); make
- *     it before any stream capture begins.
+ *     it before any stream capture begins;
+ *   - its kernels report a bounded wait that ran out in the first word of that array, not in the allocated status
+ *     word of the other entry points; nmg_read_status reads both and itself allocates nothing.
  * Calls no cudaMalloc / cudaFree and no allocating library routine. */
 #define NMG_NOALLOC_SCRATCH_BYTES (32u << 20)
 int nmg_spmm_noalloc(const void *val, const int16_t *idx, int64_t M, int64_t K, int n, int m, int g, int dtype,
@@ -175,9 +177,18 @@ int nmg_measure_fma_peak(double *tflops_out, void *stream);
 int nmg_memcpy_2d_async(void *dst, size_t dst_pitch, const void *src, size_t src_pitch, size_t width_bytes, size_t rows,
                         void *stream);
 
-/* Device-side status word of the last kernels launched by this thread on the current device: 0 when every
- * bounded wait completed.  Synchronises the given stream. */
+/* Device-side status of the kernels launched so far on the current device: 0 when every bounded wait completed, else
+ * the code of a wait that ran out (returned as NMG_ERR_TIMEOUT, and cleared).  Covers the status word of the
+ * workspace-taking entry points and the one nmg_spmm_noalloc keeps in its built-in array.  Synchronises the given
+ * stream; allocates nothing. */
 int nmg_read_status(void *stream, int *status_out);
+
+/* Self-test of the bounded device-side waits (no counterpart in the reference, whose kernels have no waits): launches a
+ * one-CTA kernel whose only thread waits on an mbarrier that nothing arrives at, with the same bounded wait every kernel
+ * of the library uses but a limit of `limit_ns` nanoseconds (1 .. 1e9).  The wait runs out, the kernel records code 90 in
+ * the status word and returns normally; the next nmg_read_status reports NMG_ERR_TIMEOUT once and clears it.  Nothing
+ * faults or hangs: this is how the time-out path is exercised. */
+int nmg_selftest_wait(uint64_t limit_ns, void *stream);
 
 #ifdef __cplusplus
 }

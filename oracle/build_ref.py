@@ -18,7 +18,8 @@ The reference compiles with ``-march=native`` (native_scripting.py:50).  The obj
 on a different host, so the ISA is named explicitly (``-mavx2 -mfma`` or ``-mavx512f``) and picked at load
 time from the CPU flags the same way the reference picks it (grouped_nm_tensor.py:893-897).
 
-Usage:  python oracle/build_ref.py [--reference /path/to/reference]     (builds the default problem list)
+Usage:  python oracle/build_ref.py --reference /path/to/reference     (builds the default problem list; the path may
+        also come from the environment variable NMG_REFERENCE_ROOT)
 """
 import argparse
 import ctypes
@@ -43,6 +44,7 @@ DEFAULT_PROBLEMS = [
 
 DRIVER = r"""
 #include <immintrin.h>
+#include <omp.h>
 #include <cstdint>
 #include <cstdlib>
 #include <cstring>
@@ -61,6 +63,9 @@ static inline void tile_rem(const float* ptr_a_val, const int16_t* ptr_a_idx, fl
 }
 
 extern "C" int nmg_ref_tokens_per_block() { return V4; }
+// OpenMP team size, stated by the caller instead of inherited from OMP_NUM_THREADS (launchers export 1 for their workers)
+extern "C" void nmg_ref_set_threads(int n) { if (n > 0) omp_set_num_threads(n); }
+extern "C" int nmg_ref_num_threads() { return omp_get_max_threads(); }
 
 // out[tok][Mp] = X[tok][K] * densify(A)^T ; ntok must be a multiple of V4 (dace_gnm_mult.py:605-606)
 extern "C" int nmg_ref_spmm(const int16_t* A_idx, const float* A_val, const float* X, float* out,
@@ -145,7 +150,27 @@ def build_one(gen_mod, n, m, g, K, isa, verbose=False):
     return out
 
 
-def build_all(ref_root="/root/reference", problems=None, verbose=False):
+def reference_root(explicit=None):
+    """Path of the reference tree: the argument, else $NMG_REFERENCE_ROOT; None when neither names a tree."""
+    root = explicit or os.environ.get("NMG_REFERENCE_ROOT")
+    return root if root and os.path.isdir(os.path.join(root, "src", "sten")) else None
+
+
+def is_current():
+    """Whether oracle/_ref holds every default problem, built from this version of the driver."""
+    isa = host_isa()
+    for (n, m, g, K) in DEFAULT_PROBLEMS:
+        path = os.path.join(OUT_DIR, lib_name(n, m, g, K, isa))
+        if not os.path.isfile(path):
+            return False
+        try:
+            ctypes.CDLL(path).nmg_ref_set_threads
+        except (OSError, AttributeError):
+            return False
+    return True
+
+
+def build_all(ref_root, problems=None, verbose=False):
     gen_mod = import_reference(ref_root)
     built = []
     for (n, m, g, K) in problems or DEFAULT_PROBLEMS:
@@ -176,7 +201,21 @@ def load(n, m, g, K, isa=None):
     L.nmg_ref_spmm.restype = ctypes.c_int
     L.nmg_ref_spmm.argtypes = [ctypes.c_void_p] * 4 + [ctypes.c_int64, ctypes.c_int64]
     L.nmg_ref_tokens_per_block.restype = ctypes.c_int
+    L.nmg_ref_set_threads.argtypes = [ctypes.c_int]
+    L.nmg_ref_set_threads.restype = None
+    if _THREADS:
+        L.nmg_ref_set_threads(_THREADS)
     return L.nmg_ref_spmm, int(L.nmg_ref_tokens_per_block())
+
+
+_THREADS = 0
+
+
+def set_threads(n):
+    """OpenMP team size for every kernel loaded from now on (each shared object carries the same OpenMP runtime, so one
+    call per load is enough)."""
+    global _THREADS
+    _THREADS = int(n)
 
 
 def spmm(val, idx, x, M, K, n, m, g, isa=None):
@@ -204,8 +243,11 @@ def spmm(val, idx, x, M, K, n, m, g, isa=None):
 
 if __name__ == "__main__":
     ap = argparse.ArgumentParser()
-    ap.add_argument("--reference", default="/root/reference")
+    ap.add_argument("--reference", default=None, help="root of the reference tree (or set NMG_REFERENCE_ROOT)")
     ap.add_argument("-v", "--verbose", action="store_true")
     a = ap.parse_args()
-    for pth in build_all(a.reference, verbose=a.verbose):
+    root = reference_root(a.reference)
+    if root is None:
+        ap.error("no reference tree: pass --reference or set NMG_REFERENCE_ROOT")
+    for pth in build_all(root, verbose=a.verbose):
         print(pth)

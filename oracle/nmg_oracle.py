@@ -71,6 +71,8 @@ def lib():
         L.nmg_oracle_spmm_f32.restype = ci
         L.nmg_oracle_spmm_f32.argtypes = [vp, vp, vp, i64, i64, i64, i64, ci, ci, ci, vp, i64]
         L.nmg_oracle_num_threads.restype = ci
+        L.nmg_oracle_set_threads.restype = None
+        L.nmg_oracle_set_threads.argtypes = [ci]
         _LIB = L
     return _LIB
 
@@ -81,6 +83,11 @@ def _p(a):
 
 def num_threads():
     return int(lib().nmg_oracle_num_threads())
+
+
+def set_threads(n):
+    """OpenMP team size of the following calls (explicit, so that an inherited OMP_NUM_THREADS=1 does not decide it)."""
+    lib().nmg_oracle_set_threads(int(n))
 
 
 def order(n, m):

@@ -1,16 +1,19 @@
 """Run one kernel of the library a few times on a seeded problem, for use under a profiler.
 
-    python -m sten_b200.profile_case --op fwd --nm 2:4 --g 16 --rows 4096 --cols 4096 --tokens 4096 --dtype f32 --reps 3
+    python profile_case.py --op fwd --nm 2:4 --g 16 --rows 4096 --cols 4096 --tokens 4096 --dtype f32 --reps 3
 
 ``--op`` is one of ``fwd`` (y = x W^T), ``fwd_kmajor`` (C = W B), ``bwd`` (dX = dY W), ``sparsify``, ``densify``.
 Prints the mean device time per call measured with CUDA events (meaningless under a profiler, useful without).
 """
 import argparse
+import os
+import sys
 
 import torch
 
-from . import _native as nat
-from . import ops
+sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
+from sten_b200 import _native as nat  # noqa: E402
+from sten_b200 import ops  # noqa: E402
 
 
 def main():

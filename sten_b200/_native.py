@@ -39,6 +39,7 @@ SIGNATURES = {
     "nmg_measure_fma_peak": (_int, [ctypes.POINTER(ctypes.c_double), _vp]),
     "nmg_memcpy_2d_async": (_int, [_vp, _sz, _vp, _sz, _sz, _sz, _vp]),
     "nmg_read_status": (_int, [_vp, ctypes.POINTER(_int)]),
+    "nmg_selftest_wait": (ctypes.c_int, [ctypes.c_uint64, _vp]),
 }
 
 _lib = None

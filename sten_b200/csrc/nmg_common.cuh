@@ -87,6 +87,8 @@ ProfileEvents take_profile_events();
 
 // One int per device that kernels set to a non-zero code when a bounded wait runs out.
 int get_status_word(int **dev_ptr);
+// Status word of nmg_spmm_noalloc on device `dev` (start of the built-in scratch array), or NULL before its first call there.
+int *noalloc_status_word(int dev);
 
 // ------------------------------------------------------------------------------------------------ dtypes
 template <typename T> struct DT;
@@ -146,13 +148,14 @@ __device__ __forceinline__ uint64_t global_timer_ns() {
     asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
     return t;
 }
-__device__ __forceinline__ bool mbar_wait_bounded(uint64_t *bar, uint32_t parity, int *status, int code) {
+__device__ __forceinline__ bool mbar_wait_bounded(uint64_t *bar, uint32_t parity, int *status, int code,
+                                                  uint64_t limit_ns = kWaitLimitNs) {
     if (mbar_try_wait(bar, parity)) return true;
     const uint64_t t0 = global_timer_ns();
     for (;;) {
         for (int i = 0; i < 64; i++)
             if (mbar_try_wait(bar, parity)) return true;
-        if (global_timer_ns() - t0 > kWaitLimitNs) break;
+        if (global_timer_ns() - t0 > limit_ns) break;
     }
     if (status) atomicExch(status, code);
     return false;

@@ -224,7 +224,6 @@ struct GemmParams {
     int out_token_major;
     int out_staged;    // feature-major output whose rows are 16-byte aligned: go through the staging tile
     int tiles_f, tiles_t;
-    int debug;         // measurement aid (NMG_TC_DEBUG): bit 0 skips the epilogue's global stores, bit 1 its TMEM reads too; results are garbage
     int *status;
 };
 constexpr int GEMM_STAGING_BYTES = GEMM_DRAIN_WARPS * 4096;  // per drain warp: 32 feature rows x 128 bytes
@@ -368,14 +367,6 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_tc_kernel(const GemmPara
                 const bool last = c == nchunks - 1;
                 // handle(sl, r): slice sl of the unit is in registers r (this lane's feature row, 32 tokens)
                 auto handle = [&](int sl, uint32_t (&r)[32]) {
-                    if ((prm.debug & 1) && last) {
-                        if (sl == sl0 + SLICES - 1) {
-                            tc_fence_before();
-                            __syncwarp();
-                            if (lane == 0) mbar_arrive(&acc_free[b]);
-                        }
-                        return;
-                    }
                     if (SPLIT && c > 0) {
                         uint32_t run[32];
                         tmem_ld32(lane_base + (uint32_t)(TC_ACC_COLS + sl * 32), run);
@@ -463,15 +454,14 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_tc_kernel(const GemmPara
                 // and stored; tmem_ld_fence ties the wait to the registers so no use can move above it.
                 uint32_t ra[32], rb[32];
                 const uint32_t acc_addr = lane_base + (uint32_t)(b * TC_ACC_COLS);
-                const bool skip_ld = (prm.debug & 2) != 0;
-                if (!skip_ld) tmem_ld32_issue(acc_addr + (uint32_t)(sl0 * 32), ra);
+                tmem_ld32_issue(acc_addr + (uint32_t)(sl0 * 32), ra);
 #pragma unroll 1
                 for (int sl = sl0; sl < sl0 + SLICES; sl += 2) {
                     tmem_ld_fence(ra);
-                    if (!skip_ld) tmem_ld32_issue(acc_addr + (uint32_t)((sl + 1) * 32), rb);
+                    tmem_ld32_issue(acc_addr + (uint32_t)((sl + 1) * 32), rb);
                     handle(sl, ra);
                     tmem_ld_fence(rb);
-                    if (sl + 2 < sl0 + SLICES && !skip_ld) tmem_ld32_issue(acc_addr + (uint32_t)((sl + 2) * 32), ra);
+                    if (sl + 2 < sl0 + SLICES) tmem_ld32_issue(acc_addr + (uint32_t)((sl + 2) * 32), ra);
                     handle(sl + 1, rb);
                 }
                 if (!last) {  // promotion finished: hand the accumulator back
@@ -602,8 +592,6 @@ int tc_dense_matmul(const Geo &geo, int dtype, bool transposed, const void *val,
     gp.tiles_f = (int)((rows + TC_BM - 1) / TC_BM);
     gp.tiles_t = (int)((tokens + TC_BN - 1) / TC_BN);
     gp.status = status;
-    static const int debug_flags = [] { const char *e = getenv("NMG_TC_DEBUG"); return e ? atoi(e) : 0; }();
-    gp.debug = debug_flags;
     if (dtype == NMG_F16) return gemm_launch<__half>(gp, maps, st);
     if (dtype == NMG_BF16) return gemm_launch<__nv_bfloat16>(gp, maps, st);
     return gemm_launch<float>(gp, maps, st);

@@ -51,6 +51,12 @@ static int noalloc_scratch(unsigned char **out) {
     return NMG_OK;
 }
 
+int *noalloc_status_word(int dev) {
+    if (dev < 0 || dev >= kMaxDevices) return nullptr;
+    std::lock_guard<std::mutex> lk(g_noalloc_mu);
+    return reinterpret_cast<int *>(g_noalloc_ptr[dev]);
+}
+
 }  // namespace nmg
 
 using namespace nmg;

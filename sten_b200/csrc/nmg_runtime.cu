@@ -88,6 +88,13 @@ int get_status_word(int **dev_ptr) {
     return NMG_OK;
 }
 
+// The status word of the current device if one exists already, else NULL; never allocates.
+static int *peek_status_word(int dev) {
+    std::lock_guard<std::mutex> lk(g_mu);
+    auto it = g_status.find(dev);
+    return it == g_status.end() ? nullptr : it->second;
+}
+
 // ------------------------------------------------------------------------------------------------ tensor maps
 typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
                                   const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
@@ -160,21 +167,53 @@ int nmg_memcpy_2d_async(void *dst, size_t dst_pitch, const void *src, size_t src
     return NMG_OK;
 }
 
+// Two words can exist per device: the allocated one every workspace-taking entry point hands to its kernels, and the
+// first word of the built-in scratch array that nmg_spmm_noalloc uses.  Both are read (whichever exist); nothing is
+// allocated here, so a caller that only ever uses nmg_spmm_noalloc can still ask for the status.
 int nmg_read_status(void *stream, int *status_out) {
     if (!status_out) NMG_FAIL(NMG_ERR_INVALID, "status_out is NULL");
-    int *dev = nullptr;
-    int rc = nmg::get_status_word(&dev);
-    if (rc) return rc;
-    NMG_CUDA(cudaMemcpyAsync(status_out, dev, sizeof(int), cudaMemcpyDeviceToHost, (cudaStream_t)stream));
-    NMG_CUDA(cudaStreamSynchronize((cudaStream_t)stream));
+    int dev = 0;
+    NMG_CUDA(cudaGetDevice(&dev));
+    int *words[2] = {nmg::peek_status_word(dev), nmg::noalloc_status_word(dev)};
+    int codes[2] = {0, 0};
+    cudaStream_t st = (cudaStream_t)stream;
+    for (int i = 0; i < 2; i++)
+        if (words[i]) NMG_CUDA(cudaMemcpyAsync(&codes[i], words[i], sizeof(int), cudaMemcpyDeviceToHost, st));
+    NMG_CUDA(cudaStreamSynchronize(st));
+    *status_out = codes[0] ? codes[0] : codes[1];
     if (*status_out != 0) {
-        NMG_CUDA(cudaMemsetAsync(dev, 0, sizeof(int), (cudaStream_t)stream));
+        for (int i = 0; i < 2; i++)
+            if (words[i] && codes[i]) NMG_CUDA(cudaMemsetAsync(words[i], 0, sizeof(int), st));
         NMG_FAIL(NMG_ERR_TIMEOUT, "a device-side bounded wait ran out (code %d)", *status_out);
     }
     return NMG_OK;
 }
 
 }  // extern "C"
+
+// ------------------------------------------------------------------------------------------------ wait self-test
+namespace nmg {
+// One thread waits, with the library's bounded wait, on an mbarrier that nothing ever arrives at.  The wait gives up after
+// `limit_ns`, records code 90 in the status word and the kernel returns normally.
+__global__ void selftest_wait_kernel(int *status, unsigned long long limit_ns) {
+    __shared__ uint64_t bar;
+    if (threadIdx.x == 0) {
+        mbar_init(&bar, 1);
+        mbar_fence_init();
+        mbar_wait_bounded(&bar, 0, status, 90, limit_ns);
+    }
+}
+}  // namespace nmg
+
+extern "C" int nmg_selftest_wait(uint64_t limit_ns, void *stream) {
+    if (limit_ns == 0 || limit_ns > 1000000000ull) NMG_FAIL(NMG_ERR_INVALID, "limit_ns must be between 1 and 1e9 (one second)");
+    int *status = nullptr;
+    int rc = nmg::get_status_word(&status);
+    if (rc) return rc;
+    nmg::selftest_wait_kernel<<<1, 32, 0, (cudaStream_t)stream>>>(status, (unsigned long long)limit_ns);
+    NMG_CUDA(cudaGetLastError());
+    return NMG_OK;
+}
 
 // ------------------------------------------------------------------------------------------------ fp32 FMA peak
 namespace nmg {

@@ -37,7 +37,6 @@ struct TcParams {
     float *partial;       // [ksplit][tiles_f * 128][ld_partial] fp32, feature-major
     int64_t ld_partial;
     int *status;
-    int debug;            // measurement aid (NMG_TC_DEBUG): bit 0 skips the expansion stores, bit 1 the TMA loads; results are garbage
 };
 
 // ---- weight-tile expansion ------------------------------------------------------------------------------
@@ -376,7 +375,6 @@ spmm_tc_kernel(const TcParams prm, const __grid_constant__ CUtensorMap tmap0, co
                 const int s = kb % TC_STAGES;
                 const uint32_t ph = (uint32_t)((kb / TC_STAGES) & 1);
                 if (!mbar_wait_bounded(&empty[s], ph ^ 1, prm.status, 11)) break;
-                if ((prm.debug & 2) && kb >= TC_STAGES) { mbar_arrive(&full_b[s]); continue; }
                 mbar_expect_tx(&full_b[s], TC_B_BYTES);
                 const int xc = TERMS == 1 ? 0 : kSplitX[kb % TERMS];
                 const CUtensorMap *tm = xc == 0 ? &tmap0 : (xc == 1 ? &tmap1 : &tmap2);
@@ -433,19 +431,18 @@ spmm_tc_kernel(const TcParams prm, const __grid_constant__ CUtensorMap tmap0, co
                     }
                 }
                 if (!mbar_wait_bounded(&empty[s], ph ^ 1, prm.status, 14)) return false;
-                if (!((prm.debug & 1) && kb >= TC_STAGES)) write(buf, a_stages + s * TC_A_BYTES);
+                write(buf, a_stages + s * TC_A_BYTES);
                 fence_proxy_async_smem();  // generic-proxy stores -> visible to the tensor core's async-proxy reads
                 mbar_arrive(&full_a[s]);
                 return true;
             };
-            const bool nofetch = (prm.debug & 4) != 0;
             if (group < nkb) fetch(buf_a, group);
             for (int kb = group; kb < nkb; kb += 2 * GROUPS) {
-                if (kb + GROUPS < nkb && !nofetch) fetch(buf_b, kb + GROUPS);
+                if (kb + GROUPS < nkb) fetch(buf_b, kb + GROUPS);
                 if (!publish(kb, buf_a)) break;
                 if (kb + GROUPS >= nkb) break;
-                if (kb + 2 * GROUPS < nkb && !nofetch) fetch(buf_a, kb + 2 * GROUPS);
-                if (!publish(kb + GROUPS, nofetch ? buf_a : buf_b)) break;
+                if (kb + 2 * GROUPS < nkb) fetch(buf_a, kb + 2 * GROUPS);
+                if (!publish(kb + GROUPS, buf_b)) break;
             }
         };
         if (TRANSPOSED) {
@@ -473,330 +470,6 @@ spmm_tc_kernel(const TcParams prm, const __grid_constant__ CUtensorMap tmap0, co
     if (warp == 1) {
         tc_fence_after();
         tmem_dealloc(tmem_base, TMEM_COLS);
-    }
-}
-
-// =========================================================================================================
-// Two-CTA variant (thread-block cluster of 2, tcgen05 cta_group::2).
-//
-// With one CTA per 128 x 256 tile the shared-memory ports carry, per k-block, the tensor core's operand reads
-// (48 KB), the TMA writes of the activation tile (32 KB) and the expansion stores (16 KB): 96 KB per 512 ideal MMA
-// clocks, well above what one SM's shared memory sustains, and the kernel tops out near 65 % of the dense peak.
-// Here two CTAs on neighbouring SMs form one 256 x 256 tile: each expands its own 128 weight rows and loads only
-// HALF of the activation tile (128 tokens); the MMA (M = 256, issued by the even CTA) reads both halves from both
-// shared memories.  Per SM and k-block that is 32 KB of operand reads + 16 KB TMA + 16 KB expansion stores.
-//
-// Barrier topology: `full[s]` lives in the even ("leader") CTA and collects, per stage, the expansion warps of both
-// CTAs (remote mbarrier arrives), the TMA bytes of both CTAs (both loads name the leader's barrier) and the
-// leader's expect_tx.  `empty[s]`, `chunk_done` exist in both CTAs and are signalled by multicast tcgen05.commit.
-// `promoted` (fp32 mode) lives in the leader and collects the draining warps of both CTAs.
-// Every wait is bounded and every thread reaches the closing cluster barrier, also after a failed wait.
-constexpr int TC2_STAGES = 6;
-constexpr int TC2_B_BYTES = 128 * TC_BK * 2;  // this CTA's half of the activation tile: 128 tokens x 64 elements
-
-__device__ __forceinline__ uint32_t cluster_ctarank() {
-    uint32_t r;
-    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
-    return r;
-}
-__device__ __forceinline__ void cluster_sync_all() {
-    asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
-    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
-}
-// shared::cluster address of `local` (a shared::cta address of this CTA) in the CTA with the given cluster rank
-__device__ __forceinline__ uint32_t map_to_rank(uint32_t local, uint32_t rank) {
-    uint32_t r;
-    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(local), "r"(rank));
-    return r;
-}
-__device__ __forceinline__ void mbar_arrive_remote(uint32_t cluster_addr) {
-    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
-}
-__device__ __forceinline__ bool mbar_try_wait_cluster(uint64_t *bar, uint32_t parity) {
-    uint32_t ok;
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n\t"
-        "selp.u32 %0, 1, 0, p;\n\t}"
-        : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
-    return ok != 0;
-}
-__device__ __forceinline__ bool mbar_wait_cluster_bounded(uint64_t *bar, uint32_t parity, int *status, int code) {
-    if (mbar_try_wait_cluster(bar, parity)) return true;
-    const uint64_t t0 = global_timer_ns();
-    for (;;) {
-        for (int i = 0; i < 64; i++)
-            if (mbar_try_wait_cluster(bar, parity)) return true;
-        if (global_timer_ns() - t0 > kWaitLimitNs) break;
-    }
-    if (status) atomicExch(status, code);
-    return false;
-}
-__device__ __forceinline__ void tma_load_2d_pair(void *smem_dst, const CUtensorMap *map, int x, int y, uint32_t bar_cluster_addr) {
-    asm volatile(
-        "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
-        ::"r"(smem_u32(smem_dst)), "l"(map), "r"(x), "r"(y), "r"(bar_cluster_addr)
-        : "memory");
-}
-__device__ __forceinline__ void tc2_commit_both(uint64_t *bar) {
-    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
-                 ::"r"(smem_u32(bar)), "h"((uint16_t)3) : "memory");
-}
-__device__ __forceinline__ void tc2_mma_f16(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "setp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}"
-        ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
-        : "memory");
-}
-__device__ __forceinline__ void tmem_alloc_pair(uint32_t *smem_slot, uint32_t cols) {
-    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(smem_slot)), "r"(cols) : "memory");
-    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
-}
-__device__ __forceinline__ void tmem_dealloc_pair(uint32_t taddr, uint32_t cols) {
-    asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(cols) : "memory");
-}
-template <typename E> __device__ __forceinline__ uint32_t make_idesc_pair() {  // M = 256 across the pair, N = 256
-    const uint32_t fmt = DT<E>::id == NMG_BF16 ? 1u : 0u;
-    return (1u << 4) | (fmt << 7) | (fmt << 10) | ((uint32_t)(256 >> 3) << 17) | ((uint32_t)(256 >> 4) << 24);
-}
-
-template <int N_, int M_, typename T, bool TRANSPOSED>
-__global__ void __launch_bounds__(TC_THREADS, 1)
-spmm_tc2_kernel(const TcParams prm, const __grid_constant__ CUtensorMap tmap0, const __grid_constant__ CUtensorMap tmap1,
-                const __grid_constant__ CUtensorMap tmap2) {
-    constexpr int TERMS = TcMode<T>::TERMS;
-    using E = typename TcMode<T>::elem;
-    static_assert((3 * TC2_STAGES + 2) * 8 <= 248, "barrier block too small");
-    static_assert(TC_BM % (4 * M_) == 0 && TC_BK % M_ == 0 && M_ % 4 == 0 && N_ <= 2, "tile must hold whole row-blocks");
-    constexpr Order<N_, M_> ORD{};
-    constexpr int C = Order<N_, M_>::C;
-    constexpr bool SPLIT = TERMS > 1;
-    constexpr int GROUPS = 3;
-    constexpr uint32_t TMEM_COLS = SPLIT ? 2 * TC_ACC_COLS : TC_ACC_COLS;
-
-    extern __shared__ char smem_raw[];
-    char *smem = reinterpret_cast<char *>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
-    char *a_stages = smem;
-    char *b_stages = smem + TC2_STAGES * TC_A_BYTES;
-    char *misc = smem + TC2_STAGES * (TC_A_BYTES + TC2_B_BYTES);
-    uint64_t *full = reinterpret_cast<uint64_t *>(misc);  // meaningful in the leader only
-    uint64_t *empty = full + TC2_STAGES;
-    uint64_t *chunk_done = empty + TC2_STAGES;
-    uint64_t *promoted = chunk_done + 1;                    // leader only
-    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(misc + 248);
-    uint16_t *sel = reinterpret_cast<uint16_t *>(misc + 256);
-
-    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const uint32_t rank = cluster_ctarank();
-    const bool leader = rank == 0;
-    int tile_f, tile_t;
-    tile_of_cta((int)(blockIdx.x >> 1), prm.tiles_f, prm.tiles_t, tile_f, tile_t);  // tiles_f counts 256-feature tiles here
-    const int64_t tok0 = (int64_t)tile_t * TC_BN;
-    const int64_t feat0 = (int64_t)tile_f * 256 + (int64_t)rank * TC_BM;
-    const int nkb = (int)((prm.red + TC_BK - 1) / TC_BK) * TERMS;
-    const int chunk_it = SPLIT ? TC_CHUNK_KB * TERMS : nkb;
-    const int nchunks = (nkb + chunk_it - 1) / chunk_it;
-
-    if (tid == 0) {
-        for (int s = 0; s < TC2_STAGES; s++) {
-            mbar_init(&full[s], 8 + 1);  // 4 expansion warps of each CTA + the leader's expect_tx arrive
-            mbar_init(&empty[s], 1);
-        }
-        mbar_init(chunk_done, 1);
-        mbar_init(promoted, 8);          // 4 draining warps of each CTA
-        mbar_fence_init();
-    }
-    for (int e = tid; e < C * (M_ / 2); e += TC_THREADS) {
-        const int p = e / (M_ / 2), q = e - p * (M_ / 2);
-        uint32_t code = 0;
-        for (int h = 0; h < 2; h++) {
-            uint32_t nib = 0x44;
-            for (int sl = 0; sl < N_; sl++)
-                if (ORD.v[p * Order<N_, M_>::LD + sl] == 2 * q + h) nib = sl == 0 ? 0x10 : 0x32;
-            code |= nib << (8 * h);
-        }
-        sel[e] = (uint16_t)code;
-    }
-    if (warp == 1) tmem_alloc_pair(tmem_slot, TMEM_COLS);
-    tc_fence_before();
-    __syncthreads();
-    cluster_sync_all();  // barriers of both CTAs are initialised before anyone arrives remotely
-    tc_fence_after();
-    const uint32_t tmem_base = *tmem_slot;
-    const uint32_t full_leader0 = map_to_rank(smem_u32(&full[0]), 0);      // cluster address of the leader's full[0]
-    const uint32_t promoted_leader = map_to_rank(smem_u32(promoted), 0);
-
-    auto store_slice = [&](const uint32_t (&r)[32], int sl, int64_t feat, float b) {
-        T *out = static_cast<T *>(prm.out);
-        const int64_t tokc = tok0 + sl * 32;
-        const bool vec = !prm.out_token_major && tokc + 32 <= prm.ntok && (prm.ld_out % (16 / (int)sizeof(T))) == 0 &&
-                         (reinterpret_cast<uintptr_t>(out) & 15) == 0;
-        if (vec) {
-            uint4 *dst = reinterpret_cast<uint4 *>(out + feat * prm.ld_out + tokc);
-            if constexpr (sizeof(T) == 4) {
-#pragma unroll
-                for (int v = 0; v < 8; v++)
-                    dst[v] = make_uint4(__float_as_uint(__uint_as_float(r[4 * v]) + b), __float_as_uint(__uint_as_float(r[4 * v + 1]) + b),
-                                        __float_as_uint(__uint_as_float(r[4 * v + 2]) + b), __float_as_uint(__uint_as_float(r[4 * v + 3]) + b));
-            } else {
-#pragma unroll
-                for (int v = 0; v < 4; v++) {
-                    uint32_t w[4];
-#pragma unroll
-                    for (int h = 0; h < 4; h++) {
-                        const T lo = DT<T>::from_f32(__uint_as_float(r[8 * v + 2 * h]) + b);
-                        const T hi = DT<T>::from_f32(__uint_as_float(r[8 * v + 2 * h + 1]) + b);
-                        w[h] = (uint32_t)bits16<T>(lo) | ((uint32_t)bits16<T>(hi) << 16);
-                    }
-                    dst[v] = make_uint4(w[0], w[1], w[2], w[3]);
-                }
-            }
-        } else {
-#pragma unroll
-            for (int j = 0; j < 32; j++) {
-                const int64_t tok = tokc + j;
-                if (tok < prm.ntok) {
-                    const T o = DT<T>::from_f32(__uint_as_float(r[j]) + b);
-                    if (prm.out_token_major) out[tok * prm.ld_out + feat] = o;
-                    else out[feat * prm.ld_out + tok] = o;
-                }
-            }
-        }
-    };
-    // Drain one accumulation chunk of this CTA's 128 x 256 accumulator (see the one-CTA kernel).
-    auto drain_chunk = [&](int c) -> bool {
-        const int q = warp & 3;
-        const int64_t feat = feat0 + q * 32 + lane;
-        const bool feat_ok = feat < prm.out_feats;
-        const float b = (prm.bias && feat_ok) ? DT<T>::to_f32(static_cast<const T *>(prm.bias)[feat]) : 0.f;
-        const uint32_t lane_base = tmem_base + ((uint32_t)(q * 32) << 16);
-        if (!mbar_wait_cluster_bounded(chunk_done, (uint32_t)(c & 1), prm.status, 25)) return false;
-        tc_fence_after();
-        const bool last = c == nchunks - 1;
-        for (int sl = 0; sl < TC_BN / 32; sl++) {
-            uint32_t r[32];
-            tmem_ld32(lane_base + (uint32_t)(sl * 32), r);
-            if (SPLIT && c > 0) {
-                uint32_t run[32];
-                tmem_ld32(lane_base + (uint32_t)(TC_ACC_COLS + sl * 32), run);
-#pragma unroll
-                for (int j = 0; j < 32; j++) r[j] = __float_as_uint(__fadd_rn(__uint_as_float(run[j]), __uint_as_float(r[j])));
-            }
-            if (!last) {
-                tmem_st32(lane_base + (uint32_t)(TC_ACC_COLS + sl * 32), r);
-                continue;
-            }
-            if (tok0 + sl * 32 < prm.ntok && feat_ok) store_slice(r, sl, feat, b);
-        }
-        tc_fence_before();
-        if (!last) {
-            __syncwarp();
-            if (lane == 0) mbar_arrive_remote(promoted_leader);
-        }
-        return true;
-    };
-
-    if (warp == 0) {
-        // ------------------------------------------------------------------ TMA producer (one lane per CTA)
-        if (lane == 0) {
-            for (int kb = 0; kb < nkb; kb++) {
-                const int s = kb % TC2_STAGES;
-                const uint32_t ph = (uint32_t)((kb / TC2_STAGES) & 1);
-                if (!mbar_wait_cluster_bounded(&empty[s], ph ^ 1, prm.status, 21)) break;
-                if ((prm.debug & 2) && kb >= TC2_STAGES) {  // measurement aid: no load, only the leader's arrival
-                    if (leader) mbar_arrive(&full[s]);
-                    continue;
-                }
-                if (leader) mbar_expect_tx(&full[s], 2 * TC2_B_BYTES);  // both halves report to this barrier
-                const int xc = TERMS == 1 ? 0 : kSplitX[kb % TERMS];
-                const CUtensorMap *tm = xc == 0 ? &tmap0 : (xc == 1 ? &tmap1 : &tmap2);
-                tma_load_2d_pair(b_stages + s * TC2_B_BYTES, tm, (kb / TERMS) * TC_BK, (int)(tok0 + rank * 128), full_leader0 + s * 8);
-            }
-        }
-    } else if (warp == 1) {
-        // ------------------------------------------------------------------ MMA issuer (one lane of the leader)
-        if (leader && lane == 0) {
-            const uint32_t idesc = make_idesc_pair<E>();
-            bool ok = true;
-            int chunk = 0, in_chunk = 0;
-            for (int kb = 0; kb < nkb && ok; kb++) {
-                const int s = kb % TC2_STAGES;
-                const uint32_t ph = (uint32_t)((kb / TC2_STAGES) & 1);
-                const bool first = in_chunk == 0;
-                if (first && chunk > 0) ok = mbar_wait_cluster_bounded(promoted, (uint32_t)((chunk - 1) & 1), prm.status, 26);
-                ok = ok && mbar_wait_cluster_bounded(&full[s], ph, prm.status, 22);
-                if (!ok) break;
-                tc_fence_after();
-                const uint64_t adesc = make_sw128_desc(smem_u32(a_stages + s * TC_A_BYTES));
-                const uint64_t bdesc = make_sw128_desc(smem_u32(b_stages + s * TC2_B_BYTES));
-#pragma unroll
-                for (int k = 0; k < TC_BK / 16; k++)
-                    tc2_mma_f16(tmem_base, adesc + 2 * k, bdesc + 2 * k, idesc, (first && k == 0) ? 0u : 1u);
-                tc2_commit_both(&empty[s]);
-                if (++in_chunk == chunk_it || kb + 1 == nkb) {
-                    tc2_commit_both(chunk_done);
-                    in_chunk = 0;
-                    chunk++;
-                }
-            }
-            if (!ok) tc2_commit_both(chunk_done);
-        }
-    } else {
-        // ------------------------------------------------------------------ expansion groups (both CTAs)
-        const int group = (warp - 2) >> 2;
-        const int gwarp = (warp - 2) & 3;
-        const int gtid = tid - 64 - group * 128;
-        int drained = 0;
-        auto run_group = [&](auto fetch, auto write, auto &buf_a, auto &buf_b) {
-            auto publish = [&](int kb, auto &buf) -> bool {
-                const int s = kb % TC2_STAGES;
-                const uint32_t ph = (uint32_t)((kb / TC2_STAGES) & 1);
-                if (SPLIT && group == 0) {
-                    while (drained < kb / chunk_it) {
-                        if (!drain_chunk(drained)) return false;
-                        drained++;
-                    }
-                }
-                if (!mbar_wait_cluster_bounded(&empty[s], ph ^ 1, prm.status, 24)) return false;
-                if (!((prm.debug & 1) && kb >= TC2_STAGES)) write(buf, a_stages + s * TC_A_BYTES);
-                fence_proxy_async_smem();
-                __syncwarp();
-                if (lane == 0) mbar_arrive_remote(full_leader0 + s * 8);
-                return true;
-            };
-            const bool nofetch = (prm.debug & 4) != 0;
-            if (group < nkb) fetch(buf_a, group);
-            for (int kb = group; kb < nkb; kb += 2 * GROUPS) {
-                if (kb + GROUPS < nkb && !nofetch) fetch(buf_b, kb + GROUPS);
-                if (!publish(kb, buf_a)) break;
-                if (kb + GROUPS >= nkb) break;
-                if (kb + 2 * GROUPS < nkb && !nofetch) fetch(buf_a, kb + 2 * GROUPS);
-                if (!publish(kb + GROUPS, nofetch ? buf_a : buf_b)) break;
-            }
-        };
-        if (TRANSPOSED) {
-            TrRegs<N_, M_> ra, rb;
-            run_group([&](TrRegs<N_, M_> &t, int it) {
-                          fetch_transposed<N_, M_>(t, prm, prm.nval[TERMS == 1 ? 0 : kSplitW[it % TERMS]], feat0, it / TERMS, gtid);
-                      },
-                      [&](const TrRegs<N_, M_> &t, char *tile) { write_transposed<N_, M_>(t, tile, sel, gtid); }, ra, rb);
-        } else {
-            FwdRegs<N_, M_> ra, rb;
-            run_group([&](FwdRegs<N_, M_> &t, int it) {
-                          fetch_forward<N_, M_>(t, prm, prm.nval[TERMS == 1 ? 0 : kSplitW[it % TERMS]], feat0, it / TERMS, gwarp, lane);
-                      },
-                      [&](const FwdRegs<N_, M_> &t, char *tile) { write_forward<N_, M_>(t, tile, sel, gwarp, lane); }, ra, rb);
-        }
-        if (group == 0)
-            while (drained < nchunks && drain_chunk(drained)) drained++;
-    }
-    __syncthreads();
-    cluster_sync_all();  // the peer no longer reads this CTA's shared memory or signals its barriers
-    if (warp == 1) {
-        tc_fence_after();
-        tmem_dealloc_pair(tmem_base, TMEM_COLS);
     }
 }
 
@@ -920,39 +593,6 @@ static int tc_launch_one(const TcParams &p, const CUtensorMap *tm, cudaStream_t 
     return NMG_OK;
 }
 
-static size_t tc2_smem_bytes(int C) {
-    return (size_t)TC2_STAGES * (TC_A_BYTES + TC2_B_BYTES) + 256 + (size_t)C * 16 + 1024;
-}
-
-template <int N_, int M_, typename T, bool TR>
-static int tc2_launch_one(const TcParams &p, const CUtensorMap *tm, cudaStream_t st) {
-    const size_t smem = tc2_smem_bytes((int)comb(N_, M_));
-    const int64_t ctas = 2 * (int64_t)p.tiles_f * p.tiles_t;  // tiles_f counts 256-feature tiles: one CTA pair each
-    if (ctas > 0x7fffffff) NMG_FAIL(NMG_ERR_UNSUPPORTED, "too many output tiles for one launch");
-    NMG_CUDA(cudaFuncSetAttribute(spmm_tc2_kernel<N_, M_, T, TR>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3((unsigned)ctas);
-    cfg.blockDim = dim3(TC_THREADS);
-    cfg.dynamicSmemBytes = smem;
-    cfg.stream = st;
-    cudaLaunchAttribute attr[1];
-    attr[0].id = cudaLaunchAttributeClusterDimension;
-    attr[0].val.clusterDim.x = 2;
-    attr[0].val.clusterDim.y = 1;
-    attr[0].val.clusterDim.z = 1;
-    cfg.attrs = attr;
-    cfg.numAttrs = 1;
-    NMG_CUDA(cudaLaunchKernelEx(&cfg, spmm_tc2_kernel<N_, M_, T, TR>, p, tm[0], tm[1], tm[2]));
-    return NMG_OK;
-}
-
-template <int N_, int M_>
-static int tc2_launch_nm(int dtype, bool transposed, const TcParams &p, const CUtensorMap *tm, cudaStream_t st) {
-    if (dtype == NMG_F16) return transposed ? tc2_launch_one<N_, M_, __half, true>(p, tm, st) : tc2_launch_one<N_, M_, __half, false>(p, tm, st);
-    if (dtype == NMG_F32) return transposed ? tc2_launch_one<N_, M_, float, true>(p, tm, st) : tc2_launch_one<N_, M_, float, false>(p, tm, st);
-    return transposed ? tc2_launch_one<N_, M_, __nv_bfloat16, true>(p, tm, st) : tc2_launch_one<N_, M_, __nv_bfloat16, false>(p, tm, st);
-}
-
 template <int N_, int M_>
 static int tc_launch_nm(int dtype, bool transposed, const TcParams &p, const CUtensorMap *tm, cudaStream_t st) {
     if (dtype == NMG_F16) return transposed ? tc_launch_one<N_, M_, __half, true>(p, tm, st) : tc_launch_one<N_, M_, __half, false>(p, tm, st);
@@ -960,13 +600,11 @@ static int tc_launch_nm(int dtype, bool transposed, const TcParams &p, const CUt
     return transposed ? tc_launch_one<N_, M_, __nv_bfloat16, true>(p, tm, st) : tc_launch_one<N_, M_, __nv_bfloat16, false>(p, tm, st);
 }
 
-// Policy of the two tensor-core variants.  NMG_TC_DENSE=0 / 1 in the environment forces one of them (measurement aid).
+// Policy of the two tensor-core variants.
 bool tc_use_dense(const Geo &geo, int dtype, int64_t tokens) {
-    static const int forced = [] { const char *e = getenv("NMG_TC_DENSE"); return e ? atoi(e) : -1; }();
     const bool fused = tc_supported(geo, dtype), dense = tc_dense_supported(geo, dtype);
     if (!dense) return false;
     if (!fused) return true;
-    if (forced == 0 || forced == 1) return forced == 1;
     // Measured crossover (4096^2 and 16384^2 bf16 weights): a tie around 1024 tokens (0.055 / 0.053 ms and 0.567 / 0.598 ms,
     // fused / two-pass), two passes clearly ahead at 1536 (0.099 / 0.072 ms and 0.836 / 0.799 ms); fp32 (six split products,
     // so six in-kernel expansions per tile) prefers two passes from 256 tokens.
@@ -980,13 +618,7 @@ int tc_matmul(const Geo &geo, int dtype, bool transposed, bool dense, const void
     if (n_outs < 1 || (n_outs > 1 && !dense)) NMG_FAIL(NMG_ERR_UNSUPPORTED, "several output buffers need the two-pass tensor-core variant");
     void *out = outs[0];
     const int64_t red = transposed ? geo.M : geo.K;
-    const int64_t feats_all = transposed ? geo.K : geo.M;
-    // The CTA-pair kernel is correct but measured slower than the one-CTA kernel (10.3 ms against 8.3 ms on the
-    // 16384^3 2:8 problem: its skeleton is faster, 6.1 ms against 6.9 ms, but expansion stores and TMA cost more in
-    // pair mode), so it is opt-in: NMG_TC_PAIR=1 in the environment selects it when there are >= 256 output features.
-    static const bool pair_allowed = [] { const char *e = getenv("NMG_TC_PAIR"); return e && e[0] == '1'; }();
-    const bool pair = pair_allowed && feats_all >= 256 && !dense;
-    const uint32_t box_tok = pair ? 128 : TC_BN;
+    const uint32_t box_tok = TC_BN;
     CUtensorMap tm[3];
     int rc;
     const void *planes[3] = {nval, nval, nval};
@@ -1027,7 +659,7 @@ int tc_matmul(const Geo &geo, int dtype, bool transposed, bool dense, const void
     int *status = nullptr;
     if ((rc = get_status_word(&status))) return rc;
     const int64_t feats = transposed ? geo.K : geo.M;
-    const int64_t ftile = pair ? 256 : TC_BM;
+    const int64_t ftile = TC_BM;
     TcParams p{};
     p.pat = pat;
     for (int c = 0; c < 3; c++) p.nval[c] = planes[c];
@@ -1036,9 +668,7 @@ int tc_matmul(const Geo &geo, int dtype, bool transposed, bool dense, const void
     p.tiles_f = (int)((feats + ftile - 1) / ftile);
     p.tiles_t = (int)((tokens + TC_BN - 1) / TC_BN);
     p.status = status;
-    static const int debug_flags = [] { const char *e = getenv("NMG_TC_DEBUG"); return e ? atoi(e) : 0; }();
-    p.debug = debug_flags;
-    p.ksplit = pair ? 1 : tc_ksplit(geo, dtype, transposed, tokens);
+    p.ksplit = tc_ksplit(geo, dtype, transposed, tokens);
     if (p.ksplit > 1) {
         const size_t need = tc_ksplit_workspace_bytes(geo, dtype, transposed, tokens);
         if (!ws || ws_bytes < need) NMG_FAIL(NMG_ERR_WORKSPACE, "workspace of %zu bytes required for the partial tiles, got %zu", need, ws_bytes);
@@ -1050,7 +680,7 @@ int tc_matmul(const Geo &geo, int dtype, bool transposed, bool dense, const void
     rc = NMG_ERR_UNSUPPORTED;
 #define NMG_TC_CASE(N_, M_)                                                                         \
     if (geo.n == N_ && geo.m == M_)                                                                \
-        rc = pair ? tc2_launch_nm<N_, M_>(dtype, transposed, p, tm, st) : tc_launch_nm<N_, M_>(dtype, transposed, p, tm, st);
+        rc = tc_launch_nm<N_, M_>(dtype, transposed, p, tm, st);
     NMG_TC_CASE(1, 4)
     NMG_TC_CASE(2, 4)
     NMG_TC_CASE(1, 8)

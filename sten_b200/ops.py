@@ -157,8 +157,20 @@ def spmm(val, idx, M, K, n, m, g, act, bias=None, layout=nat.NMG_ACT_TOKEN_MAJOR
     tokens = act.shape[0] if token_major else act.shape[1]
     if (act.shape[1] if token_major else act.shape[0]) != K:
         raise ValueError(f"activation shape {tuple(act.shape)} does not match K={K}")
+    out_shape = (tokens, M) if layout == nat.NMG_ACT_TOKEN_MAJOR else (M, tokens)
     if out is None:
-        out = torch.empty((tokens, M) if layout == nat.NMG_ACT_TOKEN_MAJOR else (M, tokens), dtype=val.dtype, device=dev)
+        out = torch.empty(out_shape, dtype=val.dtype, device=dev)
+    else:
+        # the kernel writes out_shape[0] rows of out_shape[1] elements, ld_out apart: anything else would land outside `out`
+        if out.dtype != val.dtype or out.device != dev:
+            raise ValueError(f"out must be a {val.dtype} tensor on {dev}, got {out.dtype} on {out.device}")
+        if tuple(out.shape) != out_shape:
+            raise ValueError(f"out must have shape {out_shape} for this layout, got {tuple(out.shape)}")
+        if out_shape[1] > 1 and out.stride(1) != 1:
+            raise ValueError("out must have unit stride along its rows (a transposed view cannot be written in place)")
+        if out_shape[0] > 1 and out.stride(0) < out_shape[1]:
+            raise ValueError(f"out rows overlap: stride {out.stride(0)} is smaller than the row length {out_shape[1]}")
+    ld_out = out.stride(0) if out_shape[0] > 1 else out_shape[1]
     if tokens == 0:
         return out
     val, idx = val.contiguous(), idx.contiguous()
@@ -169,7 +181,7 @@ def spmm(val, idx, M, K, n, m, g, act, bias=None, layout=nat.NMG_ACT_TOKEN_MAJOR
         ws, nbytes = _workspace(_spmm_workspace_bytes(M, K, tokens, n, m, g, code, layout, algo, 1 if packed is not None else 0), dev)
         nat.check(L.nmg_spmm(val.data_ptr(), idx.data_ptr(), packed.data_ptr() if packed is not None else None, M, K, n,
                              m, g, code, act.data_ptr(), ld_act, tokens,
-                             bias.data_ptr() if bias is not None else None, out.data_ptr(), (out.shape[1] if out.is_contiguous() else out.stride(0)), layout, algo,
+                             bias.data_ptr() if bias is not None else None, out.data_ptr(), ld_out, layout, algo,
                              ws.data_ptr() if ws is not None else None, nbytes, _stream(dev)))
     return out
 

@@ -193,7 +193,8 @@ class RowShardedNMMatmul:
             raise ValueError("exchange must be 'gather' (NCCL all-gather per round) or 'peer' (the matmul kernel stores into every rank's buffer)")
         self.exchange = exchange
         self.multicast = True  # peer exchange: store through the NVSwitch multicast address when the allocation has one
-        self._peer_out = None
+        self._peer_out = [None, None]  # two symmetric output buffers, used alternately (see _forward_peer)
+        self._peer_calls = 0
         self._flag = None
         self.group = group
         self.world = dist.get_world_size(group) if dist.is_initialized() else 1
@@ -232,24 +233,37 @@ class RowShardedNMMatmul:
     def _forward_peer(self, x2d):
         """Every panel's matmul writes its rows of ``C`` into all ranks' buffers from its own epilogue (stores over
         NVLink, overlapped tile by tile with the tensor-core work); one tiny all-reduce orders the ranks afterwards.
-        The returned buffer is reused by the next call: consume or copy it before calling again."""
+
+        Two output buffers alternate between calls.  The all-reduce that ends call ``i`` proves that every rank's stores
+        of call ``i`` have landed; it does not prove that a peer has finished READING call ``i``'s result.  With one
+        buffer a fast rank could start call ``i+1`` and overwrite, over NVLink, what a slow rank's consumer kernels are
+        still reading.  With two, call ``i+1`` writes the buffer call ``i-1`` returned, and a rank can only start call
+        ``i+1`` after every rank has queued the all-reduce of call ``i`` behind its own consumers of call ``i-1``.
+        Contract: the returned tensor stays valid until the call after the next one is issued on any rank; consume it on
+        the stream the layer is called on (or a stream that stream waits for) before making that call."""
         tokens = x2d.shape[0]
         rp, R = self.rows_per_panel, self.world
         ld = tokens
-        if self._peer_out is None or tuple(self._peer_out.local.shape) != (self.M_total, ld) or self._peer_out.local.dtype != x2d.dtype:
-            self._peer_out = PeerBuffer((self.M_total, ld), x2d.dtype, x2d.device, self.group)
-            self._flag = torch.zeros(1, device=x2d.device)
+        slot = self._peer_calls & 1
+        self._peer_calls += 1
+        buf = self._peer_out[slot]
+        if buf is None or tuple(buf.local.shape) != (self.M_total, ld) or buf.local.dtype != x2d.dtype:
+            buf = self._peer_out[slot] = PeerBuffer((self.M_total, ld), x2d.dtype, x2d.device, self.group)
+            if self._flag is None:
+                self._flag = torch.zeros(1, device=x2d.device)
         es = x2d.element_size()
+        use_mc = bool(buf.multicast_ptr and self.multicast)
+        self.last_exchange = ("multimem.st through the NVSwitch multicast address" if use_mc else "one st.global per peer") + f"; {buf.how}"
         for p, panel in enumerate(self.panels):
             q = p * R + self.rank
             M, K, n, m, g = _geometry(panel)
-            ptrs = [base + q * rp * ld * es for base in self._peer_out.ptrs]
+            ptrs = [base + q * rp * ld * es for base in buf.ptrs]
             # own copy first: outs[0] is the buffer the bias / alignment checks refer to
             ptrs = [ptrs[self.rank]] + [a for r, a in enumerate(ptrs) if r != self.rank]
-            mc = self._peer_out.multicast_ptr + q * rp * ld * es if (self._peer_out.multicast_ptr and self.multicast) else None
+            mc = buf.multicast_ptr + q * rp * ld * es if use_mc else None
             ops.spmm_replicated(panel.val, panel.idx, M, K, n, m, g, x2d, ptrs, ld, multicast_ptr=mc)
         dist.all_reduce(self._flag, group=self.group)  # stream-ordered: completes when every rank's stores are done
-        return self._peer_out.local
+        return buf.local
 
     def forward(self, x2d, out=None):
         """``x2d``: [tokens, K] (replicated).  Returns ``C`` [M, tokens] complete on every rank."""

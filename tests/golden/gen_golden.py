@@ -1,8 +1,8 @@
 """Generate the golden fixtures of tests/golden/ from the reference implementation itself.
 
-Run in a container that has the reference tree (default /root/reference):
+Run where the reference tree is available, naming it on the command line or in NMG_REFERENCE_ROOT:
 
-    python tests/golden/gen_golden.py
+    python tests/golden/gen_golden.py /path/to/reference [small|big|layout|spmm|pickle ...]
 
 It imports the reference package (a stub stands in for the third-party ``dace`` module, which the
 sparsifier / densifier never touch), runs the reference's own CPU sparsifier
@@ -11,8 +11,13 @@ sparsifier / densifier never touch), runs the reference's own CPU sparsifier
 
   * ``small_cases.npz``   inputs, ``val``, ``idx`` and ``to_dense()`` of small 2-D and 3-D cases that cover every
                           remainder (M %% m, K %% (C*g)), ties, zeros, and all dim permutations;
-  * ``big_hashes.json``   sha256 of ``val`` / ``idx`` for the 1024 x 1024 and 4096 x 4096 benchmark weights
-                          (inputs come from ``torch.Generator().manual_seed``; their sha256 is stored too);
+  * ``big_hashes.json``   sha256 of ``val`` / ``idx`` for the 1024 x 1024 and 4096 x 4096 benchmark weights and for the
+                          16384 x 16384 bf16 2:8 weight of the sharded benchmark (N(0, 0.02) rounded to bf16, selection
+                          on the fp32 magnitudes of the rounded values; ``val`` hashed as bf16 bits) --
+                          inputs come from ``torch.Generator().manual_seed``; their sha256 is stored too;
+  * ``reference_linear.pkl``  a pickle WRITTEN BY THE REFERENCE: a ``torch.nn.Linear`` whose weight is the reference's
+                          ``SparseParameterWrapper`` around a ``GroupedNMTensor`` (made by its ``SparsityBuilder``), plus the
+                          input and the dense weight it was made from in ``reference_linear.npz``;
   * ``layout.json``       ``make_n_m`` tables and every key of ``compute_nm_strides`` for a list of shapes;
   * ``spmm_cases.npz``    outputs of the reference's AVX micro-kernels (built by oracle/build_ref.py) on small
                           problems with k-remainders.
@@ -44,11 +49,46 @@ def seeded_normal(shape, seed):
     return torch.randn(*shape, generator=g, dtype=torch.float32)
 
 
-def main(ref_root="/root/reference"):
+def main(ref_root=None, *parts):
+    ref_root = build_ref.reference_root(ref_root)
+    if ref_root is None:
+        raise SystemExit("no reference tree: pass its path or set NMG_REFERENCE_ROOT")
+    parts = set(parts) or {"small", "big", "layout", "spmm", "pickle"}
     build_ref.import_reference(ref_root)
-    os.chdir("/tmp")  # the reference JIT writes ./.compile_cache
+    import tempfile
+    os.chdir(tempfile.gettempdir())  # the reference JIT writes ./.compile_cache
     from sten.grouped_nm.grouped_nm_tensor import GroupedNMTensor, compute_nm_strides, make_n_m
+    if "small" in parts:
+        gen_small(GroupedNMTensor)
+    if "big" in parts:
+        gen_big(GroupedNMTensor)
+    if "layout" in parts:
+        gen_layout(compute_nm_strides, make_n_m)
+    if "spmm" in parts:
+        gen_spmm(GroupedNMTensor)
+    if "pickle" in parts:
+        gen_pickle()
+    print("done")
 
+
+def gen_pickle():
+    """A model pickled by the reference runtime itself (sten.py:178-189, 413-420 define what lands in the file)."""
+    import sten
+    torch.manual_seed(7)
+    lin = torch.nn.Linear(100, 24)
+    x = seeded_normal((9, 100), 8)
+    sb = sten.SparsityBuilder()
+    sb.set_weight("weight", initial_sparsifier=sten.GroupedNMSparsifier(2, 4, 2), out_format=sten.GroupedNMTensor)
+    dense_w = lin.weight.detach().clone().numpy()
+    sparse = sb.get_sparse_model(lin)
+    torch.save(sparse, os.path.join(HERE, "reference_linear.pkl"))
+    gnm = sparse.weight.wrapped_tensor
+    np.savez_compressed(os.path.join(HERE, "reference_linear.npz"), w=dense_w, b=lin.bias.detach().numpy(), x=x.numpy(),
+                        val=gnm.val.numpy(), idx=gnm.idx.numpy(), to_dense=gnm.to_dense().contiguous().numpy())
+    print("pickled a reference-made sparse Linear:", type(sparse.weight).__module__, type(gnm).__module__)
+
+
+def gen_small(GroupedNMTensor):
     # ---------------------------------------------------------------- small cases
     small = {}
     meta = []
@@ -90,6 +130,9 @@ def main(ref_root="/root/reference"):
     with open(os.path.join(HERE, "small_cases.json"), "w") as f:
         json.dump(meta, f, indent=1)
 
+
+
+def gen_big(GroupedNMTensor):
     # ---------------------------------------------------------------- benchmark-size hashes
     big = []
     for (M, K, n, m, g, seed_) in [
@@ -103,9 +146,22 @@ def main(ref_root="/root/reference"):
                         val_sha256=sha(t.val.numpy()), idx_sha256=sha(t.idx.numpy()),
                         val_shape=list(t.val.shape), idx_shape=list(t.idx.shape)))
         print("hashed", M, K, n, m, g)
+    # the sharded benchmark's weight: N(0, 0.02) rounded to bf16; the reference sees the rounded values as fp32
+    M = K = 16384
+    n, m, g, seed_ = 2, 8, 16, 0
+    w = (seeded_normal((M, K), seed_) * 0.02).bfloat16()
+    t = GroupedNMTensor.from_dense(w.float(), n, m, sparse_dim=0, group_size=g, group_dim=1)
+    val16 = t.val.bfloat16()
+    assert torch.equal(val16.float(), t.val)  # kept values are the bf16 inputs, exactly
+    big.append(dict(M=M, K=K, n=n, m=m, g=g, seed=seed_, scale=0.02, dtype="bf16",
+                    dense_sha256=sha(w.view(torch.int16).numpy()), val_sha256=sha(val16.view(torch.int16).numpy()),
+                    idx_sha256=sha(t.idx.numpy()), val_shape=list(t.val.shape), idx_shape=list(t.idx.shape)))
+    print("hashed", M, K, n, m, g, "bf16")
     with open(os.path.join(HERE, "big_hashes.json"), "w") as f:
         json.dump(big, f, indent=1)
 
+
+def gen_layout(compute_nm_strides, make_n_m):
     # ---------------------------------------------------------------- layout tables
     layout = {"make_n_m": {}, "nm_strides": []}
     for (n, m) in [(1, 4), (2, 4), (3, 4), (1, 8), (2, 8), (4, 8), (1, 16), (2, 16), (3, 6), (5, 12), (2, 2), (0, 3)]:
@@ -124,6 +180,9 @@ def main(ref_root="/root/reference"):
     with open(os.path.join(HERE, "layout.json"), "w") as f:
         json.dump(layout, f)
 
+
+
+def gen_spmm(GroupedNMTensor):
     # ---------------------------------------------------------------- matmul through the reference micro-kernels
     spmm = {}
     seed = 500
@@ -142,7 +201,6 @@ def main(ref_root="/root/reference"):
         spmm[f"{n}_{m}_{g}_{M}x{K}_{ntok}/w"] = w.numpy()
         spmm[f"{n}_{m}_{g}_{M}x{K}_{ntok}/x"] = x.numpy()
     np.savez_compressed(os.path.join(HERE, "spmm_cases.npz"), **spmm)
-    print("done")
 
 
 if __name__ == "__main__":

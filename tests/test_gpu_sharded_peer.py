@@ -46,6 +46,30 @@ def _worker(rank, world, port, result_q):
             return float((a.double() - b.double()).norm() / b.double().norm()) <= 2e-3
 
         same = torch.equal(results[("peer", 1)], results[("peer", 2)]) and close(results[("gather", 2)], results[("peer", 1)])
+        # Consecutive calls with DIFFERENT activations and a consumer kernel in between, never synchronising the host:
+        # a rank that runs ahead must not overwrite a result a slower rank is still reading (the layer alternates two
+        # peer buffers for that).  Rank 1 is made slow by extra work queued before each of its consumers.  Both store
+        # paths are covered: through the NVSwitch multicast address (when the allocation has one) and one store per peer.
+        how = {}
+        for multicast in (True, False):
+            layer = RowShardedNMMatmul.from_full_weight(w, n, m, g, rounds=1, exchange="peer")
+            layer.multicast = multicast
+            xs = [torch.randn(tokens, K, generator=gen).bfloat16().to(dev) for _ in range(4)]
+            ballast = torch.randn(4096, 4096, device=dev)
+            consumed = []
+            for xi in xs:
+                ci = layer(xi)
+                if rank == 1:
+                    for _ in range(3):
+                        ballast = (ballast @ ballast).clamp_(-1, 1)
+                consumed.append(ci.double())  # the consumer: reads the peer buffer on the layer's stream
+            torch.cuda.synchronize()
+            how[multicast] = layer.last_exchange
+            for xi, got in zip(xs, consumed):
+                want = full.double() @ xi.double().t()
+                errs[("consecutive", multicast, len(errs))] = float((got - want).norm() / want.norm())
+        errs["store paths"] = 0.0 if ("one st.global per peer" in how[False]) else 1.0
+        print(f"rank {rank}: peer exchange ran as {how}", flush=True)
         # host operands: every rank uploads half of X, downloads the rows it computed
         layer = RowShardedNMMatmul.from_full_weight(w, n, m, g, rounds=1, exchange="peer")
         x_host = x.cpu().pin_memory()

@@ -294,4 +294,14 @@ def test_workspace_and_argument_errors():
         ops.spmm(val, idx, M, K, n, m, g, x[:, :-1])
     with pytest.raises(TypeError):
         ops.spmm(val, idx, M, K, n, m, g, x.half())
+    # a caller-supplied `out` the kernel could not write safely is refused before any launch
+    for bad in (torch.empty(tokens, M, device=cuda(), dtype=torch.float16),      # wrong dtype
+                torch.empty(tokens, M - 1, device=cuda()),                        # wrong shape
+                torch.empty(M, tokens, device=cuda()).t(),                        # transposed view: rows not contiguous
+                torch.empty(tokens, 1, device=cuda()).expand(tokens, M)):         # overlapping rows
+        with pytest.raises(ValueError):
+            ops.spmm(val, idx, M, K, n, m, g, x, out=bad)
+    wide = torch.zeros(tokens, M + 8, device=cuda())
+    ops.spmm(val, idx, M, K, n, m, g, x, out=wide[:, :M])                         # a column slice is fine: ld_out = stride(0)
+    assert torch.equal(wide[:, :M], ops.spmm(val, idx, M, K, n, m, g, x)) and float(wide[:, M:].abs().max()) == 0
     assert ops.read_status() == 0
