@@ -48,8 +48,10 @@ typedef enum {
                                         row shard of W yields a contiguous row slab of C) */
 } nmg_act_layout;
 
-/* Kernel family for nmg_spmm / nmg_spmm_t (NMG_ALGO_AUTO picks by dtype and shape). */
-typedef enum { NMG_ALGO_AUTO = 0, NMG_ALGO_SIMT = 1, NMG_ALGO_TENSOR = 2 } nmg_algo;
+/* Kernel family for nmg_spmm / nmg_spmm_t (NMG_ALGO_AUTO picks by dtype and shape).  NMG_ALGO_TENSOR_DENSE restricts
+ * the tensor-core path to the kernels that multiply at the dense rate (no structured-sparse MMA); it only differs from
+ * NMG_ALGO_TENSOR for nmg_spmm_t and exists for comparison and measurement. */
+typedef enum { NMG_ALGO_AUTO = 0, NMG_ALGO_SIMT = 1, NMG_ALGO_TENSOR = 2, NMG_ALGO_TENSOR_DENSE = 3 } nmg_algo;
 
 int nmg_version(void);
 const char *nmg_last_error(void);
@@ -113,7 +115,12 @@ int nmg_spmm(const void *val, const int16_t *idx, const void *packed, int64_t M,
 
 /* Transposed product for the backward pass: dX[tokens][ld_dx >= K] = dY[tokens][ld_dy >= M] * W.
  * The reference has no counterpart (its dispatcher installs a failing backward stub: src/sten/sten.py:1690-1693);
- * the registration shape follows the CSR linear backward (sten.py:2362-2383). */
+ * the registration shape follows the CSR linear backward (sten.py:2362-2383).
+ * Here the weight's rows -- the axis the n:m blocks run along -- are the reduction axis, so for 16-bit weights with
+ * n <= 2 and m in {4, 8, 16, 32, 64} (every aligned group of four rows then holds at most two kept values) the tensor
+ * cores multiply only the kept values: from 1280 tokens on, NMG_ALGO_AUTO / NMG_ALGO_TENSOR compress W^T into the
+ * workspace (two values + two 2-bit positions per group of four rows) and run tcgen05.mma.sp, structured-sparse MMA at
+ * twice the dense rate.  fp32 weights, other patterns and fewer tokens use the dense-rate kernels described above. */
 size_t nmg_spmm_t_workspace_bytes(int64_t M, int64_t K, int64_t tokens, int n, int m, int g, int dtype,
                                   int algo, int have_packed);
 int nmg_spmm_t(const void *val, const int16_t *idx, const void *packed, int64_t M, int64_t K, int n, int m, int g,

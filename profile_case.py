@@ -25,13 +25,13 @@ def main():
     ap.add_argument("--cols", type=int, default=4096)
     ap.add_argument("--tokens", type=int, default=4096)
     ap.add_argument("--dtype", default="f32", choices=["f32", "f16", "bf16"])
-    ap.add_argument("--algo", default="auto", choices=["auto", "simt", "tensor"])
+    ap.add_argument("--algo", default="auto", choices=["auto", "simt", "tensor", "tensor_dense"])
     ap.add_argument("--reps", type=int, default=3)
     ap.add_argument("--no-packed", action="store_true", help="rebuild the column-ordered weight copy in every call")
     a = ap.parse_args()
     n, m = map(int, a.nm.split(":"))
     dtype = {"f32": torch.float32, "f16": torch.float16, "bf16": torch.bfloat16}[a.dtype]
-    algo = {"auto": nat.NMG_ALGO_AUTO, "simt": nat.NMG_ALGO_SIMT, "tensor": nat.NMG_ALGO_TENSOR}[a.algo]
+    algo = {"auto": nat.NMG_ALGO_AUTO, "simt": nat.NMG_ALGO_SIMT, "tensor": nat.NMG_ALGO_TENSOR, "tensor_dense": nat.NMG_ALGO_TENSOR_DENSE}[a.algo]
     dev = torch.device("cuda", 0)
     M, K, g = a.rows, a.cols, a.g
     w = torch.randn(M, K, generator=torch.Generator().manual_seed(0)).to(dev)

@@ -11,7 +11,7 @@ LIB_PATH = os.path.join(_HERE, "libnmg_b200.so")
 
 NMG_F32, NMG_F16, NMG_BF16 = 0, 1, 2
 NMG_ACT_TOKEN_MAJOR, NMG_ACT_K_MAJOR, NMG_ACT_TOKEN_MAJOR_OUT_ROWS = 0, 1, 2
-NMG_ALGO_AUTO, NMG_ALGO_SIMT, NMG_ALGO_TENSOR = 0, 1, 2
+NMG_ALGO_AUTO, NMG_ALGO_SIMT, NMG_ALGO_TENSOR, NMG_ALGO_TENSOR_DENSE = 0, 1, 2, 3
 NMG_NOALLOC_SCRATCH_BYTES = 32 << 20
 
 # name -> (restype, argtypes); must list every function of include/nmg_b200.h (checked by the test-suite)

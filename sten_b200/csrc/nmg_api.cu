@@ -68,6 +68,7 @@ extern "C" size_t nmg_spmm_workspace_bytes(int64_t M, int64_t K, int64_t tokens,
     if (make_geo(M, K, n, m, g, &geo) || tokens < 1 || n < 1) return 0;
     size_t simt = simt_fwd_workspace_bytes(geo, tokens, dtype, layout);
     size_t tensor = 0;
+    if (algo == NMG_ALGO_TENSOR_DENSE) algo = NMG_ALGO_TENSOR;
     if (algo != NMG_ALGO_SIMT && (tc_supported(geo, dtype) || tc_dense_supported(geo, dtype)) && layout != NMG_ACT_K_MAJOR)
         tensor = (tc_use_dense(geo, dtype, tokens) ? tc_dense_workspace_bytes(geo, dtype, false)
                                                    : (have_packed ? 0 : natural_bytes(geo, dtype, nullptr) + 512) +
@@ -92,7 +93,9 @@ static int spmm_impl(const void *val, const int16_t *idx, const void *packed, in
     const bool out_tm = layout == NMG_ACT_TOKEN_MAJOR;       // output rows are tokens
     if (ld_act < (tm ? K : tokens)) NMG_FAIL(NMG_ERR_INVALID, "ld_act=%lld is smaller than the activation row", (long long)ld_act);
     if (ld_out < (out_tm ? M : tokens)) NMG_FAIL(NMG_ERR_INVALID, "ld_out=%lld is smaller than the output row", (long long)ld_out);
-    if (algo != NMG_ALGO_AUTO && algo != NMG_ALGO_SIMT && algo != NMG_ALGO_TENSOR) NMG_FAIL(NMG_ERR_INVALID, "unknown algo %d", algo);
+    if (algo != NMG_ALGO_AUTO && algo != NMG_ALGO_SIMT && algo != NMG_ALGO_TENSOR && algo != NMG_ALGO_TENSOR_DENSE)
+        NMG_FAIL(NMG_ERR_INVALID, "unknown algo %d", algo);
+    if (algo == NMG_ALGO_TENSOR_DENSE) algo = NMG_ALGO_TENSOR;  // the forward product has no structured-sparse variant
     cudaStream_t st = (cudaStream_t)stream;
     const bool can_tensor = tm && tensor_ok(geo, dtype, act, ld_act);
     if (algo == NMG_ALGO_TENSOR && !can_tensor)
@@ -148,10 +151,16 @@ extern "C" int nmg_spmm_uses_packed(int64_t M, int64_t K, int64_t tokens, int n,
     Geo geo;
     if (make_geo(M, K, n, m, g, &geo) || tokens < 1 || n < 1) return 0;
     const bool any_tc = tc_supported(geo, dtype) || tc_dense_supported(geo, dtype);
-    const bool wants = algo == NMG_ALGO_TENSOR || (algo == NMG_ALGO_AUTO && (transposed ? K : M) >= 64);
+    const bool wants = algo == NMG_ALGO_TENSOR || algo == NMG_ALGO_TENSOR_DENSE || (algo == NMG_ALGO_AUTO && (transposed ? K : M) >= 64);
     const bool tensor = any_tc && wants && (transposed || layout != NMG_ACT_K_MAJOR);
     if (tensor) return tc_use_dense(geo, dtype, tokens) ? 0 : 1;
     return transposed ? 1 : 0;  // SIMT: the transposed kernel reads the packed copy, the forward kernel val / idx
+}
+
+// Whether nmg_spmm_t takes the structured-sparse tensor-core path: a supported 16-bit weight, enough tokens for the
+// two-pass regime, and the caller did not ask for the dense-rate kernels.
+static bool use_sp(const Geo &geo, int dtype, int64_t tokens, int algo) {
+    return algo != NMG_ALGO_SIMT && algo != NMG_ALGO_TENSOR_DENSE && tc_sp_supported(geo, dtype) && tc_use_dense(geo, dtype, tokens);
 }
 
 extern "C" size_t nmg_spmm_t_workspace_bytes(int64_t M, int64_t K, int64_t tokens, int n, int m, int g, int dtype,
@@ -165,6 +174,7 @@ extern "C" size_t nmg_spmm_t_workspace_bytes(int64_t M, int64_t K, int64_t token
         tensor = (tc_use_dense(geo, dtype, tokens) ? tc_dense_workspace_bytes(geo, dtype, true)
                                                    : pack + tc_ksplit_workspace_bytes(geo, dtype, true, tokens)) +
                  tc_split_workspace_bytes(geo, dtype, true, tokens);
+    if (use_sp(geo, dtype, tokens, algo) && tc_sp_workspace_bytes(geo) > tensor) tensor = tc_sp_workspace_bytes(geo);
     return simt > tensor ? simt : tensor;
 }
 
@@ -178,16 +188,21 @@ extern "C" int nmg_spmm_t(const void *val, const int16_t *idx, const void *packe
     if (n < 1) NMG_FAIL(NMG_ERR_INVALID, "n must be >= 1");
     if (ld_dy < M) NMG_FAIL(NMG_ERR_INVALID, "ld_dy=%lld is smaller than M", (long long)ld_dy);
     if (ld_dx < K) NMG_FAIL(NMG_ERR_INVALID, "ld_dx=%lld is smaller than K", (long long)ld_dx);
-    if (algo != NMG_ALGO_AUTO && algo != NMG_ALGO_SIMT && algo != NMG_ALGO_TENSOR) NMG_FAIL(NMG_ERR_INVALID, "unknown algo %d", algo);
+    if (algo != NMG_ALGO_AUTO && algo != NMG_ALGO_SIMT && algo != NMG_ALGO_TENSOR && algo != NMG_ALGO_TENSOR_DENSE)
+        NMG_FAIL(NMG_ERR_INVALID, "unknown algo %d", algo);
     cudaStream_t st = (cudaStream_t)stream;
     const bool can_tensor = tensor_ok(geo, dtype, dy, ld_dy);
-    if (algo == NMG_ALGO_TENSOR && !can_tensor)
+    if ((algo == NMG_ALGO_TENSOR || algo == NMG_ALGO_TENSOR_DENSE) && !can_tensor)
         NMG_FAIL(NMG_ERR_UNSUPPORTED, "tensor-core path needs gradient rows that are 16-byte aligned (16-bit dtypes) and a chunk that fits shared memory");
     char *ws = static_cast<char *>(workspace);
     size_t left = workspace_bytes;
     const uint16_t *pat = nullptr;
     const void *nval = nullptr;
-    const bool tensor = algo == NMG_ALGO_TENSOR || (algo == NMG_ALGO_AUTO && can_tensor && K >= 64);
+    const bool tensor = algo == NMG_ALGO_TENSOR || algo == NMG_ALGO_TENSOR_DENSE || (algo == NMG_ALGO_AUTO && can_tensor && K >= 64);
+    // The rows of W are the reduction axis here, so the n:m structure is one the tensor cores can skip: structured-sparse
+    // MMA at twice the dense rate (16-bit weights, n <= 2, m a power of two >= 4).
+    if (tensor && use_sp(geo, dtype, tokens, algo))
+        return tc_sp_matmul_t(geo, dtype, val, idx, dy, ld_dy, tokens, dx, ld_dx, workspace, workspace_bytes, st);
     const bool dense = tensor && tc_use_dense(geo, dtype, tokens);
     if (!dense && (rc = resolve_packed(geo, dtype, val, idx, packed, &ws, &left, &pat, &nval, st))) return rc;
     void *dxs[1] = {dx};

@@ -55,6 +55,14 @@ int tc_dense_matmul(const Geo &geo, int dtype, bool transposed, const void *val,
                     int64_t tokens, const void *bias, void *const *outs, int n_outs, void *mc_out, int64_t ld_out, int out_token_major,
                     void *ws, size_t ws_bytes, cudaStream_t st);
 
+// Structured-sparse tensor-core path of the transposed product (nmg_gemm_sp.cu): tcgen05.mma.sp on W^T compressed along
+// the reduction axis (the weight's rows).  16-bit weights with n <= 2 and m in {4, 8, 16, 32, 64}; taken from the token
+// count at which the two-pass variant is taken (the compression pass is per call, like the dense expansion).
+bool tc_sp_supported(const Geo &geo, int dtype);
+size_t tc_sp_workspace_bytes(const Geo &geo);
+int tc_sp_matmul_t(const Geo &geo, int dtype, const void *val, const int16_t *idx, const void *dy, int64_t ld_dy, int64_t tokens,
+                   void *dx, int64_t ld_dx, void *ws, size_t ws_bytes, cudaStream_t st);
+
 // ---- specialised forward kernel: parameters, shared-memory plan, per-(n, m) launchers
 struct FwdParams {
     const void *val;

@@ -481,6 +481,11 @@ def change_wrapper_metadata(tensor, device, dtype):
     torch.Tensor.__hash__,
     torch.Tensor.is_sparse.__get__,
     torch.Tensor.backward,
+    # dtype / device questions are answered by the one-element dummy, which carries the payload's dtype and device: no
+    # reason to densify a weight (what the generic fallback would do) because nn.Module.to() asks whether it is floating point
+    torch.Tensor.is_floating_point,
+    torch.Tensor.is_complex,
+    torch.Tensor.is_cuda.__get__,
 )
 def _base_impl(base_impl, func, types, *args, **kwargs):
     return base_impl(func, types, args, kwargs)

@@ -92,6 +92,11 @@ def test_kernel_choice_queries_are_pure_host_arithmetic():
     assert 4096 * 4096 * 2 <= ws <= 4096 * 4096 * 2 + 4096
     ws32 = L.nmg_spmm_workspace_bytes(4096, 4096, 4096, 2, 4, 16, F32, TM, TENSOR, 0)
     assert ws32 >= 6 * 4096 * 4096 * 2
+    # transposed product, 16-bit, two-pass regime: the workspace holds W^T compressed 2:4 along the reduction (M * K bytes of
+    # values + M * K / 8 bytes of metadata), or the dense W^T (2 * M * K bytes) when the dense-rate kernels are forced
+    ws_sp = L.nmg_spmm_t_workspace_bytes(4096, 4096, 4096, 2, 4, 16, BF, TENSOR, 0)
+    assert ws_sp >= 4096 * 4096 * 2
+    assert L.nmg_spmm_t_workspace_bytes(4096, 4096, 4096, 2, 4, 16, BF, nat.NMG_ALGO_TENSOR_DENSE, 0) >= 4096 * 4096 * 2
     # replicated output: argument validation happens before any CUDA call
     one = ctypes.c_void_p(16)
     outs = (ctypes.c_void_p * 1)(16)
