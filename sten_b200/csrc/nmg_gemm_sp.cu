@@ -11,11 +11,12 @@
 //   expand_sp_kernel   (val, idx) -> A_sp[K][R/2] (the kept values of W^T, two per group of four rows, 16-bit) and the
 //                      metadata, laid out in 2 KB atoms of 128 features x 128 reduction elements in the order the
 //                      tensor core's metadata copy (tcgen05.cp 128x128b) expects.  R = M rounded up to 128.
-//   gemm_sp_kernel     persistent, one CTA per SM, 128 features x 256 tokens per tile.  Warp 0 issues the TMA loads:
-//                      A_sp tiles (128 x 64 stored values = 128 reduction elements, with their metadata atom) into a
-//                      ring of 3, dY tiles (256 tokens x 64 reduction elements) into a ring of 4.  Warp 1 copies each
-//                      metadata atom into TMEM and issues tcgen05.mma.sp (128 x 256 x 32 per instruction, fp32
-//                      accumulator in TMEM).  Warps 2..9 drain: each reads its share of the finished accumulator into
+//   gemm_sp_kernel     persistent CTA pairs (cluster of 2), 256 features x 256 tokens per pair and tile.  Warp 0 of each
+//                      CTA issues its TMA loads: A_sp tiles of its 128 features (128 x 64 stored values = 128 reduction
+//                      elements, with their metadata atom) into a ring of 4, its half of the dY tile (128 tokens x 64
+//                      reduction elements) into a ring of 8.  Warp 1 of the even CTA copies each metadata atom into
+//                      TMEM and issues tcgen05.mma.sp.cta_group::2 (256 x 256 x 32 per instruction, fp32 accumulators
+//                      in both CTAs' TMEM).  Warps 2..9 drain: each reads its share of the finished accumulator into
 //                      registers at once and hands the accumulator back before converting and storing, so the next
 //                      tile's MMAs overlap the stores with a single accumulator (the metadata needs TMEM columns too).
 //
@@ -117,11 +118,24 @@ __global__ void __launch_bounds__(EXPAND_THREADS) expand_sp_kernel(const SpExpan
 }
 
 // =========================================================================================================
-// Matmul
+// Matmul: CTA pairs (thread-block cluster of 2, tcgen05 cta_group::2), one 256-feature x 256-token tile per pair.
+//
+// An SM takes in about 64 bytes per clock from L2.  With one CTA per 128 x 256 tile the operands of 128 reduction
+// elements are 18 KB of A_sp + 64 KB of dY per 512 tensor-core clocks, 160 bytes per clock: the tensor core would idle
+// most of the time.  Two CTAs on neighbouring SMs therefore share one tile of 256 features: each loads the A_sp rows of
+// its own 128 features and only HALF of the dY tile (128 tokens); the MMA (M = 256, issued by the even CTA) reads both
+// halves of dY from both shared memories.  Per SM that is 50 KB per 512 clocks.  No load is multicast.
+//
+// Barrier topology.  full_a / full_b live in the even ("leader") CTA: both CTAs' TMA loads name the leader's barrier,
+// the leader's producer posts the expected bytes of both.  empty_a / empty_b / acc_full exist in both CTAs and are
+// signalled by multicast tcgen05.commit.  acc_free lives in the leader and collects the drain warps of both CTAs.
+// Every wait is bounded and every thread reaches the closing cluster barrier, also after a failed wait.
 // =========================================================================================================
-constexpr int SP_NA = 3;                                   // ring of A_sp tiles (+ metadata atom), 128 reduction elements each
-constexpr int SP_NB = 4;                                   // ring of dY tiles, 64 reduction elements each
+constexpr int SP_NA = 4;                                   // ring of A_sp tiles (+ metadata atom), 128 reduction elements each
+constexpr int SP_NB = 8;                                   // ring of dY half tiles: 128 tokens x 64 reduction elements
 constexpr int SP_A_SLOT = TC_A_BYTES + SP_ATOM_BYTES;      // 16 KB values + 2 KB metadata
+constexpr int SP_B_SLOT = 128 * TC_BK * 2;                 // 16 KB
+constexpr int SP_PAIR_FEATS = 256;
 constexpr int SP_DRAIN_WARPS = 8;
 constexpr int SP_THREADS = 32 * (2 + SP_DRAIN_WARPS);
 constexpr uint32_t SP_TMEM_COLS = 512;
@@ -129,34 +143,95 @@ constexpr uint32_t SP_E_COL = 256;                         // metadata columns: 
 
 struct SpGemmParams {
     void *out;            // [tokens][ld_out]
-    const uint8_t *meta;
     int64_t out_feats, red, ntok, ld_out, n_rt;
-    int tiles_f, tiles_t;
+    int tiles_f, tiles_t; // tiles_f counts 256-feature tiles
     int *status;
 };
 struct SpGemmMaps {
     CUtensorMap a;  // A_sp [K][R/2], box 64 x 128, 128-byte swizzle
-    CUtensorMap b;  // dY [tokens][M], box 64 x 256
+    CUtensorMap b;  // dY [tokens][M], box 64 x 128
+    CUtensorMap e;  // metadata as [atoms * 2][256] 32-bit words, box 256 x 2 = one 2 KB atom
 };
 
-__device__ __forceinline__ void bulk_load(void *smem_dst, const void *gsrc, uint32_t bytes, uint64_t *bar) {
-    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
-                 ::"r"(smem_u32(smem_dst)), "l"(gsrc), "r"(bytes), "r"(smem_u32(bar)) : "memory");
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+    asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// shared::cluster address of `local` (a shared::cta address of this CTA) in the CTA with the given cluster rank
+__device__ __forceinline__ uint32_t map_to_rank(uint32_t local, uint32_t rank) {
+    uint32_t r;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(local), "r"(rank));
+    return r;
+}
+__device__ __forceinline__ void mbar_arrive_remote(uint32_t cluster_addr) {
+    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait_cluster(uint64_t *bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
+    return ok != 0;
+}
+__device__ __forceinline__ bool mbar_wait_cluster_bounded(uint64_t *bar, uint32_t parity, int *status, int code) {
+    if (mbar_try_wait_cluster(bar, parity)) return true;
+    const uint64_t t0 = global_timer_ns();
+    for (;;) {
+        for (int i = 0; i < 64; i++)
+            if (mbar_try_wait_cluster(bar, parity)) return true;
+        if (global_timer_ns() - t0 > kWaitLimitNs) break;
+    }
+    if (status) atomicExch(status, code);
+    return false;
+}
+// 2-D tiled TMA load of a CTA pair, no multicast: the box lands in THIS CTA's shared memory, the bytes are reported to
+// the mbarrier at `bar_cluster_addr`, which may live in the peer CTA.
+__device__ __forceinline__ void tma_load_2d_pair(void *smem_dst, const CUtensorMap *map, int x, int y, uint32_t bar_cluster_addr) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+        ::"r"(smem_u32(smem_dst)), "l"(map), "r"(x), "r"(y), "r"(bar_cluster_addr)
+        : "memory");
+}
+// commit of the pair's MMAs: arrives at the barrier at this shared-memory offset in BOTH CTAs
+__device__ __forceinline__ void tc2_commit_both(uint64_t *bar) {
+    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+                 ::"r"(smem_u32(bar)), "h"((uint16_t)3) : "memory");
+}
+__device__ __forceinline__ void tmem_alloc_pair(uint32_t *smem_slot, uint32_t cols) {
+    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(smem_slot)), "r"(cols) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc_pair(uint32_t taddr, uint32_t cols) {
+    asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(cols) : "memory");
 }
 // Copy 128 rows x 16 bytes of shared memory (row i at byte i * 16: eight-row groups 128 bytes apart, no swizzle) into
-// four TMEM columns of all 128 lanes.  Descriptor: start address >> 4, leading byte offset (unused: one 16-byte column),
-// stride byte offset 128 >> 4 between eight-row groups, version 1, no swizzle.
-__device__ __forceinline__ void tc_copy_meta(uint32_t taddr, uint32_t smem_addr) {
+// four TMEM columns of all 128 lanes, in both CTAs of the pair (each from its own shared memory, same offset).
+// Descriptor: start address >> 4, leading byte offset (unused: one 16-byte column), stride byte offset 128 >> 4 between
+// eight-row groups, version 1, no swizzle.
+__device__ __forceinline__ void tc2_copy_meta(uint32_t taddr, uint32_t smem_addr) {
     const uint64_t desc = (uint64_t)((smem_addr >> 4) & 0x3FFF) | ((uint64_t)(128 >> 4) << 16) | ((uint64_t)(128 >> 4) << 32) | ((uint64_t)1 << 46);
-    asm volatile("tcgen05.cp.cta_group::1.128x128b [%0], %1;" ::"r"(taddr), "l"(desc) : "memory");
+    asm volatile("tcgen05.cp.cta_group::2.128x128b [%0], %1;" ::"r"(taddr), "l"(desc) : "memory");
 }
-__device__ __forceinline__ void tc_mma_sp_f16(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t e_tmem, uint32_t idesc, uint32_t accumulate) {
+__device__ __forceinline__ void tc2_mma_sp_f16(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t e_tmem, uint32_t idesc, uint32_t accumulate) {
     asm volatile(
         "{\n\t.reg .pred p;\n\t"
         "setp.ne.b32 p, %5, 0;\n\t"
-        "tcgen05.mma.sp.cta_group::1.kind::f16 [%0], %1, %2, [%3], %4, p;\n\t}"
+        "tcgen05.mma.sp.cta_group::2.kind::f16 [%0], %1, %2, [%3], %4, p;\n\t}"
         ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(e_tmem), "r"(idesc), "r"(accumulate)
         : "memory");
+}
+// Instruction descriptor of the pair: M = 256 across both CTAs, N = 256, A structured-sparse (bit 2); bits 0-1 select the
+// metadata column inside an aligned pair of TMEM columns.
+template <typename T> __device__ __forceinline__ uint32_t make_idesc_sp_pair() {
+    const uint32_t fmt = DT<T>::id == NMG_BF16 ? 1u : 0u;
+    return (1u << 2) | (1u << 4) | (fmt << 7) | (fmt << 10) | ((uint32_t)(256 >> 3) << 17) | ((uint32_t)(256 >> 4) << 24);
 }
 
 template <typename T>
@@ -164,43 +239,50 @@ __global__ void __launch_bounds__(SP_THREADS, 1) gemm_sp_kernel(const SpGemmPara
     extern __shared__ char smem_raw[];
     char *smem = reinterpret_cast<char *>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     char *a_ring = smem;                                 // SP_NA slots: 16 KB tile (1024-aligned) + 2 KB metadata
-    char *b_ring = smem + SP_NA * SP_A_SLOT;             // SP_NB slots of 32 KB (SP_A_SLOT is a multiple of 1024)
-    char *misc = b_ring + SP_NB * TC_B_BYTES;
-    uint64_t *full_a = reinterpret_cast<uint64_t *>(misc);
-    uint64_t *empty_a = full_a + SP_NA;
-    uint64_t *full_b = empty_a + SP_NA;
-    uint64_t *empty_b = full_b + SP_NB;
+    char *b_ring = smem + SP_NA * SP_A_SLOT;             // SP_NB slots of 16 KB
+    char *misc = b_ring + SP_NB * SP_B_SLOT;
+    uint64_t *full_a = reinterpret_cast<uint64_t *>(misc);   // meaningful in the leader only
+    uint64_t *full_b = full_a + SP_NA;                        // leader only
+    uint64_t *empty_a = full_b + SP_NB;
+    uint64_t *empty_b = empty_a + SP_NA;
     uint64_t *acc_full = empty_b + SP_NB;
-    uint64_t *acc_free = acc_full + 1;
-    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(misc + 192);
-    static_assert((2 * SP_NA + 2 * SP_NB + 2) * 8 <= 192 && SP_A_SLOT % 1024 == 0, "shared-memory plan");
+    uint64_t *acc_free = acc_full + 1;                        // leader only
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(misc + 248);
+    static_assert((2 * SP_NA + 2 * SP_NB + 2) * 8 <= 248 && SP_A_SLOT % 1024 == 0 && SP_B_SLOT % 1024 == 0, "shared-memory plan");
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const uint32_t rank = cluster_ctarank();
+    const bool leader = rank == 0;
+    const int pair = (int)(blockIdx.x >> 1), npairs = (int)(gridDim.x >> 1);
     const int ntiles = prm.tiles_f * prm.tiles_t;
-    const int my_tiles = ((int)blockIdx.x < ntiles) ? (ntiles - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x : 0;
+    const int my_tiles = (pair < ntiles) ? (ntiles - pair + npairs - 1) / npairs : 0;
     const int nj = (int)((prm.red + TC_BK - 1) / TC_BK);  // dY tiles (64 reduction elements) per output tile
 
     if (tid == 0) {
         for (int s = 0; s < SP_NA; s++) { mbar_init(&full_a[s], 1); mbar_init(&empty_a[s], 1); }
         for (int s = 0; s < SP_NB; s++) { mbar_init(&full_b[s], 1); mbar_init(&empty_b[s], 1); }
         mbar_init(acc_full, 1);
-        mbar_init(acc_free, SP_DRAIN_WARPS);
+        mbar_init(acc_free, 2 * SP_DRAIN_WARPS);  // the drain warps of both CTAs
         mbar_fence_init();
     }
-    if (warp == 1) tmem_alloc(tmem_slot, SP_TMEM_COLS);
+    if (warp == 1) tmem_alloc_pair(tmem_slot, SP_TMEM_COLS);
     tc_fence_before();
     __syncthreads();
+    cluster_sync_all();  // barriers of both CTAs are initialised before anyone arrives remotely
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
+    const uint32_t full_a_leader = map_to_rank(smem_u32(&full_a[0]), 0);
+    const uint32_t full_b_leader = map_to_rank(smem_u32(&full_b[0]), 0);
+    const uint32_t acc_free_leader = map_to_rank(smem_u32(acc_free), 0);
 
     auto tile_origin = [&](int ti, int &tile_f, int &tok0) {
         int tile_t;
-        tile_of_cta((int)blockIdx.x + ti * (int)gridDim.x, prm.tiles_f, prm.tiles_t, tile_f, tile_t);
+        tile_of_cta(pair + ti * npairs, prm.tiles_f, prm.tiles_t, tile_f, tile_t);
         tok0 = tile_t * TC_BN;
     };
 
     if (warp == 0) {
-        // ------------------------------------------------------------------ TMA producer (one lane)
+        // ------------------------------------------------------------------ TMA producer (one lane per CTA)
         if (lane == 0) {
             int at = 0, bt = 0;
             bool ok = true;
@@ -208,32 +290,33 @@ __global__ void __launch_bounds__(SP_THREADS, 1) gemm_sp_kernel(const SpGemmPara
             for (int ti = 0; ti < my_tiles && ok; ti++) {
                 int tile_f, tok0;
                 tile_origin(ti, tile_f, tok0);
+                const int half_f = tile_f * 2 + (int)rank;  // this CTA's 128-feature tile = its metadata atom row
                 for (int j = 0; j < nj; j++) {
                     if ((j & 1) == 0) {
                         const int sa = at % SP_NA;
-                        if (!(ok = mbar_wait_bounded(&empty_a[sa], (uint32_t)(((at / SP_NA) & 1) ^ 1), prm.status, 31))) break;
-                        mbar_expect_tx(&full_a[sa], SP_A_SLOT);
+                        if (!(ok = mbar_wait_cluster_bounded(&empty_a[sa], (uint32_t)(((at / SP_NA) & 1) ^ 1), prm.status, 31))) break;
+                        if (leader) mbar_expect_tx(&full_a[sa], 2 * SP_A_SLOT);  // both CTAs report to this barrier
                         char *slot = a_ring + sa * SP_A_SLOT;
-                        tma_load_2d(slot, &maps.a, (j >> 1) * 64, tile_f * TC_BM, &full_a[sa]);
-                        bulk_load(slot + TC_A_BYTES, prm.meta + ((int64_t)tile_f * prm.n_rt + (j >> 1)) * SP_ATOM_BYTES, SP_ATOM_BYTES, &full_a[sa]);
+                        tma_load_2d_pair(slot, &maps.a, (j >> 1) * 64, half_f * TC_BM, full_a_leader + sa * 8);
+                        tma_load_2d_pair(slot + TC_A_BYTES, &maps.e, 0, (int)(((int64_t)half_f * prm.n_rt + (j >> 1)) * 2), full_a_leader + sa * 8);
                         at++;
                     }
                     const int sb = bt % SP_NB;
-                    if (!(ok = mbar_wait_bounded(&empty_b[sb], (uint32_t)(((bt / SP_NB) & 1) ^ 1), prm.status, 32))) break;
-                    mbar_expect_tx(&full_b[sb], TC_B_BYTES);
-                    tma_load_2d(b_ring + sb * TC_B_BYTES, &maps.b, j * TC_BK, tok0, &full_b[sb]);
+                    if (!(ok = mbar_wait_cluster_bounded(&empty_b[sb], (uint32_t)(((bt / SP_NB) & 1) ^ 1), prm.status, 32))) break;
+                    if (leader) mbar_expect_tx(&full_b[sb], 2 * SP_B_SLOT);
+                    tma_load_2d_pair(b_ring + sb * SP_B_SLOT, &maps.b, j * TC_BK, tok0 + (int)rank * 128, full_b_leader + sb * 8);
                     bt++;
                 }
             }
         }
     } else if (warp == 1) {
-        // ------------------------------------------------------------------ MMA issuer (one lane)
-        if (lane == 0) {
-            const uint32_t idesc = make_idesc<T>() | (1u << 2);  // bit 2: A is 2:4 structured-sparse; bits 0-1 select the metadata column of a pair
+        // ------------------------------------------------------------------ MMA issuer (one lane of the leader)
+        if (leader && lane == 0) {
+            const uint32_t idesc = make_idesc_sp_pair<T>();
             bool ok = true;
             int at = 0, bt = 0;
             for (int ti = 0; ti < my_tiles && ok; ti++) {
-                if (ti > 0) ok = mbar_wait_bounded(acc_free, (uint32_t)((ti - 1) & 1), prm.status, 36);
+                if (ti > 0) ok = mbar_wait_cluster_bounded(acc_free, (uint32_t)((ti - 1) & 1), prm.status, 36);
                 if (!ok) break;
                 tc_fence_after();
                 int sa = 0;
@@ -242,28 +325,28 @@ __global__ void __launch_bounds__(SP_THREADS, 1) gemm_sp_kernel(const SpGemmPara
                     const int sb = bt % SP_NB;
                     if ((j & 1) == 0) {
                         sa = at % SP_NA;
-                        if (!(ok = mbar_wait_bounded(&full_a[sa], (uint32_t)((at / SP_NA) & 1), prm.status, 33))) break;
+                        if (!(ok = mbar_wait_cluster_bounded(&full_a[sa], (uint32_t)((at / SP_NA) & 1), prm.status, 33))) break;
                         tc_fence_after();
                         e_set = tmem_base + SP_E_COL + 4u * (uint32_t)(at & 1);
-                        tc_copy_meta(e_set, smem_u32(a_ring + sa * SP_A_SLOT + TC_A_BYTES));
+                        tc2_copy_meta(e_set, smem_u32(a_ring + sa * SP_A_SLOT + TC_A_BYTES));
                     }
-                    if (!(ok = mbar_wait_bounded(&full_b[sb], (uint32_t)((bt / SP_NB) & 1), prm.status, 34))) break;
+                    if (!(ok = mbar_wait_cluster_bounded(&full_b[sb], (uint32_t)((bt / SP_NB) & 1), prm.status, 34))) break;
                     tc_fence_after();
                     // second half of the A slot: 32 stored values = 64 bytes = 4 descriptor units further
                     const uint64_t adesc = make_sw128_desc(smem_u32(a_ring + sa * SP_A_SLOT)) + (uint64_t)((j & 1) * 4);
-                    const uint64_t bdesc = make_sw128_desc(smem_u32(b_ring + sb * TC_B_BYTES));
+                    const uint64_t bdesc = make_sw128_desc(smem_u32(b_ring + sb * SP_B_SLOT));
                     const uint32_t e_addr = e_set + 2u * (uint32_t)(j & 1);  // metadata columns are addressed in pairs
 #pragma unroll
                     for (int k = 0; k < 2; k++)  // 32 reduction elements per instruction: 16 stored values of A (2 units), 32 of dY (4 units)
-                        tc_mma_sp_f16(tmem_base, adesc + 2 * k, bdesc + 4 * k, e_addr, idesc | (uint32_t)k, (j == 0 && k == 0) ? 0u : 1u);
-                    tc_commit(&empty_b[sb]);
-                    if ((j & 1) || j == nj - 1) { tc_commit(&empty_a[sa]); at++; }
+                        tc2_mma_sp_f16(tmem_base, adesc + 2 * k, bdesc + 4 * k, e_addr, idesc | (uint32_t)k, (j == 0 && k == 0) ? 0u : 1u);
+                    tc2_commit_both(&empty_b[sb]);
+                    if ((j & 1) || j == nj - 1) { tc2_commit_both(&empty_a[sa]); at++; }
                 }
-                tc_commit(acc_full);  // arrives when the tile's MMAs have written TMEM (also on the error path)
+                tc2_commit_both(acc_full);  // arrives in both CTAs when the tile's MMAs have written TMEM (also on the error path)
             }
         }
     } else {
-        // ------------------------------------------------------------------ drain warps
+        // ------------------------------------------------------------------ drain warps (both CTAs, own 128 features)
         const int q = warp & 3;                                          // TMEM lane quarter this warp may access
         constexpr int SLICES = (TC_BN / 32) / (SP_DRAIN_WARPS / 4);      // 32-column slices per warp: 4
         const int sl0 = ((warp - 2) >> 2) * SLICES;
@@ -273,8 +356,8 @@ __global__ void __launch_bounds__(SP_THREADS, 1) gemm_sp_kernel(const SpGemmPara
         for (int ti = 0; ti < my_tiles && ok; ti++) {
             int tile_f, tok0;
             tile_origin(ti, tile_f, tok0);
-            const int64_t feat = (int64_t)tile_f * TC_BM + q * 32 + lane;
-            if (!(ok = mbar_wait_bounded(acc_full, (uint32_t)(ti & 1), prm.status, 35))) break;
+            const int64_t feat = (int64_t)tile_f * SP_PAIR_FEATS + (int64_t)rank * TC_BM + q * 32 + lane;
+            if (!(ok = mbar_wait_cluster_bounded(acc_full, (uint32_t)(ti & 1), prm.status, 35))) break;
             tc_fence_after();
             // the warp's whole share of the accumulator goes to registers first, then the accumulator is handed back:
             // the next tile's MMAs run while this one is converted and stored
@@ -285,7 +368,7 @@ __global__ void __launch_bounds__(SP_THREADS, 1) gemm_sp_kernel(const SpGemmPara
             for (int s = 0; s < SLICES; s++) tmem_ld_fence(r[s]);
             tc_fence_before();
             __syncwarp();
-            if (lane == 0) mbar_arrive(acc_free);
+            if (lane == 0) mbar_arrive_remote(acc_free_leader);
             if (feat >= prm.out_feats) continue;
 #pragma unroll
             for (int s = 0; s < SLICES; s++) {
@@ -304,9 +387,10 @@ __global__ void __launch_bounds__(SP_THREADS, 1) gemm_sp_kernel(const SpGemmPara
         }
     }
     __syncthreads();
+    cluster_sync_all();  // the peer no longer reads this CTA's shared memory or signals its barriers
     if (warp == 1) {
         tc_fence_after();
-        tmem_dealloc(tmem_base, SP_TMEM_COLS);
+        tmem_dealloc_pair(tmem_base, SP_TMEM_COLS);
     }
 }
 
@@ -329,7 +413,7 @@ static SpLayout sp_layout(const Geo &geo) {
     const int64_t R = sp_red_padded(geo);
     l.ld_a = R / 2;
     l.n_rt = R / SP_ATOM;
-    l.n_ft = (geo.K + SP_ATOM - 1) / SP_ATOM;
+    l.n_ft = round_up((geo.K + SP_ATOM - 1) / SP_ATOM, 2);  // a CTA pair covers two feature tiles; the second may lie outside the weight
     l.asp_bytes = ((size_t)geo.K * (size_t)l.ld_a * 2 + 255) & ~(size_t)255;
     l.meta_bytes = (size_t)l.n_ft * (size_t)l.n_rt * SP_ATOM_BYTES;
     l.total = l.asp_bytes + l.meta_bytes + 256;
@@ -349,7 +433,7 @@ template <typename T, int N_> static int sp_expand_launch(const SpExpandParams &
 }
 
 template <typename T> static int sp_gemm_launch(const SpGemmParams &p, const SpGemmMaps &maps, cudaStream_t st) {
-    const size_t smem = (size_t)SP_NA * SP_A_SLOT + (size_t)SP_NB * TC_B_BYTES + 256 + 1024;
+    const size_t smem = (size_t)SP_NA * SP_A_SLOT + (size_t)SP_NB * SP_B_SLOT + 256 + 1024;
     int dev = 0, sms = 148;
     NMG_CUDA(cudaGetDevice(&dev));
     NMG_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
@@ -357,15 +441,20 @@ template <typename T> static int sp_gemm_launch(const SpGemmParams &p, const SpG
     if (tiles > 0x3fffffff) NMG_FAIL(NMG_ERR_UNSUPPORTED, "too many output tiles for one launch");
     NMG_CUDA(cudaFuncSetAttribute(gemm_sp_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3((unsigned)(tiles < sms ? tiles : sms));  // persistent
+    const int64_t pairs = sms / 2;
+    cfg.gridDim = dim3((unsigned)(2 * (tiles < pairs ? tiles : pairs)));  // persistent CTA pairs
     cfg.blockDim = dim3(SP_THREADS);
     cfg.dynamicSmemBytes = smem;
     cfg.stream = st;
-    cudaLaunchAttribute attr[1];
-    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;  // overlap the prologue with the expansion pass's tail
-    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cudaLaunchAttribute attr[2];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 2;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;  // overlap the prologue with the expansion pass's tail
+    attr[1].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
-    cfg.numAttrs = 1;
+    cfg.numAttrs = 2;
     NMG_CUDA(cudaLaunchKernelEx(&cfg, gemm_sp_kernel<T>, p, maps));
     return NMG_OK;
 }
@@ -409,13 +498,14 @@ int tc_sp_matmul_t(const Geo &geo, int dtype, const void *val, const int16_t *id
 
     SpGemmMaps maps;
     if ((rc = encode_tmap_2d(&maps.a, dtype, base, (uint64_t)lay.ld_a, (uint64_t)geo.K, (uint64_t)lay.ld_a, 64, TC_BM, 1))) return rc;
-    if ((rc = encode_tmap_2d(&maps.b, dtype, dy, (uint64_t)geo.M, (uint64_t)tokens, (uint64_t)ld_dy, TC_BK, TC_BN, 1))) return rc;
+    if ((rc = encode_tmap_2d(&maps.b, dtype, dy, (uint64_t)geo.M, (uint64_t)tokens, (uint64_t)ld_dy, TC_BK, 128, 1))) return rc;
+    if ((rc = encode_tmap_2d(&maps.e, NMG_F32, meta, 256, (uint64_t)(lay.n_ft * lay.n_rt * 2), 256, 256, 2, 0))) return rc;
     int *status = nullptr;
     if ((rc = get_status_word(&status))) return rc;
     SpGemmParams gp{};
-    gp.out = dx; gp.meta = reinterpret_cast<const uint8_t *>(meta);
+    gp.out = dx;
     gp.out_feats = geo.K; gp.red = geo.M; gp.ntok = tokens; gp.ld_out = ld_dx; gp.n_rt = lay.n_rt;
-    gp.tiles_f = (int)lay.n_ft;
+    gp.tiles_f = (int)(lay.n_ft / 2);
     gp.tiles_t = (int)((tokens + TC_BN - 1) / TC_BN);
     gp.status = status;
     rc = dtype == NMG_F16 ? sp_gemm_launch<__half>(gp, maps, st) : sp_gemm_launch<__nv_bfloat16>(gp, maps, st);

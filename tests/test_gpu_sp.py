@@ -74,7 +74,7 @@ def test_zeros_among_the_kept_values_and_exact_small_integers():
 def test_patterns_outside_the_structure_fall_back_to_the_dense_rate_kernels():
     from sten_b200 import _native as nat, ops
     # 3:6 (blocks are not made of groups of four) and fp32 stay on the dense-rate kernels, with the same results as before
-    M, K, tokens = 60, 336, 1300
+    M, K, tokens = 96, 336, 1300
     w = seeded_normal((M, K), 77).bfloat16().to(cuda())
     val, idx = ops.sparsify(w.unsqueeze(0), 3, 6, 4)
     dy = seeded_normal((tokens, M), 78).bfloat16().to(cuda())
