@@ -12,9 +12,9 @@
 //                      metadata, laid out in 2 KB atoms of 128 features x 128 reduction elements in the order the
 //                      tensor core's metadata copy (tcgen05.cp 128x128b) expects.  R = M rounded up to 128.
 //   gemm_sp_kernel     persistent CTA pairs (cluster of 2), 256 features x 256 tokens per pair and tile.  Warp 0 of each
-//                      CTA issues its TMA loads: A_sp tiles of its 128 features (128 x 64 stored values = 128 reduction
-//                      elements, with their metadata atom) into a ring of 4, its half of the dY tile (128 tokens x 64
-//                      reduction elements) into a ring of 8.  Warp 1 of the even CTA copies each metadata atom into
+//                      CTA issues its TMA loads into a ring of four stages of 128 reduction elements: the A_sp tile of
+//                      its 128 features (128 x 64 stored values), their metadata atom, and its half of the dY tile (128
+//                      tokens, two boxes of 64 reduction elements).  Warp 1 of the even CTA copies each metadata atom into
 //                      TMEM and issues tcgen05.mma.sp.cta_group::2 (256 x 256 x 32 per instruction, fp32 accumulators
 //                      in both CTAs' TMEM).  Warps 2..9 drain: each reads its share of the finished accumulator into
 //                      registers at once and hands the accumulator back before converting and storing, so the next
@@ -126,15 +126,16 @@ __global__ void __launch_bounds__(EXPAND_THREADS) expand_sp_kernel(const SpExpan
 // its own 128 features and only HALF of the dY tile (128 tokens); the MMA (M = 256, issued by the even CTA) reads both
 // halves of dY from both shared memories.  Per SM that is 50 KB per 512 clocks.  No load is multicast.
 //
-// Barrier topology.  full_a / full_b live in the even ("leader") CTA: both CTAs' TMA loads name the leader's barrier,
-// the leader's producer posts the expected bytes of both.  empty_a / empty_b / acc_full exist in both CTAs and are
+// Barrier topology.  full[s] lives in the even ("leader") CTA: both CTAs' TMA loads name the leader's barrier,
+// the leader's producer posts the expected bytes of both.  empty[s] / acc_full exist in both CTAs and are
 // signalled by multicast tcgen05.commit.  acc_free lives in the leader and collects the drain warps of both CTAs.
 // Every wait is bounded and every thread reaches the closing cluster barrier, also after a failed wait.
 // =========================================================================================================
-constexpr int SP_NA = 4;                                   // ring of A_sp tiles (+ metadata atom), 128 reduction elements each
-constexpr int SP_NB = 8;                                   // ring of dY half tiles: 128 tokens x 64 reduction elements
-constexpr int SP_A_SLOT = TC_A_BYTES + SP_ATOM_BYTES;      // 16 KB values + 2 KB metadata
-constexpr int SP_B_SLOT = 128 * TC_BK * 2;                 // 16 KB
+constexpr int SP_STAGES = 4;                               // ring of stages, 128 reduction elements each
+constexpr int SP_B_HALF = 128 * TC_BK * 2;                 // 16 KB: 128 tokens x 64 reduction elements of dY
+constexpr int SP_OFF_B = TC_A_BYTES;                       // stage layout: A_sp tile (16 KB) | two dY boxes (2 x 16 KB) | metadata atom (2 KB)
+constexpr int SP_OFF_E = SP_OFF_B + 2 * SP_B_HALF;
+constexpr int SP_STAGE = SP_OFF_E + SP_ATOM_BYTES;         // 50 KB
 constexpr int SP_PAIR_FEATS = 256;
 constexpr int SP_DRAIN_WARPS = 8;
 constexpr int SP_THREADS = 32 * (2 + SP_DRAIN_WARPS);
@@ -238,17 +239,13 @@ template <typename T>
 __global__ void __launch_bounds__(SP_THREADS, 1) gemm_sp_kernel(const SpGemmParams prm, const __grid_constant__ SpGemmMaps maps) {
     extern __shared__ char smem_raw[];
     char *smem = reinterpret_cast<char *>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
-    char *a_ring = smem;                                 // SP_NA slots: 16 KB tile (1024-aligned) + 2 KB metadata
-    char *b_ring = smem + SP_NA * SP_A_SLOT;             // SP_NB slots of 16 KB
-    char *misc = b_ring + SP_NB * SP_B_SLOT;
-    uint64_t *full_a = reinterpret_cast<uint64_t *>(misc);   // meaningful in the leader only
-    uint64_t *full_b = full_a + SP_NA;                        // leader only
-    uint64_t *empty_a = full_b + SP_NB;
-    uint64_t *empty_b = empty_a + SP_NA;
-    uint64_t *acc_full = empty_b + SP_NB;
+    char *misc = smem + SP_STAGES * SP_STAGE;
+    uint64_t *full = reinterpret_cast<uint64_t *>(misc);     // meaningful in the leader only
+    uint64_t *empty = full + SP_STAGES;
+    uint64_t *acc_full = empty + SP_STAGES;
     uint64_t *acc_free = acc_full + 1;                        // leader only
     uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(misc + 248);
-    static_assert((2 * SP_NA + 2 * SP_NB + 2) * 8 <= 248 && SP_A_SLOT % 1024 == 0 && SP_B_SLOT % 1024 == 0, "shared-memory plan");
+    static_assert((2 * SP_STAGES + 2) * 8 <= 248 && SP_STAGE % 1024 == 0, "shared-memory plan");
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const uint32_t rank = cluster_ctarank();
@@ -256,11 +253,10 @@ __global__ void __launch_bounds__(SP_THREADS, 1) gemm_sp_kernel(const SpGemmPara
     const int pair = (int)(blockIdx.x >> 1), npairs = (int)(gridDim.x >> 1);
     const int ntiles = prm.tiles_f * prm.tiles_t;
     const int my_tiles = (pair < ntiles) ? (ntiles - pair + npairs - 1) / npairs : 0;
-    const int nj = (int)((prm.red + TC_BK - 1) / TC_BK);  // dY tiles (64 reduction elements) per output tile
+    const int nst = (int)((prm.red + SP_ATOM - 1) / SP_ATOM);  // stages (128 reduction elements) per output tile
 
     if (tid == 0) {
-        for (int s = 0; s < SP_NA; s++) { mbar_init(&full_a[s], 1); mbar_init(&empty_a[s], 1); }
-        for (int s = 0; s < SP_NB; s++) { mbar_init(&full_b[s], 1); mbar_init(&empty_b[s], 1); }
+        for (int s = 0; s < SP_STAGES; s++) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
         mbar_init(acc_full, 1);
         mbar_init(acc_free, 2 * SP_DRAIN_WARPS);  // the drain warps of both CTAs
         mbar_fence_init();
@@ -271,8 +267,7 @@ __global__ void __launch_bounds__(SP_THREADS, 1) gemm_sp_kernel(const SpGemmPara
     cluster_sync_all();  // barriers of both CTAs are initialised before anyone arrives remotely
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
-    const uint32_t full_a_leader = map_to_rank(smem_u32(&full_a[0]), 0);
-    const uint32_t full_b_leader = map_to_rank(smem_u32(&full_b[0]), 0);
+    const uint32_t full_leader = map_to_rank(smem_u32(&full[0]), 0);
     const uint32_t acc_free_leader = map_to_rank(smem_u32(acc_free), 0);
 
     auto tile_origin = [&](int ti, int &tile_f, int &tok0) {
@@ -284,28 +279,23 @@ __global__ void __launch_bounds__(SP_THREADS, 1) gemm_sp_kernel(const SpGemmPara
     if (warp == 0) {
         // ------------------------------------------------------------------ TMA producer (one lane per CTA)
         if (lane == 0) {
-            int at = 0, bt = 0;
+            int it = 0;
             bool ok = true;
             asm volatile("griddepcontrol.wait;" ::: "memory");  // the expansion pass's output arrives through the loads below
             for (int ti = 0; ti < my_tiles && ok; ti++) {
                 int tile_f, tok0;
                 tile_origin(ti, tile_f, tok0);
                 const int half_f = tile_f * 2 + (int)rank;  // this CTA's 128-feature tile = its metadata atom row
-                for (int j = 0; j < nj; j++) {
-                    if ((j & 1) == 0) {
-                        const int sa = at % SP_NA;
-                        if (!(ok = mbar_wait_cluster_bounded(&empty_a[sa], (uint32_t)(((at / SP_NA) & 1) ^ 1), prm.status, 31))) break;
-                        if (leader) mbar_expect_tx(&full_a[sa], 2 * SP_A_SLOT);  // both CTAs report to this barrier
-                        char *slot = a_ring + sa * SP_A_SLOT;
-                        tma_load_2d_pair(slot, &maps.a, (j >> 1) * 64, half_f * TC_BM, full_a_leader + sa * 8);
-                        tma_load_2d_pair(slot + TC_A_BYTES, &maps.e, 0, (int)(((int64_t)half_f * prm.n_rt + (j >> 1)) * 2), full_a_leader + sa * 8);
-                        at++;
-                    }
-                    const int sb = bt % SP_NB;
-                    if (!(ok = mbar_wait_cluster_bounded(&empty_b[sb], (uint32_t)(((bt / SP_NB) & 1) ^ 1), prm.status, 32))) break;
-                    if (leader) mbar_expect_tx(&full_b[sb], 2 * SP_B_SLOT);
-                    tma_load_2d_pair(b_ring + sb * SP_B_SLOT, &maps.b, j * TC_BK, tok0 + (int)rank * 128, full_b_leader + sb * 8);
-                    bt++;
+                for (int j = 0; j < nst; j++, it++) {
+                    const int s = it % SP_STAGES;
+                    if (!(ok = mbar_wait_cluster_bounded(&empty[s], (uint32_t)(((it / SP_STAGES) & 1) ^ 1), prm.status, 31))) break;
+                    if (leader) mbar_expect_tx(&full[s], 2 * SP_STAGE);  // both CTAs report to this barrier
+                    char *stage = smem + s * SP_STAGE;
+                    const uint32_t bar = full_leader + s * 8;
+                    tma_load_2d_pair(stage, &maps.a, j * 64, half_f * TC_BM, bar);
+                    tma_load_2d_pair(stage + SP_OFF_B, &maps.b, j * SP_ATOM, tok0 + (int)rank * 128, bar);
+                    tma_load_2d_pair(stage + SP_OFF_B + SP_B_HALF, &maps.b, j * SP_ATOM + TC_BK, tok0 + (int)rank * 128, bar);
+                    tma_load_2d_pair(stage + SP_OFF_E, &maps.e, 0, (int)(((int64_t)half_f * prm.n_rt + j) * 2), bar);
                 }
             }
         }
@@ -314,33 +304,25 @@ __global__ void __launch_bounds__(SP_THREADS, 1) gemm_sp_kernel(const SpGemmPara
         if (leader && lane == 0) {
             const uint32_t idesc = make_idesc_sp_pair<T>();
             bool ok = true;
-            int at = 0, bt = 0;
+            int it = 0;
             for (int ti = 0; ti < my_tiles && ok; ti++) {
                 if (ti > 0) ok = mbar_wait_cluster_bounded(acc_free, (uint32_t)((ti - 1) & 1), prm.status, 36);
                 if (!ok) break;
                 tc_fence_after();
-                int sa = 0;
-                uint32_t e_set = 0;
-                for (int j = 0; j < nj; j++, bt++) {
-                    const int sb = bt % SP_NB;
-                    if ((j & 1) == 0) {
-                        sa = at % SP_NA;
-                        if (!(ok = mbar_wait_cluster_bounded(&full_a[sa], (uint32_t)((at / SP_NA) & 1), prm.status, 33))) break;
-                        tc_fence_after();
-                        e_set = tmem_base + SP_E_COL + 4u * (uint32_t)(at & 1);
-                        tc2_copy_meta(e_set, smem_u32(a_ring + sa * SP_A_SLOT + TC_A_BYTES));
-                    }
-                    if (!(ok = mbar_wait_cluster_bounded(&full_b[sb], (uint32_t)((bt / SP_NB) & 1), prm.status, 34))) break;
+                for (int j = 0; j < nst; j++, it++) {
+                    const int s = it % SP_STAGES;
+                    if (!(ok = mbar_wait_cluster_bounded(&full[s], (uint32_t)((it / SP_STAGES) & 1), prm.status, 33))) break;
                     tc_fence_after();
-                    // second half of the A slot: 32 stored values = 64 bytes = 4 descriptor units further
-                    const uint64_t adesc = make_sw128_desc(smem_u32(a_ring + sa * SP_A_SLOT)) + (uint64_t)((j & 1) * 4);
-                    const uint64_t bdesc = make_sw128_desc(smem_u32(b_ring + sb * SP_B_SLOT));
-                    const uint32_t e_addr = e_set + 2u * (uint32_t)(j & 1);  // metadata columns are addressed in pairs
+                    const uint32_t stage = smem_u32(smem + s * SP_STAGE);
+                    const uint32_t e_set = tmem_base + SP_E_COL + 4u * (uint32_t)(it & 1);
+                    tc2_copy_meta(e_set, stage + SP_OFF_E);
+                    const uint64_t adesc = make_sw128_desc(stage);
+                    const uint64_t bdesc0 = make_sw128_desc(stage + SP_OFF_B), bdesc1 = make_sw128_desc(stage + SP_OFF_B + SP_B_HALF);
 #pragma unroll
-                    for (int k = 0; k < 2; k++)  // 32 reduction elements per instruction: 16 stored values of A (2 units), 32 of dY (4 units)
-                        tc2_mma_sp_f16(tmem_base, adesc + 2 * k, bdesc + 4 * k, e_addr, idesc | (uint32_t)k, (j == 0 && k == 0) ? 0u : 1u);
-                    tc2_commit_both(&empty_b[sb]);
-                    if ((j & 1) || j == nj - 1) { tc2_commit_both(&empty_a[sa]); at++; }
+                    for (int k = 0; k < 4; k++)  // 32 reduction elements per instruction: 16 stored values of A (2 descriptor units), 32 of dY (4 units)
+                        tc2_mma_sp_f16(tmem_base, adesc + 2 * k, (k < 2 ? bdesc0 : bdesc1) + 4 * (k & 1), e_set + (uint32_t)(k & 2),
+                                       idesc | (uint32_t)(k & 1), (j == 0 && k == 0) ? 0u : 1u);  // metadata columns are addressed in pairs
+                    tc2_commit_both(&empty[s]);
                 }
                 tc2_commit_both(acc_full);  // arrives in both CTAs when the tile's MMAs have written TMEM (also on the error path)
             }
@@ -433,7 +415,7 @@ template <typename T, int N_> static int sp_expand_launch(const SpExpandParams &
 }
 
 template <typename T> static int sp_gemm_launch(const SpGemmParams &p, const SpGemmMaps &maps, cudaStream_t st) {
-    const size_t smem = (size_t)SP_NA * SP_A_SLOT + (size_t)SP_NB * SP_B_SLOT + 256 + 1024;
+    const size_t smem = (size_t)SP_STAGES * SP_STAGE + 256 + 1024;
     int dev = 0, sms = 148;
     NMG_CUDA(cudaGetDevice(&dev));
     NMG_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
