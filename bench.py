@@ -316,6 +316,50 @@ def sweep_table(torch, ops, nat, dev, peaks, fma_peak):
     return rows
 
 
+def transposed_table(torch, ops, nat, dev, peaks):
+    """Transposed product dX = dY W (the backward pass) in bf16: structured-sparse tensor cores (tcgen05.mma.sp) with the
+    compressed copy built per call and kept across calls, the dense-rate tensor-core kernels, and cuBLAS on the densified
+    weight.  4096^2 at every pattern of the sweep, and the 16384^2 2:8 weight of the sharded workload."""
+    rows = []
+
+    def timed(fn, reps=10):
+        fn()
+        torch.cuda.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for _ in range(reps):
+            fn()
+        b.record()
+        torch.cuda.synchronize()
+        return a.elapsed_time(b) / reps
+
+    cases = [(SW_M, SW_K, SW_TOK, n, m, 1.0, 10) for (n, m) in SWEEP] + [(SH_M, SH_K, SH_TOK, SH_N, SH_MM, 0.02, 4)]
+    for (M, K, TOK, n, m, scale, reps) in cases:
+        w = (torch.randn(M, K, generator=torch.Generator(device=dev).manual_seed(0), device=dev) * scale).bfloat16()
+        dy = torch.randn(TOK, M, generator=torch.Generator(device=dev).manual_seed(2), device=dev).bfloat16()
+        val, idx = ops.sparsify(w.unsqueeze(0), n, m, G)
+        del w
+        dense = ops.densify(val, idx, 1, M, K, n, m, G)[0]
+        sp24 = ops.pack_sp24(val, idx, M, K, n, m, G)
+        t_sp = timed(lambda: ops.spmm_t(val, idx, M, K, n, m, G, dy), reps)
+        t_kept = timed(lambda: ops.spmm_t(val, idx, M, K, n, m, G, dy, sp24=sp24), reps)
+        t_rate = timed(lambda: ops.spmm_t(val, idx, M, K, n, m, G, dy, algo=nat.NMG_ALGO_TENSOR_DENSE), reps)
+        t_cublas = timed(lambda: torch.mm(dy, dense), reps)
+        dx = ops.spmm_t(val, idx, M, K, n, m, G, dy, sp24=sp24)
+        cols = sampled_rows(torch, CHECK_ROWS, K, 13, dev)
+        err = rel_fro(dx[:, cols], dy.double() @ dense[:, cols].double())
+        flops_dense = 2.0 * M * K * TOK
+        rows.append({"shape": f"{M}x{K}x{TOK}", "nm": f"{n}:{m}", "dtype": "bf16",
+                     "ms_sparse_mma": t_sp, "ms_sparse_mma_kept_copy": t_kept, "ms_dense_rate_kernels": t_rate, "cublas_dense_ms": t_cublas,
+                     "speedup_vs_cublas": t_cublas / t_kept, "speedup_vs_dense_rate_kernels": t_rate / t_kept,
+                     "dense_equivalent_tflops": flops_dense / t_kept / 1e9, "useful_tflops": flops_dense * n / m / t_kept / 1e9,
+                     "frac_of_sparse_tensor_peak": flops_dense / t_kept / 1e9 / (2 * peaks["bf16_tflops"]),
+                     "rel_fro_vs_float64": err, "tolerance": TOL["bf16"]})
+        del val, idx, dense, sp24, dy, dx
+        torch.cuda.empty_cache()
+    return rows
+
+
 def run_ours(args):
     import torch
     import torch.distributed as dist
@@ -522,12 +566,13 @@ def run_ours(args):
                         "unit": "TFLOP/s", "frac": achieved / fma.value if fma.value else None,
                         "peak_source": "fp32 FFMA loop measured in this run (nmg_measure_fma_peak)", "traffic": None,
                         "ms_per_launch": kms, "algorithmic_flops_per_launch": alg}
-        sweep = None
+        sweep = transposed = None
         if world == 1 and not args.no_sweep:
             if args.workload == "sharded":
-                del layer, panels, x, y_dev
+                del layer, panels, x, y_dev, y_last
                 torch.cuda.empty_cache()
             sweep = sweep_table(torch, ops, nat, dev, peaks, fma.value)
+            transposed = transposed_table(torch, ops, nat, dev, peaks)
         cpu = None
         if world == 1:  # the CPU baseline is reported at N = 1 only; `bench.py --impl reference` times it at every N
             dt, flops, kind, cores, desc = time_cpu(args.workload, 3, 1)
@@ -538,7 +583,7 @@ def run_ours(args):
             "dtype": dtype_name, "data": "synthetic", "config": config_dict(args.workload, world, exchange_used if args.workload == "sharded" else "none", rounds if args.workload == "sharded" else 1),
             "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
             "gpu_launches": args.steps * launches_per_step, "clocks": clocks, "roofline": roofline, "cpu_baseline": cpu,
-            "fp32_fma_peak_tflops": fma.value, "sweep": sweep, "check": check,
+            "fp32_fma_peak_tflops": fma.value, "sweep": sweep, "transposed": transposed, "check": check,
         }
     if world > 1:
         dist.barrier()

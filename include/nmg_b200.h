@@ -127,6 +127,19 @@ int nmg_spmm_t(const void *val, const int16_t *idx, const void *packed, int64_t 
                int dtype, const void *dy, int64_t ld_dy, int64_t tokens, void *dx, int64_t ld_dx, int algo,
                void *workspace, size_t workspace_bytes, void *stream);
 
+/* The transposed product from a compressed transposed copy the caller keeps ("sp24": W^T with two stored values and two
+ * 2-bit positions per aligned group of four weight rows, in the tensor core's 2:4 operand layout).  nmg_spmm_t builds
+ * this copy in its workspace on every call; a caller that runs many backward passes on one weight builds it once with
+ * nmg_pack_sp24 and calls nmg_spmm_t_sp24, which launches the structured-sparse matmul alone.  The copy is an internal
+ * cache like the packed copy: derived from (val, idx), never serialised, layout may change between versions.
+ * nmg_sp24_bytes returns 0 when the weight is outside the structure (fp32, n > 2, m not in {4, 8, 16, 32, 64}).
+ * sp24 must be 256-byte aligned; dy rows 16-byte aligned.  No counterpart in the reference (it has no backward). */
+size_t nmg_sp24_bytes(int64_t M, int64_t K, int n, int m, int g, int dtype);
+int nmg_pack_sp24(const void *val, const int16_t *idx, int64_t M, int64_t K, int n, int m, int g, int dtype, void *sp24,
+                  size_t sp24_bytes, void *stream);
+int nmg_spmm_t_sp24(const void *sp24, int64_t M, int64_t K, int n, int m, int g, int dtype, const void *dy, int64_t ld_dy,
+                    int64_t tokens, void *dx, int64_t ld_dx, void *stream);
+
 /* Whether nmg_spmm (transposed = 0) or nmg_spmm_t (transposed = 1) would read the packed copy for this problem under
  * `algo`, assuming aligned operands: 1 or 0.  Lets a host build and keep packed copies only for the weights and batch
  * sizes that use them (the two-pass tensor-core variant and the SIMT forward kernel do not).  `layout` is ignored for

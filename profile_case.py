@@ -28,6 +28,7 @@ def main():
     ap.add_argument("--algo", default="auto", choices=["auto", "simt", "tensor", "tensor_dense"])
     ap.add_argument("--reps", type=int, default=3)
     ap.add_argument("--no-packed", action="store_true", help="rebuild the column-ordered weight copy in every call")
+    ap.add_argument("--sp24", action="store_true", help="bwd: keep the compressed transposed copy across calls (as the plugin's backward does)")
     a = ap.parse_args()
     n, m = map(int, a.nm.split(":"))
     dtype = {"f32": torch.float32, "f16": torch.float16, "bf16": torch.bfloat16}[a.dtype]
@@ -42,6 +43,7 @@ def main():
     xt = x.t().contiguous()
     wd = w.to(dtype).unsqueeze(0)
     packed = None if a.no_packed else ops.pack(val, idx, M, K, n, m, g)
+    sp24 = ops.pack_sp24(val, idx, M, K, n, m, g) if a.sp24 else None
 
     def call():
         if a.op == "fwd":
@@ -49,7 +51,7 @@ def main():
         if a.op == "fwd_kmajor":
             return ops.spmm(val, idx, M, K, n, m, g, xt, layout=nat.NMG_ACT_K_MAJOR, algo=algo)
         if a.op == "bwd":
-            return ops.spmm_t(val, idx, M, K, n, m, g, dy, algo=algo, packed=packed)
+            return ops.spmm_t(val, idx, M, K, n, m, g, dy, algo=algo, packed=packed, sp24=sp24)
         if a.op == "sparsify":
             return ops.sparsify(wd, n, m, g)
         return ops.densify(val, idx, 1, M, K, n, m, g)

@@ -174,7 +174,7 @@ extern "C" size_t nmg_spmm_t_workspace_bytes(int64_t M, int64_t K, int64_t token
         tensor = (tc_use_dense(geo, dtype, tokens) ? tc_dense_workspace_bytes(geo, dtype, true)
                                                    : pack + tc_ksplit_workspace_bytes(geo, dtype, true, tokens)) +
                  tc_split_workspace_bytes(geo, dtype, true, tokens);
-    if (use_sp(geo, dtype, tokens, algo) && tc_sp_workspace_bytes(geo) > tensor) tensor = tc_sp_workspace_bytes(geo);
+    if (use_sp(geo, dtype, tokens, algo) && tc_sp_copy_bytes(geo) + 256 > tensor) tensor = tc_sp_copy_bytes(geo) + 256;
     return simt > tensor ? simt : tensor;
 }
 
@@ -201,11 +201,52 @@ extern "C" int nmg_spmm_t(const void *val, const int16_t *idx, const void *packe
     const bool tensor = algo == NMG_ALGO_TENSOR || algo == NMG_ALGO_TENSOR_DENSE || (algo == NMG_ALGO_AUTO && can_tensor && K >= 64);
     // The rows of W are the reduction axis here, so the n:m structure is one the tensor cores can skip: structured-sparse
     // MMA at twice the dense rate (16-bit weights, n <= 2, m a power of two >= 4).
-    if (tensor && use_sp(geo, dtype, tokens, algo))
-        return tc_sp_matmul_t(geo, dtype, val, idx, dy, ld_dy, tokens, dx, ld_dx, workspace, workspace_bytes, st);
+    if (tensor && use_sp(geo, dtype, tokens, algo)) {
+        const size_t need = tc_sp_copy_bytes(geo);
+        char *buf = align256(workspace);
+        if (!workspace || workspace_bytes < need + 256) NMG_FAIL(NMG_ERR_WORKSPACE, "workspace of %zu bytes required for the compressed transposed weight, got %zu", need + 256, workspace_bytes);
+        const ProfileEvents pe = take_profile_events();
+        if (pe.start) NMG_CUDA(cudaEventRecord(pe.start, st));
+        if ((rc = tc_sp_pack(geo, dtype, val, idx, buf, need, st))) return rc;
+        rc = tc_sp_matmul_t(geo, dtype, buf, dy, ld_dy, tokens, dx, ld_dx, st);
+        if (rc == NMG_OK && pe.stop) NMG_CUDA(cudaEventRecord(pe.stop, st));
+        return rc;
+    }
     const bool dense = tensor && tc_use_dense(geo, dtype, tokens);
     if (!dense && (rc = resolve_packed(geo, dtype, val, idx, packed, &ws, &left, &pat, &nval, st))) return rc;
     void *dxs[1] = {dx};
     if (tensor) return tc_matmul(geo, dtype, true, dense, val, idx, pat, nval, dy, ld_dy, tokens, nullptr, dxs, 1, nullptr, ld_dx, 1, ws, left, st);
     return simt_bwd(geo, dtype, pat, nval, dy, ld_dy, tokens, dx, ld_dx, ws, left, st);
+}
+
+// ---- compressed transposed copy ("sp24") kept by the caller ---------------------------------------------------------
+extern "C" size_t nmg_sp24_bytes(int64_t M, int64_t K, int n, int m, int g, int dtype) {
+    Geo geo;
+    if (make_geo(M, K, n, m, g, &geo) || !tc_sp_supported(geo, dtype)) return 0;
+    return tc_sp_copy_bytes(geo);
+}
+
+extern "C" int nmg_pack_sp24(const void *val, const int16_t *idx, int64_t M, int64_t K, int n, int m, int g, int dtype, void *sp24,
+                             size_t sp24_bytes, void *stream) {
+    Geo geo;
+    int rc = make_geo(M, K, n, m, g, &geo);
+    if (rc) return rc;
+    if ((rc = check_common(dtype, 1, val, idx, sp24, sp24))) return rc;
+    return tc_sp_pack(geo, dtype, val, idx, sp24, sp24_bytes, (cudaStream_t)stream);
+}
+
+extern "C" int nmg_spmm_t_sp24(const void *sp24, int64_t M, int64_t K, int n, int m, int g, int dtype, const void *dy, int64_t ld_dy,
+                               int64_t tokens, void *dx, int64_t ld_dx, void *stream) {
+    Geo geo;
+    int rc = make_geo(M, K, n, m, g, &geo);
+    if (rc) return rc;
+    if ((rc = check_common(dtype, tokens, sp24, sp24, dy, dx))) return rc;
+    if (ld_dy < M) NMG_FAIL(NMG_ERR_INVALID, "ld_dy=%lld is smaller than M", (long long)ld_dy);
+    if (ld_dx < K) NMG_FAIL(NMG_ERR_INVALID, "ld_dx=%lld is smaller than K", (long long)ld_dx);
+    cudaStream_t st = (cudaStream_t)stream;
+    const ProfileEvents pe = take_profile_events();
+    if (pe.start) NMG_CUDA(cudaEventRecord(pe.start, st));
+    rc = tc_sp_matmul_t(geo, dtype, sp24, dy, ld_dy, tokens, dx, ld_dx, st);
+    if (rc == NMG_OK && pe.stop) NMG_CUDA(cudaEventRecord(pe.stop, st));
+    return rc;
 }

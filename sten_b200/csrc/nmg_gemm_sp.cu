@@ -401,7 +401,6 @@ static SpLayout sp_layout(const Geo &geo) {
     l.total = l.asp_bytes + l.meta_bytes + 256;
     return l;
 }
-size_t tc_sp_workspace_bytes(const Geo &geo) { return sp_layout(geo).total + 256; }
 
 template <typename T, int N_> static int sp_expand_launch(const SpExpandParams &p, size_t smem, int64_t items, cudaStream_t st) {
     int dev = 0, sms = 148;
@@ -441,19 +440,19 @@ template <typename T> static int sp_gemm_launch(const SpGemmParams &p, const SpG
     return NMG_OK;
 }
 
-// dx[tokens][ld_dx] = dy[tokens][ld_dy] * W for a 16-bit weight the structured-sparse path supports.  dy rows must be
-// 16-byte aligned (TMA).  ws: tc_sp_workspace_bytes(geo) bytes, holds A_sp and the metadata for the duration of the call.
-int tc_sp_matmul_t(const Geo &geo, int dtype, const void *val, const int16_t *idx, const void *dy, int64_t ld_dy, int64_t tokens,
-                   void *dx, int64_t ld_dx, void *ws, size_t ws_bytes, cudaStream_t st) {
+// (val, idx) -> compressed transposed copy at `buf` (tc_sp_copy_bytes(geo) bytes, 256-byte aligned): A_sp followed by
+// the metadata atoms.  One memset (metadata nibbles start as the valid pair (0, 3): atoms of a ragged last feature tile
+// are only partly written) and one kernel.
+int tc_sp_pack(const Geo &geo, int dtype, const void *val, const int16_t *idx, void *buf, size_t buf_bytes, cudaStream_t st) {
     if (!tc_sp_supported(geo, dtype)) NMG_FAIL(NMG_ERR_UNSUPPORTED, "the structured-sparse path needs a 16-bit weight with n <= 2 and m in {4, 8, 16, 32, 64}");
     const SpLayout lay = sp_layout(geo);
-    if (!ws || ws_bytes < lay.total + 256) NMG_FAIL(NMG_ERR_WORKSPACE, "workspace of %zu bytes required for the compressed transposed weight, got %zu", lay.total + 256, ws_bytes);
-    char *base = reinterpret_cast<char *>(((uintptr_t)ws + 255) & ~(uintptr_t)255);
+    if (!buf || buf_bytes < lay.total) NMG_FAIL(NMG_ERR_WORKSPACE, "buffer of %zu bytes required for the compressed transposed weight, got %zu", lay.total, buf_bytes);
+    if (reinterpret_cast<uintptr_t>(buf) & 255) NMG_FAIL(NMG_ERR_INVALID, "the compressed transposed copy must be 256-byte aligned");
+    char *base = static_cast<char *>(buf);
     char *meta = base + lay.asp_bytes;
     int rc;
     PatternTable tab;
     if ((rc = get_pattern_table(geo.n, geo.m, &tab))) return rc;
-    // every metadata nibble starts as the valid pair (0, 3): atoms of the ragged last feature tile are only partly written
     NMG_CUDA(cudaMemsetAsync(meta, 0xCC, lay.meta_bytes, st));
 
     SpExpandParams sp{};
@@ -467,17 +466,24 @@ int tc_sp_matmul_t(const Geo &geo, int dtype, const void *val, const int16_t *id
     const size_t esmem = sp_expand_smem(geo);
     const int64_t items = lay.n_rt * (SP_ATOM / SP_ROWS_ITEM) * geo.nc;
     const bool aligned = (reinterpret_cast<uintptr_t>(val) & 15) == 0 && (reinterpret_cast<uintptr_t>(idx) & 15) == 0;
-    const ProfileEvents pe = take_profile_events();
-    if (pe.start) NMG_CUDA(cudaEventRecord(pe.start, st));
-    if (dtype == NMG_F16) {
-        rc = !aligned ? sp_expand_launch<__half, 0>(sp, esmem, items, st)
-             : geo.n == 1 ? sp_expand_launch<__half, 1>(sp, esmem, items, st) : sp_expand_launch<__half, 2>(sp, esmem, items, st);
-    } else {
-        rc = !aligned ? sp_expand_launch<__nv_bfloat16, 0>(sp, esmem, items, st)
-             : geo.n == 1 ? sp_expand_launch<__nv_bfloat16, 1>(sp, esmem, items, st) : sp_expand_launch<__nv_bfloat16, 2>(sp, esmem, items, st);
-    }
-    if (rc) return rc;
+    if (dtype == NMG_F16)
+        return !aligned ? sp_expand_launch<__half, 0>(sp, esmem, items, st)
+               : geo.n == 1 ? sp_expand_launch<__half, 1>(sp, esmem, items, st) : sp_expand_launch<__half, 2>(sp, esmem, items, st);
+    return !aligned ? sp_expand_launch<__nv_bfloat16, 0>(sp, esmem, items, st)
+           : geo.n == 1 ? sp_expand_launch<__nv_bfloat16, 1>(sp, esmem, items, st) : sp_expand_launch<__nv_bfloat16, 2>(sp, esmem, items, st);
+}
+size_t tc_sp_copy_bytes(const Geo &geo) { return sp_layout(geo).total; }
 
+// dx[tokens][ld_dx] = dy[tokens][ld_dy] * W from the compressed transposed copy.  dy rows must be 16-byte aligned (TMA).
+int tc_sp_matmul_t(const Geo &geo, int dtype, const void *sp_copy, const void *dy, int64_t ld_dy, int64_t tokens, void *dx, int64_t ld_dx,
+                   cudaStream_t st) {
+    if (!tc_sp_supported(geo, dtype)) NMG_FAIL(NMG_ERR_UNSUPPORTED, "the structured-sparse path needs a 16-bit weight with n <= 2 and m in {4, 8, 16, 32, 64}");
+    if (!sp_copy || (reinterpret_cast<uintptr_t>(sp_copy) & 255)) NMG_FAIL(NMG_ERR_INVALID, "the compressed transposed copy must be non-NULL and 256-byte aligned");
+    if ((reinterpret_cast<uintptr_t>(dy) & 15) || (ld_dy % 8)) NMG_FAIL(NMG_ERR_UNSUPPORTED, "the structured-sparse path needs 16-byte aligned gradient rows");
+    const SpLayout lay = sp_layout(geo);
+    const char *base = static_cast<const char *>(sp_copy);
+    const char *meta = base + lay.asp_bytes;
+    int rc;
     SpGemmMaps maps;
     if ((rc = encode_tmap_2d(&maps.a, dtype, base, (uint64_t)lay.ld_a, (uint64_t)geo.K, (uint64_t)lay.ld_a, 64, TC_BM, 1))) return rc;
     if ((rc = encode_tmap_2d(&maps.b, dtype, dy, (uint64_t)geo.M, (uint64_t)tokens, (uint64_t)ld_dy, TC_BK, 128, 1))) return rc;
@@ -490,9 +496,7 @@ int tc_sp_matmul_t(const Geo &geo, int dtype, const void *val, const int16_t *id
     gp.tiles_f = (int)(lay.n_ft / 2);
     gp.tiles_t = (int)((tokens + TC_BN - 1) / TC_BN);
     gp.status = status;
-    rc = dtype == NMG_F16 ? sp_gemm_launch<__half>(gp, maps, st) : sp_gemm_launch<__nv_bfloat16>(gp, maps, st);
-    if (rc == NMG_OK && pe.stop) NMG_CUDA(cudaEventRecord(pe.stop, st));
-    return rc;
+    return dtype == NMG_F16 ? sp_gemm_launch<__half>(gp, maps, st) : sp_gemm_launch<__nv_bfloat16>(gp, maps, st);
 }
 
 }  // namespace nmg

@@ -59,9 +59,10 @@ int tc_dense_matmul(const Geo &geo, int dtype, bool transposed, const void *val,
 // the reduction axis (the weight's rows).  16-bit weights with n <= 2 and m in {4, 8, 16, 32, 64}; taken from the token
 // count at which the two-pass variant is taken (the compression pass is per call, like the dense expansion).
 bool tc_sp_supported(const Geo &geo, int dtype);
-size_t tc_sp_workspace_bytes(const Geo &geo);
-int tc_sp_matmul_t(const Geo &geo, int dtype, const void *val, const int16_t *idx, const void *dy, int64_t ld_dy, int64_t tokens,
-                   void *dx, int64_t ld_dx, void *ws, size_t ws_bytes, cudaStream_t st);
+size_t tc_sp_copy_bytes(const Geo &geo);  // compressed transposed copy: values of W^T (M * K bytes) + metadata (M * K / 8)
+int tc_sp_pack(const Geo &geo, int dtype, const void *val, const int16_t *idx, void *buf, size_t buf_bytes, cudaStream_t st);
+int tc_sp_matmul_t(const Geo &geo, int dtype, const void *sp_copy, const void *dy, int64_t ld_dy, int64_t tokens, void *dx, int64_t ld_dx,
+                   cudaStream_t st);
 
 // ---- specialised forward kernel: parameters, shared-memory plan, per-(n, m) launchers
 struct FwdParams {

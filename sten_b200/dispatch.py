@@ -533,8 +533,9 @@ def _to(base_impl, func, types, *args, **kwargs):
         device = rest.pop(0)
         if rest and isinstance(rest[0], torch.dtype):
             dtype = rest.pop(0)
-    non_blocking = rest.pop(0) if rest else kwargs.get("non_blocking", False)
-    do_copy = rest.pop(0) if rest else kwargs.get("copy", False)
+    # nn.Module.to() passes non_blocking positionally and may pass None; Tensor.to() itself only takes booleans
+    non_blocking = bool(rest.pop(0) if rest else kwargs.get("non_blocking", False))
+    do_copy = bool(rest.pop(0) if rest else kwargs.get("copy", False))
     device = torch.device(device) if device is not None else self.device
     if device.type == "cuda" and device.index is None and self.device.type == "cuda":
         device = torch.device("cuda", torch.cuda.current_device())

@@ -124,6 +124,22 @@ class GroupedNMTensor:
             self.__dict__["_packed_cache"] = cache
         return cache[1]
 
+    def packed_sp24(self):
+        """Compressed transposed copy for the structured-sparse backward product (``nmg_pack_sp24``), or None when the
+        weight is outside the 2:4 structure (fp32, n > 2, m not a power of two >= 4).  Cached like ``packed()``."""
+        s = self.nm_strides
+        if len(s["dense_shape"]) != 2 or s["sparse_dim"] != 0:
+            return None
+        M, K = (int(v) for v in s["dense_shape"])
+        if not self.val.is_cuda or ops.sp24_bytes(M, K, s["n"], s["m"], s["group_size"], self.val.dtype) == 0:
+            return None
+        key = (self.val.data_ptr(), self.val._version, self.idx.data_ptr(), self.idx._version, self.val.dtype)
+        cache = self.__dict__.get("_sp24_cache")
+        if cache is None or cache[0] != key:
+            cache = (key, ops.pack_sp24(self.val, self.idx, M, K, s["n"], s["m"], s["group_size"]))
+            self.__dict__["_sp24_cache"] = cache
+        return cache[1]
+
     def to(self, device=None, dtype=None, non_blocking=False, copy=False):
         """Same layout on another device / in another floating dtype (indices are dtype independent)."""
         val = self.val.to(device=device, dtype=dtype, non_blocking=non_blocking, copy=copy)

@@ -63,6 +63,12 @@ def _packed_or_none(gnm, geometry, tokens, layout=nat.NMG_ACT_TOKEN_MAJOR, trans
     return gnm.packed()
 
 
+def _sp24_or_none(gnm, tokens):
+    """The cached compressed transposed copy when the backward product of this many tokens runs on the structured-sparse
+    tensor cores (16-bit weight inside the 2:4 structure), else None (nothing is built)."""
+    return gnm.packed_sp24() if tokens >= ops.SP24_MIN_TOKENS else None
+
+
 def sparse_dense_mul_dispatch(weight, dense2d, bias, layout):
     """One C-ABI call; replaces the compile-or-load + ctypes call of the reference (sten_impls.py:44-140)."""
     gnm, M, K, n, m, g = _weight_geometry(weight)
@@ -98,8 +104,9 @@ def _linear_bwd(ctx, grad_outputs, input_sparsifiers):
     dy2d = dy.reshape(-1, M)
     dx = dw = db = None
     if needs[0]:
-        dx = ops.spmm_t(gnm.val, gnm.idx, M, K, n, m, g, dy2d,
-                        packed=_packed_or_none(gnm, (M, K, n, m, g), dy2d.shape[0], transposed=True)).reshape(x.shape)
+        sp24 = _sp24_or_none(gnm, dy2d.shape[0])
+        dx = ops.spmm_t(gnm.val, gnm.idx, M, K, n, m, g, dy2d, sp24=sp24,
+                        packed=None if sp24 is not None else _packed_or_none(gnm, (M, K, n, m, g), dy2d.shape[0], transposed=True)).reshape(x.shape)
     if needs[1]:
         # dense weight gradient (training of nmg weights is outside the inference hot path): plain GEMM
         dw = dy2d.t().mm(x.reshape(-1, K))
@@ -133,8 +140,9 @@ def _mm_bwd(ctx, grad_outputs, input_sparsifiers):
     if needs[1]:
         # dB = W^T dC : the transposed kernel computes (dC^T W)[N, K]; hand back its transpose
         dct = dc.t().contiguous()
-        db = ops.spmm_t(gnm.val, gnm.idx, M, K, n, m, g, dct,
-                        packed=_packed_or_none(gnm, (M, K, n, m, g), dct.shape[0], transposed=True)).t()
+        sp24 = _sp24_or_none(gnm, dct.shape[0])
+        db = ops.spmm_t(gnm.val, gnm.idx, M, K, n, m, g, dct, sp24=sp24,
+                        packed=None if sp24 is not None else _packed_or_none(gnm, (M, K, n, m, g), dct.shape[0], transposed=True)).t()
     return dw, db
 
 

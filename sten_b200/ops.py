@@ -212,8 +212,33 @@ def spmm_replicated(val, idx, M, K, n, m, g, act, out_ptrs, ld_out, bias=None, m
                                         ws.data_ptr() if ws is not None else None, nbytes, _stream(dev)))
 
 
-def spmm_t(val, idx, M, K, n, m, g, dy, algo=nat.NMG_ALGO_AUTO, packed=None):
-    """dy [tokens, M] -> dx [tokens, K] = dy @ W."""
+SP24_MIN_TOKENS = 1280  # from here on the transposed product of a 16-bit weight runs on the structured-sparse tensor cores
+
+
+@functools.lru_cache(maxsize=4096)
+def sp24_bytes(M, K, n, m, g, dtype):
+    """Size of the compressed transposed copy of a weight, 0 when the weight is outside the 2:4 structure."""
+    code = _DTYPES.get(dtype)
+    return 0 if code is None else nat.lib().nmg_sp24_bytes(M, K, n, m, g, code)
+
+
+def pack_sp24(val, idx, M, K, n, m, g):
+    """Compressed transposed copy of a 16-bit weight for the structured-sparse transposed product (opaque uint8 buffer)."""
+    dev = _require_cuda(val, idx)
+    code = _dtype_code(val)
+    nbytes = sp24_bytes(M, K, n, m, g, val.dtype)
+    if nbytes == 0:
+        raise ValueError("this weight is outside the 2:4 structure (needs a 16-bit dtype, n <= 2 and m in {4, 8, 16, 32, 64})")
+    val, idx = val.contiguous(), idx.contiguous()
+    buf = torch.empty(nbytes, dtype=torch.uint8, device=dev)
+    with torch.cuda.device(dev):
+        nat.check(nat.lib().nmg_pack_sp24(val.data_ptr(), idx.data_ptr(), M, K, n, m, g, code, buf.data_ptr(), nbytes, _stream(dev)))
+    return buf
+
+
+def spmm_t(val, idx, M, K, n, m, g, dy, algo=nat.NMG_ALGO_AUTO, packed=None, sp24=None):
+    """dy [tokens, M] -> dx [tokens, K] = dy @ W.  ``sp24``: result of pack_sp24 for the same weight; used (and the per-call
+    compression skipped) when the call would take the structured-sparse path anyway."""
     dev = _require_cuda(val, idx, dy)
     code = _dtype_code(val)
     if dy.dtype != val.dtype:
@@ -227,6 +252,11 @@ def spmm_t(val, idx, M, K, n, m, g, dy, algo=nat.NMG_ALGO_AUTO, packed=None):
         return dx
     val, idx = val.contiguous(), idx.contiguous()
     L = nat.lib()
+    if (sp24 is not None and tokens >= SP24_MIN_TOKENS and algo in (nat.NMG_ALGO_AUTO, nat.NMG_ALGO_TENSOR)
+            and dy.data_ptr() % 16 == 0 and ld_dy % 8 == 0):
+        with _on_device(dev):
+            nat.check(L.nmg_spmm_t_sp24(sp24.data_ptr(), M, K, n, m, g, code, dy.data_ptr(), ld_dy, tokens, dx.data_ptr(), K, _stream(dev)))
+        return dx
     with _on_device(dev):
         ws, nbytes = _workspace(L.nmg_spmm_t_workspace_bytes(M, K, tokens, n, m, g, code, algo,
                                                              1 if packed is not None else 0), dev)

@@ -54,6 +54,41 @@ def test_structured_sparse_transposed_product(dtype, n, m, g, M, K, tokens):
     assert ops.read_status() == 0
 
 
+def test_kept_compressed_copy_and_plugin_backward():
+    """nmg_pack_sp24 + nmg_spmm_t_sp24 (the copy kept across calls) give the bits of nmg_spmm_t (the copy built per call),
+    and the plugin's F.linear backward uses it: dX of a bf16 layer with 1536 tokens against float64."""
+    import sten_b200 as sten
+    from sten_b200 import _native as nat, ops
+    M, K, tokens, n, m, g = 384, 520, 1536, 2, 8, 16
+    w = seeded_normal((M, K), 31).bfloat16().to(cuda())
+    val, idx = ops.sparsify(w.unsqueeze(0), n, m, g)
+    dy = seeded_normal((tokens, M), 32).bfloat16().to(cuda())
+    sp24 = ops.pack_sp24(val, idx, M, K, n, m, g)
+    assert sp24.numel() == ops.sp24_bytes(M, K, n, m, g, torch.bfloat16) >= M * K
+    a = ops.spmm_t(val, idx, M, K, n, m, g, dy, sp24=sp24)
+    assert torch.equal(a, ops.spmm_t(val, idx, M, K, n, m, g, dy))
+    assert ops.sp24_bytes(M, K, n, m, g, torch.float32) == 0 and ops.sp24_bytes(60, 336, 3, 6, 4, torch.bfloat16) == 0
+    # few tokens: the kept copy is ignored, the fused kernel runs as before
+    few = ops.spmm_t(val, idx, M, K, n, m, g, dy[:200].contiguous(), sp24=sp24)
+    assert torch.equal(few, ops.spmm_t(val, idx, M, K, n, m, g, dy[:200].contiguous()))
+    # through the plugin
+    sten.set_dispatch_failure("raise")
+    lin = torch.nn.Linear(K, M, device=cuda(), dtype=torch.bfloat16)
+    lin.weight.data.copy_(w)
+    sb = sten.SparsityBuilder()
+    sb.set_weight("weight", initial_sparsifier=sten.GroupedNMSparsifier(n, m, g), out_format=sten.GroupedNMTensor)
+    sparse = sb.get_sparse_model(lin)
+    x = seeded_normal((tokens, K), 33).bfloat16().to(cuda()).requires_grad_(True)
+    sparse(x).backward(dy)
+    gnm = sparse.weight.wrapped_tensor
+    assert gnm.__dict__.get("_sp24_cache") is not None, "the backward pass did not take the structured-sparse path"
+    dense = gnm.to_dense().double()
+    assert _rel(x.grad, dy.double() @ dense) <= TOL_HALF
+    assert torch.equal(x.grad, a)
+    assert set(gnm.__getstate__()) == {"val", "idx", "nm_strides"}  # the cache is never pickled
+    assert ops.read_status() == 0
+
+
 def test_zeros_among_the_kept_values_and_exact_small_integers():
     """Weights of small integers: many exact zeros among the kept values (groups with fewer non-zeros than slots), and a
     product that is exact in bf16 x bf16 -> fp32, so the structured-sparse result must equal the float64 one bit for bit
