@@ -519,6 +519,13 @@ def _data_set(base_impl, func, types, lhs, rhs):
         make_sparse_catcher(torch.Tensor.data.__set__, handle_inplace_modifications=True)(lhs, rhs)
 
 
+@implements(torch._has_compatible_shallow_copy_type)
+def _compatible_shallow_copy(base_impl, func, types, a, b):
+    """nn.Module._apply asks this before ``param.data = fn(param)``: two sparse wrappers are interchangeable (the data
+    setter swaps the payload), a wrapper and a plain tensor are not.  Answered here without densifying either side."""
+    return isinstance(a, SparseTensorWrapper) and isinstance(b, SparseTensorWrapper)
+
+
 @implements(torch.Tensor.to)
 def _to(base_impl, func, types, *args, **kwargs):
     self = args[0]

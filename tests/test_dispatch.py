@@ -194,3 +194,35 @@ def test_patch_rebinds_function_in_scope():
     mod.K = type("K", (), {"g": staticmethod(old)})
     sten.patch(old, lambda: "new", [mod])
     assert mod.f() == "new" and mod.K.g() == "new"
+
+
+def test_module_to_moves_the_payload_without_densifying():
+    """nn.Module.to() on a module with a sparse parameter: the dtype / device questions PyTorch asks on the way
+    (is_floating_point, _has_compatible_shallow_copy_type) are answered from the wrapper, the payload's own .to() does
+    the move, and to_dense() is never called."""
+    import sten_b200 as sten
+    from sten_b200 import dispatch
+
+    class Payload:
+        def __init__(self, t):
+            self.t, self.densified = t, 0
+
+        def to_dense(self):
+            self.densified += 1
+            return self.t
+
+        def to(self, device=None, dtype=None, non_blocking=False, copy=False):
+            assert isinstance(non_blocking, bool) and isinstance(copy, bool)
+            return Payload(self.t.to(device=device, dtype=dtype))
+
+        dtype = property(lambda self: self.t.dtype)
+        device = property(lambda self: self.t.device)
+
+    sten.set_dispatch_failure("raise")
+    lin = torch.nn.Linear(4, 4)
+    first = Payload(torch.randn(4, 4))
+    lin.weight = dispatch.SparseParameterWrapper(dispatch.SparseTensorWrapper([first], True, dispatch._DEFAULT_GRAD_FMT()))
+    lin = lin.to(torch.float64)
+    assert isinstance(lin.weight, dispatch.SparseParameterWrapper)
+    assert lin.weight.dtype == torch.float64 and lin.weight.wrapped_tensor.t.dtype == torch.float64
+    assert first.densified == 0 and lin.weight.wrapped_tensor.densified == 0
