@@ -13,11 +13,17 @@ namespace nmg {
 // descending (ties: larger c, then larger p) and walk the list once, accepting a triple when its column is
 // still free and its pattern holds fewer than g columns.
 //
-// Equivalent selection used here (one warp per tile): every free column remembers its best pattern among
-// the patterns that still have room; each round the warp takes the maximum (score, c, p) over the free
-// columns with two warp reductions, appends c to pattern p, and only when p becomes full do the columns that
-// pointed at p re-evaluate.  The sequence of accepted triples is identical to the sorted walk, so val / idx
-// are identical bit for bit, without the C^2*g-element sort and without scratch memory in HBM.
+// That walk is a greedy matching of columns (capacity 1) to patterns (capacity g) by descending weight under a strict
+// total order of the pairs.  Such a matching is the unique stable one: the heaviest pair must be matched in any stable
+// matching (otherwise it blocks), remove it and repeat.  Deferred acceptance reaches the same matching in a few parallel
+// rounds instead of C*g sequential steps: every free column proposes to the best pattern it can still enter, every
+// pattern keeps its g best proposers (sorted by (score, c) descending) and releases the rest, released columns propose
+// again.  A pattern's final list in descending order is exactly the order in which the sequential walk accepted its
+// columns, so val / idx come out bit for bit identical -- without the C^2*g-element sort, without a sequential chain of
+// C*g dependent reductions, and without scratch memory in HBM.
+//
+// One warp per tile.  Lanes own columns (c = lane, lane + 32, ...) when columns propose, and patterns (p = lane,
+// lane + 32, ...) when patterns merge their proposers.  The tile is read with 16-byte loads where alignment allows.
 // =====================================================================================================
 
 struct SparsifyParams {
@@ -31,20 +37,70 @@ struct SparsifyParams {
     int slab_bytes;  // shared memory per warp
 };
 
-__device__ __forceinline__ void eval_column(const float *x, const int8_t *ord, const int16_t *cnt, int c, int cc, int n,
-                                            int g, int C, uint32_t &best_s, int &best_p) {
-    best_s = 0;
-    best_p = -1;
-    for (int p = 0; p < C; p++) {
-        if (cnt[p] >= g) continue;
-        float s = 0.f;
-        for (int i = 0; i < n; i++) s = __fadd_rn(s, fabsf(x[(int)ord[p * n + i] * cc + c]));
-        uint32_t b = __float_as_uint(s);
-        if (best_p < 0 || b >= best_s) {  // ties go to the larger pattern index
-            best_s = b;
-            best_p = p;
-        }
+// A proposal / list entry: fp32 score bits (non-negative, so unsigned order = float order) above the column index.
+// Comparing entries of one pattern as integers is the format's order (score, then larger column first).
+__device__ __forceinline__ uint64_t sp_key(uint32_t score_bits, int c) { return ((uint64_t)score_bits << 16) | (uint32_t)c; }
+
+// Shared memory of one warp (host and device agree through this function).
+struct SparsifySlab { size_t list, inbox, x, park, state, prop_p, prop_i, cnt, total; };
+__host__ __device__ inline SparsifySlab sparsify_slab(int m, int cc, int C, size_t es) {
+    SparsifySlab l;
+    size_t o = 0;
+    l.list = o;   o += (size_t)cc * 8;                                   // [C][g] kept proposers of every pattern, descending
+    l.inbox = o;  o += (size_t)cc * 8;                                   // [cc] this round's proposals, grouped by pattern
+    l.x = o;      o += (((size_t)m * cc * es) + 15) & ~(size_t)15;       // [m][cc] the tile
+    l.park = o;   o += (size_t)cc * 4;                                   // [cc] score of the column's proposal
+    l.state = o;  o += (size_t)cc * 2;                                   // [cc] pattern the column is held by, -1 = free
+    l.prop_p = o; o += (size_t)cc * 2;                                   // [cc] pattern proposed to this round
+    l.prop_i = o; o += (size_t)cc * 2;                                   // [cc] position inside that pattern's inbox segment
+    o = (o + 3) & ~(size_t)3;
+    l.cnt = o;    o += (size_t)C * 4 * 3;                                // [C] list lengths, proposals this round, segment starts
+    l.total = (o + 15) & ~(size_t)15;
+    return l;
+}
+
+
+// Zero phase of the selection.  Triples whose score is 0 come last in the format's order, sorted by larger column, then
+// larger pattern; when the walk reaches them every pattern in which a still-free column scores above zero is full.  So
+// the free columns, taken from the largest index down, each fill the largest pattern that has room left: a closed form,
+// no rounds.  (Zero-padded columns of a last chunk and all-zero columns of a pruned weight end up here; letting them
+// run through the rounds would cost one round per pattern with hundreds of tied proposals each.)
+// On entry cnt[p] holds the list lengths; rem / cum are scratch of C ints each.  All lanes of the warp call this.
+__device__ __forceinline__ void sparsify_zero_phase(int lane, int cc, int C, int g, uint64_t *list, int16_t *state, int *cnt, int *rem, int *cum) {
+    // cum[p] = free places in patterns with a larger index (suffix sum), rem[p] = free places of p
+    const int pchunk = (C + 31) / 32;
+    const int p0 = lane * pchunk, p1 = min(C, p0 + pchunk);
+    int local = 0;
+    for (int p = p0; p < p1; p++) { rem[p] = g - cnt[p]; local += g - cnt[p]; }
+    int incl = local;  // inclusive suffix sum over lanes
+    for (int d = 1; d < 32; d <<= 1) {
+        const int t = __shfl_down_sync(0xffffffffu, incl, d);
+        if (lane + d < 32) incl += t;
     }
+    int run = incl - local;  // free places in the chunks of higher lanes
+    for (int p = p1 - 1; p >= p0; p--) { cum[p] = run; run += g - cnt[p]; }
+    __syncwarp();
+    int above = 0;  // free columns in higher rows of the column-to-lane layout (larger indices), warp-uniform
+    for (int k = (cc - 1) / 32; k >= 0; k--) {
+        const int c = k * 32 + lane;
+        const bool is_free = c < cc && state[c] < 0;
+        const uint32_t mask = __ballot_sync(0xffffffffu, is_free);
+        if (is_free) {
+            const int i = above + __popc(lane == 31 ? 0u : (mask >> (lane + 1)));  // free columns with a larger index
+            int lo = 0, hi = C - 1;  // largest p with cum[p] <= i (cum decreases with p, cum[C - 1] = 0)
+            while (lo < hi) {
+                const int mid = (lo + hi) >> 1;
+                if (cum[mid] <= i) hi = mid; else lo = mid + 1;
+            }
+            // patterns without room share their cum with the next smaller pattern that has some: step down to it
+            int p = lo;
+            while (p > 0 && i - cum[p] >= rem[p]) p--;
+            list[p * g + cnt[p] + (i - cum[p])] = (uint64_t)(uint32_t)c;  // score 0
+            state[c] = (int16_t)p;
+        }
+        above += __popc(mask);
+    }
+    __syncwarp();
 }
 
 template <typename T>
@@ -52,6 +108,7 @@ __global__ void __launch_bounds__(256) sparsify_kernel(SparsifyParams prm) {
     extern __shared__ __align__(16) char smem[];
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
     const int n = prm.n, m = prm.m, g = prm.g, C = prm.C, cc = prm.cc;
+    constexpr int V = 16 / (int)sizeof(T);  // elements per 16-byte access
 
     // CTA-wide copy of the pattern table, then one slab per warp.
     int8_t *ord = reinterpret_cast<int8_t *>(smem);
@@ -60,80 +117,311 @@ __global__ void __launch_bounds__(256) sparsify_kernel(SparsifyParams prm) {
     __syncthreads();
 
     char *slab = smem + ord_bytes + (size_t)warp * prm.slab_bytes;
-    float *x = reinterpret_cast<float *>(slab);                         // [m][cc]
-    uint32_t *col_score = reinterpret_cast<uint32_t *>(x + (size_t)m * cc);  // [cc]
-    int16_t *col_pat = reinterpret_cast<int16_t *>(col_score + cc);      // [cc], -1 = column taken
-    int16_t *out_idx = col_pat + cc;                                     // [cc]
-    int16_t *cnt = out_idx + cc;                                         // [C]
+    const SparsifySlab lay = sparsify_slab(m, cc, C, sizeof(T));
+    uint64_t *list = reinterpret_cast<uint64_t *>(slab + lay.list);
+    uint64_t *inbox = reinterpret_cast<uint64_t *>(slab + lay.inbox);
+    T *x = reinterpret_cast<T *>(slab + lay.x);
+    uint32_t *park = reinterpret_cast<uint32_t *>(slab + lay.park);
+    int16_t *state = reinterpret_cast<int16_t *>(slab + lay.state);
+    int16_t *prop_p = reinterpret_cast<int16_t *>(slab + lay.prop_p);
+    int16_t *prop_i = reinterpret_cast<int16_t *>(slab + lay.prop_i);
+    int *cnt = reinterpret_cast<int *>(slab + lay.cnt);
+    int *icnt = cnt + C;
+    int *ioff = icnt + C;
 
     const T *dense = static_cast<const T *>(prm.dense);
     T *val = static_cast<T *>(prm.val);
+    const int pchunk = (C + 31) / 32;  // patterns per lane in the prefix sum
 
     for (int64_t tile = (int64_t)blockIdx.x * nwarps + warp; tile < prm.tiles; tile += (int64_t)gridDim.x * nwarps) {
         const int64_t mb = tile % prm.nb, kc = (tile / prm.nb) % prm.nc, b = tile / (prm.nb * prm.nc);
         const int64_t row0 = mb * m, col0 = kc * cc;
         const T *src = dense + b * prm.batch_stride;
+        // ---- load the tile (rows beyond M and columns beyond K read as zero)
+        const bool full_cols = col0 + cc <= prm.K;
         for (int r = 0; r < m; r++) {
             const bool row_ok = row0 + r < prm.M;
             const T *srow = src + (row0 + r) * prm.ld + col0;
-            for (int c = lane; c < cc; c += 32)
-                x[r * cc + c] = (row_ok && col0 + c < prm.K) ? DT<T>::to_f32(srow[c]) : 0.f;
+            T *xr = x + r * cc;
+            if (row_ok && full_cols && (cc % V) == 0 && (reinterpret_cast<uintptr_t>(srow) & 15) == 0) {
+                for (int c = lane * V; c < cc; c += 32 * V)
+                    *reinterpret_cast<uint4 *>(xr + c) = __ldg(reinterpret_cast<const uint4 *>(srow + c));
+            } else {
+                for (int c = lane; c < cc; c += 32) xr[c] = (row_ok && col0 + c < prm.K) ? srow[c] : DT<T>::from_f32(0.f);
+            }
         }
+        for (int c = lane; c < cc; c += 32) state[c] = -1;
         for (int p = lane; p < C; p += 32) cnt[p] = 0;
         __syncwarp();
 
-        uint32_t my_s = 0, my_cp = 0;  // best free column of this lane; my_cp = ((c << 16) | p) + 1, 0 = none
-        for (int c = lane; c < cc; c += 32) {
-            uint32_t s; int p;
-            eval_column(x, ord, cnt, c, cc, n, g, C, s, p);
-            col_score[c] = s;
-            col_pat[c] = (int16_t)p;
-            uint32_t cp = (((uint32_t)c << 16) | (uint32_t)p) + 1;
-            if (s > my_s || (s == my_s && cp > my_cp)) { my_s = s; my_cp = cp; }
-        }
-        __syncwarp();
-
-        for (int round = 0; round < cc; round++) {
-            const uint32_t top_s = __reduce_max_sync(0xffffffffu, my_cp ? my_s : 0u);
-            const uint32_t top_cp = __reduce_max_sync(0xffffffffu, (my_cp && my_s == top_s) ? my_cp : 0u);
-            if (top_cp == 0) break;  // cannot happen for a well-formed tile; keeps the loop bounded anyway
-            const int c = (int)((top_cp - 1) >> 16), p = (int)((top_cp - 1) & 0xffffu);
-            const int j = cnt[p];
-            const bool owner = (c & 31) == lane;
+        // ---- deferred acceptance.  Every round with a free column makes at least one proposal (column, pattern) that was
+        // never made before, so cc * C rounds cannot be exceeded; real weights settle in a handful.
+        for (int round = 0; round < cc * C + 2; round++) {
+            for (int p = lane; p < C; p += 32) icnt[p] = 0;
             __syncwarp();
-            if (lane == 0) { out_idx[p * g + j] = (int16_t)c; cnt[p] = (int16_t)(j + 1); }
-            if (owner) col_pat[c] = -1;
-            __syncwarp();
-            const bool filled = (j + 1 == g);
-            if (filled) {
-                for (int c2 = lane; c2 < cc; c2 += 32)
-                    if (col_pat[c2] == p) {
-                        uint32_t s; int p2;
-                        eval_column(x, ord, cnt, c2, cc, n, g, C, s, p2);
-                        col_score[c2] = s;
-                        col_pat[c2] = (int16_t)p2;
-                    }
-            }
-            if (filled || owner) {
-                my_s = 0; my_cp = 0;
-                for (int c2 = lane; c2 < cc; c2 += 32) {
-                    const int p2 = col_pat[c2];
-                    if (p2 < 0) continue;
-                    const uint32_t s = col_score[c2];
-                    const uint32_t cp = (((uint32_t)c2 << 16) | (uint32_t)p2) + 1;
-                    if (my_cp == 0 || s > my_s || (s == my_s && cp > my_cp)) { my_s = s; my_cp = cp; }
+            // columns propose: the best pattern (larger p on equal score) among those the column can still enter
+            bool proposed = false;
+            for (int c = lane; c < cc; c += 32) {
+                prop_p[c] = -1;
+                if (state[c] >= 0) continue;
+                uint32_t best_s = 0;
+                int best_p = -1;
+                for (int p = 0; p < C; p++) {
+                    float s = 0.f;
+                    for (int i = 0; i < n; i++) s = __fadd_rn(s, fabsf(DT<T>::to_f32(x[(int)ord[p * n + i] * cc + c])));
+                    const uint32_t sb = __float_as_uint(s);
+                    if (sb == 0) continue;  // zero scores are placed by the closed form after the rounds
+                    if (cnt[p] >= g && sp_key(sb, c) <= list[p * g + g - 1]) continue;  // full, and every kept proposer ranks higher
+                    if (best_p < 0 || sb >= best_s) { best_s = sb; best_p = p; }
                 }
+                if (best_p < 0) continue;  // nothing above zero is open to this column: it waits for the zero phase
+                proposed = true;
+                prop_p[c] = (int16_t)best_p;
+                prop_i[c] = (int16_t)atomicAdd(&icnt[best_p], 1);
+                park[c] = best_s;
             }
+            if (!__any_sync(0xffffffffu, proposed)) break;
+            __syncwarp();
+            // exclusive prefix sum of the proposal counts -> start of every pattern's inbox segment
+            {
+                const int p0 = lane * pchunk, p1 = min(C, p0 + pchunk);
+                int local = 0;
+                for (int p = p0; p < p1; p++) local += icnt[p];
+                int incl = local;
+                for (int d = 1; d < 32; d <<= 1) {
+                    const int t = __shfl_up_sync(0xffffffffu, incl, d);
+                    if (lane >= d) incl += t;
+                }
+                int run = incl - local;
+                for (int p = p0; p < p1; p++) { ioff[p] = run; run += icnt[p]; }
+            }
+            __syncwarp();
+            for (int c = lane; c < cc; c += 32)
+                if (prop_p[c] >= 0) inbox[ioff[prop_p[c]] + prop_i[c]] = sp_key(park[c], c);
+            __syncwarp();
+            // patterns merge their proposers into their sorted lists; what does not fit is released
+            for (int p = lane; p < C; p += 32) {
+                uint64_t *lp = list + p * g;
+                int L = cnt[p];
+                const int e0 = ioff[p], e1 = e0 + icnt[p];
+                for (int e = e0; e < e1; e++) {
+                    const uint64_t key = inbox[e];
+                    if (L == g) {
+                        if (key <= lp[g - 1]) continue;            // stays free (state is still -1)
+                        state[(int)(lp[g - 1] & 0xffffu)] = -1;     // the weakest kept proposer is released
+                        L = g - 1;
+                    }
+                    int j = L;
+                    while (j > 0 && lp[j - 1] < key) { lp[j] = lp[j - 1]; j--; }
+                    lp[j] = key;
+                    L++;
+                    state[(int)(key & 0xffffu)] = (int16_t)p;
+                }
+                cnt[p] = L;
+            }
+            __syncwarp();
         }
         __syncwarp();
+        sparsify_zero_phase(lane, cc, C, g, list, state, cnt, icnt, ioff);
 
+        // ---- write the tile: idx = the lists' columns, val = the kept rows of those columns
         int16_t *idx_out = prm.idx + tile * cc;
         T *val_out = val + tile * (int64_t)cc * n;
-        for (int s = lane; s < cc; s += 32) idx_out[s] = out_idx[s];
+        for (int s0 = lane; s0 < cc; s0 += 32) idx_out[s0] = (int16_t)(list[s0] & 0xffffu);
         for (int e = lane; e < cc * n; e += 32) {
-            const int s = e / n, t = e - s * n;
-            const int c = out_idx[s], p = s / g;
-            val_out[e] = DT<T>::from_f32(x[(int)ord[p * n + t] * cc + c]);
+            const int s0 = e / n, t = e - s0 * n;
+            const int c = (int)(list[s0] & 0xffffu), p = s0 / g;
+            val_out[e] = x[(int)ord[p * n + t] * cc + c];
+        }
+        __syncwarp();
+    }
+}
+
+// Specialisation on (n, m): the pattern table is a compile-time constant, so a column's |w| values sit in registers and
+// all C scores are straight-line adds; which patterns are full is one bit mask (C <= 32), so the first round -- where
+// nothing is full -- touches no shared state at all.  The first round's proposals are placed by rank (every proposal
+// counts the larger proposals of its own pattern, all lanes busy) instead of by one lane per pattern inserting in turn.
+template <int N_, int M_, typename T>
+__global__ void __launch_bounds__(256) sparsify_nm_kernel(SparsifyParams prm) {
+    extern __shared__ __align__(16) char smem[];
+    constexpr Order<N_, M_> ORD{};
+    constexpr int C = Order<N_, M_>::C;
+    static_assert(C <= 32, "the full-pattern mask is one word");
+    constexpr int V = 16 / (int)sizeof(T);
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
+    const int g = prm.g, cc = prm.cc;
+
+    int8_t *ord = reinterpret_cast<int8_t *>(smem);  // run-time copy of the table for the output stage
+    constexpr int ord_bytes = (C * N_ + 15) & ~15;
+    for (int i = threadIdx.x; i < C * N_; i += blockDim.x) ord[i] = (int8_t)ORD.v[(i / N_) * Order<N_, M_>::LD + (i % N_)];
+    __syncthreads();
+
+    char *slab = smem + ord_bytes + (size_t)warp * prm.slab_bytes;
+    const SparsifySlab lay = sparsify_slab(M_, cc, C, sizeof(T));
+    uint64_t *list = reinterpret_cast<uint64_t *>(slab + lay.list);
+    uint64_t *inbox = reinterpret_cast<uint64_t *>(slab + lay.inbox);
+    T *x = reinterpret_cast<T *>(slab + lay.x);
+    uint32_t *park = reinterpret_cast<uint32_t *>(slab + lay.park);
+    int16_t *state = reinterpret_cast<int16_t *>(slab + lay.state);
+    int16_t *prop_p = reinterpret_cast<int16_t *>(slab + lay.prop_p);
+    int16_t *prop_i = reinterpret_cast<int16_t *>(slab + lay.prop_i);
+    int *cnt = reinterpret_cast<int *>(slab + lay.cnt);
+    int *icnt = cnt + C;
+    int *ioff = icnt + C;
+
+    const T *dense = static_cast<const T *>(prm.dense);
+    T *val = static_cast<T *>(prm.val);
+    const bool g_pow2 = (g & (g - 1)) == 0;
+    const int g_shift = 31 - __clz(g);
+
+    for (int64_t tile = (int64_t)blockIdx.x * nwarps + warp; tile < prm.tiles; tile += (int64_t)gridDim.x * nwarps) {
+        const int64_t mb = tile % prm.nb, kc = (tile / prm.nb) % prm.nc, b = tile / (prm.nb * prm.nc);
+        const int64_t row0 = mb * M_, col0 = kc * cc;
+        const T *src = dense + b * prm.batch_stride;
+        const bool full_cols = col0 + cc <= prm.K;
+#pragma unroll
+        for (int r = 0; r < M_; r++) {
+            const bool row_ok = row0 + r < prm.M;
+            const T *srow = src + (row0 + r) * prm.ld + col0;
+            T *xr = x + r * cc;
+            if (row_ok && full_cols && (cc % V) == 0 && (reinterpret_cast<uintptr_t>(srow) & 15) == 0) {
+                for (int c = lane * V; c < cc; c += 32 * V)
+                    *reinterpret_cast<uint4 *>(xr + c) = __ldg(reinterpret_cast<const uint4 *>(srow + c));
+            } else {
+                for (int c = lane; c < cc; c += 32) xr[c] = (row_ok && col0 + c < prm.K) ? srow[c] : DT<T>::from_f32(0.f);
+            }
+        }
+        for (int c = lane; c < cc; c += 32) state[c] = -1;
+        if (lane < C) cnt[lane] = 0;
+        uint32_t full_mask = 0;  // bit p: pattern p holds g columns (warp-uniform)
+        __syncwarp();
+
+        for (int round = 0; round < cc * C + 2; round++) {
+            if (lane < C) icnt[lane] = 0;
+            __syncwarp();
+            bool proposed = false;
+            for (int c = lane; c < cc; c += 32) {
+                prop_p[c] = -1;
+                if (state[c] >= 0) continue;
+                float a[M_];
+#pragma unroll
+                for (int r = 0; r < M_; r++) a[r] = fabsf(DT<T>::to_f32(x[r * cc + c]));
+                uint32_t best_s = 0;  // a score of zero never wins: zero scores are placed by the closed form after the rounds
+                int best_p = -1;
+                if (full_mask == 0) {  // first round(s): every pattern is open, nothing but registers
+#pragma unroll
+                    for (int p = 0; p < C; p++) {
+                        float sc = 0.f;
+#pragma unroll
+                        for (int i = 0; i < N_; i++) sc = __fadd_rn(sc, a[ORD.row(p, i)]);
+                        const uint32_t sb = __float_as_uint(sc);
+                        if (sb != 0 && sb >= best_s) { best_s = sb; best_p = p; }
+                    }
+                } else {
+#pragma unroll
+                    for (int p = 0; p < C; p++) {
+                        float sc = 0.f;
+#pragma unroll
+                        for (int i = 0; i < N_; i++) sc = __fadd_rn(sc, a[ORD.row(p, i)]);
+                        const uint32_t sb = __float_as_uint(sc);
+                        bool open = sb != 0 && sb >= best_s;
+                        // full pattern: only a proposer that ranks above its weakest kept one gets in
+                        if (open && ((full_mask >> p) & 1u)) open = sp_key(sb, c) > list[p * g + g - 1];
+                        if (open) { best_s = sb; best_p = p; }
+                    }
+                }
+                if (best_p < 0) continue;  // nothing above zero is open to this column: it waits for the zero phase
+                proposed = true;
+                prop_p[c] = (int16_t)best_p;
+                prop_i[c] = (int16_t)atomicAdd(&icnt[best_p], 1);
+                park[c] = best_s;
+            }
+            if (!__any_sync(0xffffffffu, proposed)) break;
+            __syncwarp();
+            {   // exclusive prefix sum over the patterns (one per lane)
+                const int mine = lane < C ? icnt[lane] : 0;
+                int incl = mine;
+#pragma unroll
+                for (int d = 1; d < 32; d <<= 1) {
+                    const int t = __shfl_up_sync(0xffffffffu, incl, d);
+                    if (lane >= d) incl += t;
+                }
+                if (lane < C) ioff[lane] = incl - mine;
+            }
+            __syncwarp();
+            int total = 0;  // proposals of this round (warp-uniform)
+            for (int c = lane; c < cc; c += 32)
+                if (prop_p[c] >= 0) { inbox[ioff[prop_p[c]] + prop_i[c]] = sp_key(park[c], c); total++; }
+#pragma unroll
+            for (int d = 16; d > 0; d >>= 1) total += __shfl_xor_sync(0xffffffffu, total, d);
+            __syncwarp();
+            if (round == 0) {
+                // all lists are empty: a proposal's place is its rank among the proposals of its pattern
+                for (int e = lane; e < total; e += 32) {
+                    const uint64_t key = inbox[e];
+                    const int c = (int)(key & 0xffffu), p = prop_p[c];
+                    const int e0 = ioff[p], e1 = e0 + icnt[p];
+                    int rank = 0;
+                    for (int j = e0; j < e1; j++) rank += inbox[j] > key ? 1 : 0;
+                    if (rank < g) { list[p * g + rank] = key; state[c] = (int16_t)p; }
+                }
+                if (lane < C) cnt[lane] = min(icnt[lane], g);
+            } else if (lane < C) {
+                const int p = lane;
+                uint64_t *lp = list + p * g;
+                int L = cnt[p];
+                const int e0 = ioff[p], e1 = e0 + icnt[p];
+                for (int e = e0; e < e1; e++) {
+                    const uint64_t key = inbox[e];
+                    if (L == g) {
+                        if (key <= lp[g - 1]) continue;
+                        state[(int)(lp[g - 1] & 0xffffu)] = -1;
+                        L = g - 1;
+                    }
+                    int j = L;
+                    while (j > 0 && lp[j - 1] < key) { lp[j] = lp[j - 1]; j--; }
+                    lp[j] = key;
+                    L++;
+                    state[(int)(key & 0xffffu)] = (int16_t)p;
+                }
+                cnt[p] = L;
+            }
+            __syncwarp();
+            full_mask = __ballot_sync(0xffffffffu, lane < C && cnt[lane] == g);
+        }
+        __syncwarp();
+        sparsify_zero_phase(lane, cc, C, g, list, state, cnt, icnt, ioff);
+
+        int16_t *idx_out = prm.idx + tile * cc;
+        T *val_out = val + tile * (int64_t)cc * N_;
+        if ((cc & 7) == 0 && (reinterpret_cast<uintptr_t>(idx_out) & 15) == 0) {
+            for (int s0 = lane * 8; s0 < cc; s0 += 256) {
+                uint32_t w[4];
+#pragma unroll
+                for (int u = 0; u < 4; u++) w[u] = (uint32_t)(list[s0 + 2 * u] & 0xffffu) | ((uint32_t)(list[s0 + 2 * u + 1] & 0xffffu) << 16);
+                *reinterpret_cast<uint4 *>(idx_out + s0) = make_uint4(w[0], w[1], w[2], w[3]);
+            }
+        } else {
+            for (int s0 = lane; s0 < cc; s0 += 32) idx_out[s0] = (int16_t)(list[s0] & 0xffffu);
+        }
+        const int nvals = cc * N_;
+        if ((nvals % V) == 0 && (reinterpret_cast<uintptr_t>(val_out) & 15) == 0) {
+            for (int v = lane * V; v < nvals; v += 32 * V) {
+                __align__(16) T out[V];
+#pragma unroll
+                for (int u = 0; u < V; u++) {
+                    const int e = v + u, s0 = e / N_, t = e % N_;
+                    const int c = (int)(list[s0] & 0xffffu), p = g_pow2 ? (s0 >> g_shift) : s0 / g;
+                    out[u] = x[(int)ord[p * N_ + t] * cc + c];
+                }
+                *reinterpret_cast<uint4 *>(val_out + v) = *reinterpret_cast<const uint4 *>(out);
+            }
+        } else {
+            for (int e = lane; e < nvals; e += 32) {
+                const int s0 = e / N_, t = e % N_;
+                const int c = (int)(list[s0] & 0xffffu), p = s0 / g;
+                val_out[e] = x[(int)ord[p * N_ + t] * cc + c];
+            }
         }
         __syncwarp();
     }
@@ -232,27 +520,50 @@ extern "C" int nmg_sparsify(const void *dense, int64_t batch, int64_t M, int64_t
     p.M = M; p.K = K; p.ld = ld_dense; p.batch_stride = batch_stride;
     p.nb = geo.nb; p.nc = geo.nc; p.tiles = batch * geo.nb * geo.nc;
     p.n = n; p.m = m; p.g = g; p.C = geo.C; p.cc = geo.cc;
-    size_t slab = (size_t)m * geo.cc * 4 + (size_t)geo.cc * 4 + (size_t)geo.cc * 2 * 2 + (size_t)geo.C * 2;
-    slab = (slab + 15) & ~(size_t)15;
+    const size_t slab = sparsify_slab(m, geo.cc, geo.C, dtype_size(dtype)).total;
     const size_t ord_bytes = ((size_t)geo.C * n + 15) & ~(size_t)15;
     const size_t budget = 200 * 1024;
     if (ord_bytes + slab > budget)
         NMG_FAIL(NMG_ERR_UNSUPPORTED, "tile of m=%d x %d columns needs %zu bytes of shared memory (limit %zu)", m, geo.cc,
                  ord_bytes + slab, budget);
-    int warps = (int)((budget - ord_bytes) / slab);
-    if (warps > 8) warps = 8;
-    // keep several CTAs per SM resident when the slab is small
-    while (warps > 2 && (ord_bytes + warps * slab) > 56 * 1024) warps--;
+    // warps per CTA: whatever keeps the most warps resident per SM (227 KB of shared memory, at most 8 warps per CTA); on a
+    // tie the smaller CTA, for a finer tail
+    int warps = 1, best_resident = 0;
+    for (int w = 1; w <= 8; w++) {
+        const size_t per_cta = ord_bytes + (size_t)w * slab + 1024;  // + the per-CTA reservation of the driver
+        if (per_cta > 227 * 1024) break;
+        int per_sm = (int)((size_t)227 * 1024 / per_cta);
+        if (per_sm > 32) per_sm = 32;
+        if (per_sm * w > 64) per_sm = 64 / w;
+        if (per_sm * w > best_resident) { best_resident = per_sm * w; warps = w; }
+    }
     p.slab_bytes = (int)slab;
     const size_t smem = ord_bytes + warps * slab;
     int64_t ctas = (p.tiles + warps - 1) / warps;
     const int64_t max_ctas = (int64_t)sm_count() * 16;
     if (ctas > max_ctas) ctas = max_ctas;
     cudaStream_t st = (cudaStream_t)stream;
-    NMG_DISPATCH_DTYPE(dtype, T, {
-        NMG_CUDA(cudaFuncSetAttribute(sparsify_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-        sparsify_kernel<T><<<(unsigned)ctas, warps * 32, smem, st>>>(p);
-    });
+    bool launched = false;
+#define NMG_SPARSIFY_CASE(N_, M_)                                                                                     \
+    if (!launched && n == N_ && m == M_) {                                                                            \
+        NMG_DISPATCH_DTYPE(dtype, T, {                                                                                \
+            NMG_CUDA(cudaFuncSetAttribute(sparsify_nm_kernel<N_, M_, T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)); \
+            sparsify_nm_kernel<N_, M_, T><<<(unsigned)ctas, warps * 32, smem, st>>>(p);                               \
+        });                                                                                                           \
+        launched = true;                                                                                              \
+    }
+    NMG_SPARSIFY_CASE(1, 4)
+    NMG_SPARSIFY_CASE(2, 4)
+    NMG_SPARSIFY_CASE(1, 8)
+    NMG_SPARSIFY_CASE(2, 8)
+    NMG_SPARSIFY_CASE(1, 16)
+#undef NMG_SPARSIFY_CASE
+    if (!launched) {
+        NMG_DISPATCH_DTYPE(dtype, T, {
+            NMG_CUDA(cudaFuncSetAttribute(sparsify_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+            sparsify_kernel<T><<<(unsigned)ctas, warps * 32, smem, st>>>(p);
+        });
+    }
     NMG_CUDA(cudaGetLastError());
     return NMG_OK;
 }
