@@ -77,6 +77,26 @@ int nmg_sparsify(const void *dense, int64_t batch, int64_t M, int64_t K, int64_t
 int nmg_densify(const void *val, const int16_t *idx, int64_t batch, int64_t M, int64_t K, int n, int m,
                 int g, int dtype, void *dense, int64_t ld_dense, int64_t batch_stride, void *stream);
 
+/* Values of a dense tensor at the positions an EXISTING layout keeps: val[t][p][j][s] = dense[row of slot s of pattern p in
+ * tile t][column idx[t][p][j]] (zero outside the tensor).  Replaces GroupedNMTensor.clone_layout
+ * (src/sten/grouped_nm/grouped_nm_tensor.py:904-951, disabled there): it is how a gradient or an updated weight takes the
+ * layout of the weight it belongs to without a new magnitude selection.  Operand conventions as nmg_sparsify; idx is read,
+ * val (same shape and dtype as the layout's val) is written. */
+int nmg_gather(const void *dense, const int16_t *idx, int64_t batch, int64_t M, int64_t K, int64_t ld_dense,
+               int64_t batch_stride, int n, int m, int g, int dtype, void *val, void *stream);
+
+/* Per-block top-n by magnitude without the group constraint.  Replaces PerfectNMTensor.from_dense / to_dense
+ * (src/sten/grouped_nm/grouped_nm_tensor.py:1010-1066: pad, reshape, abs().argsort(descending), gather / scatter_), the
+ * upper bound the reference's conversion test compares the grouped layout against (tests/test_nmg.py:73-83).
+ * The tensor is [outer][size][inner], contiguous; blocks of m run along `size` (zero-padded to a multiple of m).
+ *   val, idx: [outer][ceil(size / m)][n][inner]; idx is int64 (what argsort returns), positions inside the block, ordered
+ *   by descending magnitude; equal magnitudes keep the smaller position first (argsort leaves that order open).
+ * nmg_perfect_nm_densify writes every element of dense (zeros included). */
+int nmg_perfect_nm_select(const void *dense, int64_t outer, int64_t size, int64_t inner, int n, int m, int dtype, void *val,
+                          int64_t *idx, void *stream);
+int nmg_perfect_nm_densify(const void *val, const int64_t *idx, int64_t outer, int64_t size, int64_t inner, int n, int m,
+                           int dtype, void *dense, void *stream);
+
 /* Column-ordered device copy of a weight ("packed" form), the second half of the format conversion: for every
  * row-block and column it holds the column's pattern id and its n kept values, i.e. val / idx re-ordered from
  * pattern-sorted to natural column order.  The tensor-core matmul and the transposed matmul read it; building it

@@ -11,7 +11,7 @@ from .dispatch import (  # noqa: F401  (names with a leading capital are covered
     register_sparsifier_implementation, set_dispatch_failure, sparsified_op, unregister_sparsifier_implementation,
 )
 from .grouped_nm_tensor import GroupedNMTensor, PerfectNMTensor
-from .nmg_impls import GroupedNMSparsifier
-from .patches import patch
+from .nmg_impls import GroupedNMSparsifier, WeightLayoutSparsifier
+from .patches import patch, patch_ddp, sparse_ddp_all_reduce_hook
 
 __version__ = "0.1.0"

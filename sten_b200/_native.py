@@ -23,6 +23,9 @@ SIGNATURES = {
     "nmg_pattern_order": (_int, [_int, _int, _vp]),
     "nmg_sparsify": (_int, [_vp, _i64, _i64, _i64, _i64, _i64, _int, _int, _int, _int, _vp, _vp, _vp]),
     "nmg_densify": (_int, [_vp, _vp, _i64, _i64, _i64, _int, _int, _int, _int, _vp, _i64, _i64, _vp]),
+    "nmg_gather": (_int, [_vp, _vp, _i64, _i64, _i64, _i64, _i64, _int, _int, _int, _int, _vp, _vp]),
+    "nmg_perfect_nm_select": (_int, [_vp, _i64, _i64, _i64, _int, _int, _int, _vp, _vp, _vp]),
+    "nmg_perfect_nm_densify": (_int, [_vp, _vp, _i64, _i64, _i64, _int, _int, _int, _vp, _vp]),
     "nmg_packed_bytes": (_sz, [_i64, _i64, _int, _int, _int, _int]),
     "nmg_pack": (_int, [_vp, _vp, _i64, _i64, _int, _int, _int, _int, _vp, _sz, _vp]),
     "nmg_spmm_workspace_bytes": (_sz, [_i64, _i64, _i64, _int, _int, _int, _int, _int, _int, _int]),

@@ -485,6 +485,44 @@ __global__ void __launch_bounds__(128) densify_kernel(DensifyParams prm) {
     }
 }
 
+// =====================================================================================================
+// Layout gather: the values of a dense tensor at the positions an existing (idx) layout keeps.  One warp per tile; the
+// tile's rows are short contiguous spans, so the indexed reads hit L1 / L2.
+// =====================================================================================================
+struct GatherParams {
+    const void *dense;
+    const int16_t *idx;
+    void *val;
+    const int8_t *order;  // [C][n] device
+    int64_t M, K, ld, batch_stride;
+    int64_t nb, nc, tiles;
+    int n, m, g, C, cc;
+};
+
+template <typename T>
+__global__ void __launch_bounds__(256) gather_layout_kernel(GatherParams prm) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
+    const int n = prm.n, m = prm.m, g = prm.g, cc = prm.cc;
+    const T *dense = static_cast<const T *>(prm.dense);
+    T *val = static_cast<T *>(prm.val);
+    for (int64_t tile = (int64_t)blockIdx.x * nwarps + warp; tile < prm.tiles; tile += (int64_t)gridDim.x * nwarps) {
+        const int64_t mb = tile % prm.nb, kc = (tile / prm.nb) % prm.nc, b = tile / (prm.nb * prm.nc);
+        const T *src = dense + b * prm.batch_stride;
+        const int16_t *isrc = prm.idx + tile * cc;
+        T *vdst = val + tile * (int64_t)cc * n;
+        for (int s = lane; s < cc; s += 32) {
+            const int c = isrc[s];
+            const int8_t *o = prm.order + (s / g) * n;
+            const int64_t col = kc * cc + c;
+            const bool col_ok = c >= 0 && c < cc && col < prm.K;  // a malformed index reads as zero, never dereferenced
+            for (int t = 0; t < n; t++) {
+                const int64_t row = mb * m + o[t];
+                vdst[s * n + t] = (col_ok && row < prm.M) ? src[row * prm.ld + col] : DT<T>::from_f32(0.f);
+            }
+        }
+    }
+}
+
 static int sm_count() {
     int dev = 0, sms = 148;
     if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
@@ -597,6 +635,32 @@ extern "C" int nmg_densify(const void *val, const int16_t *idx, int64_t batch, i
         NMG_CUDA(cudaFuncSetAttribute(densify_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
         densify_kernel<T><<<(unsigned)ctas, 128, smem, st>>>(p);
     });
+    NMG_CUDA(cudaGetLastError());
+    return NMG_OK;
+}
+
+extern "C" int nmg_gather(const void *dense, const int16_t *idx, int64_t batch, int64_t M, int64_t K, int64_t ld_dense,
+                          int64_t batch_stride, int n, int m, int g, int dtype, void *val, void *stream) {
+    Geo geo;
+    int rc = make_geo(M, K, n, m, g, &geo);
+    if (rc) return rc;
+    if ((rc = check_dtype(dtype))) return rc;
+    if (!dense || !val || !idx) NMG_FAIL(NMG_ERR_INVALID, "dense, val and idx must be non-NULL");
+    if (n < 1) NMG_FAIL(NMG_ERR_INVALID, "n must be >= 1");
+    if (batch < 1 || ld_dense < K || (batch > 1 && batch_stride < M * ld_dense))
+        NMG_FAIL(NMG_ERR_INVALID, "bad batch / leading dimension (batch=%lld ld=%lld)", (long long)batch, (long long)ld_dense);
+    PatternTable tab;
+    if ((rc = get_pattern_table(n, m, &tab))) return rc;
+    GatherParams p{};
+    p.dense = dense; p.idx = idx; p.val = val; p.order = tab.order;
+    p.M = M; p.K = K; p.ld = ld_dense; p.batch_stride = batch_stride;
+    p.nb = geo.nb; p.nc = geo.nc; p.tiles = batch * geo.nb * geo.nc;
+    p.n = n; p.m = m; p.g = g; p.C = geo.C; p.cc = geo.cc;
+    int64_t ctas = (p.tiles + 7) / 8;
+    const int64_t max_ctas = (int64_t)sm_count() * 16;
+    if (ctas > max_ctas) ctas = max_ctas;
+    cudaStream_t st = (cudaStream_t)stream;
+    NMG_DISPATCH_DTYPE(dtype, T, { gather_layout_kernel<T><<<(unsigned)ctas, 256, 0, st>>>(p); });
     NMG_CUDA(cudaGetLastError());
     return NMG_OK;
 }

@@ -90,7 +90,15 @@ class GroupedNMTensor:
         self.nm_strides["kernel"] = kernel or "sm100"
 
     def clone_layout(self, dense_tensor):
-        raise NotImplementedError("clone_layout is disabled in the reference as well (grouped_nm_tensor.py:904-907)")
+        """A tensor with THIS tensor's layout (same ``idx``, shared) holding ``dense_tensor``'s values at the kept
+        positions: no new magnitude selection.  The reference sketches this (grouped_nm_tensor.py:904-951) and leaves it
+        disabled; it is what keeps a weight gradient, or an optimizer update, in the weight's own layout."""
+        s = self.nm_strides
+        if tuple(dense_tensor.shape) != tuple(s["dense_shape"]):
+            raise ValueError(f"expected a tensor of shape {tuple(s['dense_shape'])}, got {tuple(dense_tensor.shape)}")
+        view3, _ = _kernel_view(dense_tensor.detach(), s["sparse_dim"], s["group_dim"])
+        val = ops.gather_layout(view3, self.idx, s["n"], s["m"], s["group_size"])
+        return GroupedNMTensor(val, self.idx, s)
 
     def to_dense(self):
         return grouped_n_m_to_dense(self.nm_strides, self.val, self.idx)
@@ -159,7 +167,9 @@ class GroupedNMTensor:
 
 
 class PerfectNMTensor:
-    """Per-block top-n by magnitude without the group constraint (reference :1010-1066); plain tensor ops."""
+    """Per-block top-n by magnitude without the group constraint (reference :1010-1066): ``val`` / ``idx`` of shape
+    ``[..., blocks, n, ...]`` with ``idx`` the int64 positions inside each block of m, by descending magnitude.
+    Both directions are one CUDA kernel each (``nmg_perfect_nm_select`` / ``nmg_perfect_nm_densify``)."""
 
     def __init__(self, val, idx, n, m, sparse_dim, sparse_dim_size):
         self.val = val
@@ -171,22 +181,12 @@ class PerfectNMTensor:
 
     @staticmethod
     def from_dense(dense_tensor, n, m, sparse_dim):
-        size = dense_tensor.shape[sparse_dim]
-        blocks = math.ceil(size / m)
-        padded_shape = list(dense_tensor.shape)
-        padded_shape[sparse_dim] = blocks * m
-        padded = pad_to(dense_tensor, padded_shape)
-        split = padded.reshape(*dense_tensor.shape[:sparse_dim], blocks, m, *dense_tensor.shape[sparse_dim + 1:])
-        keep = split.abs().argsort(dim=sparse_dim + 1, descending=True).narrow(sparse_dim + 1, 0, n)
-        return PerfectNMTensor(split.gather(sparse_dim + 1, keep), keep, n, m, sparse_dim, size)
+        sparse_dim %= dense_tensor.ndim
+        val, idx = ops.perfect_nm_select(dense_tensor.detach(), n, m, sparse_dim)
+        return PerfectNMTensor(val, idx, n, m, sparse_dim, dense_tensor.shape[sparse_dim])
 
     def to_dense(self):
-        shape = list(self.val.shape)
-        shape[self.sparse_dim + 1] = self.m
-        dense = torch.zeros(shape, dtype=self.val.dtype, device=self.val.device)
-        dense.scatter_(self.sparse_dim + 1, self.idx, self.val)
-        merged = shape[: self.sparse_dim] + [shape[self.sparse_dim] * self.m] + shape[self.sparse_dim + 2:]
-        return dense.reshape(merged).narrow(self.sparse_dim, 0, self.sparse_dim_size)
+        return ops.perfect_nm_densify(self.val, self.idx, self.n, self.m, self.sparse_dim, self.sparse_dim_size)
 
 
 def is_correct_nm(original_dense, sparsified_dense, sparse_dim, n, m):

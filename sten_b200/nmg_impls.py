@@ -29,6 +29,18 @@ class GroupedNMSparsifier:
         self.g = g
 
 
+class WeightLayoutSparsifier:
+    """Inline gradient sparsifier of a grouped n:m weight: the gradient keeps the weight's own layout (same ``idx``),
+    only the kept positions are stored.  Declared per weight with::
+
+        sb.set_weight_grad(name, inline_sparsifier=WeightLayoutSparsifier(), tmp_format=GroupedNMTensor,
+                           external_sparsifier=KeepAll(), out_format=GroupedNMTensor)
+
+    The reference leaves this open (``clone_layout`` is disabled, grouped_nm_tensor.py:904-951; its linear backward
+    returns dense gradients only).  With it the gradient, the optimizer's view of it and the bytes a data-parallel
+    all-reduce moves are n/m of the dense size, and the layout is identical on every rank."""
+
+
 @sten.register_sparsifier_implementation(sparsifier=GroupedNMSparsifier, inp=torch.Tensor, out=GroupedNMTensor)
 def dense_to_grouped_nm(sparsifier, tensor, grad_fmt=None):
     gnm = GroupedNMTensor.from_dense(tensor, sparsifier.n, sparsifier.m, sparse_dim=tensor.ndim - 2,
@@ -115,10 +127,26 @@ def _linear_bwd(ctx, grad_outputs, input_sparsifiers):
     return (dx, dw, db) if has_bias else (dx, dw)
 
 
+def _linear_bwd_weight_layout(ctx, grad_outputs, input_sparsifiers):
+    """Same products as ``_linear_bwd``; dW leaves as a GroupedNMTensor in the weight's layout.  dY^T X runs on the tensor
+    cores at the dense rate into a transient buffer (a sampled product on the FP32 pipes would be an order of magnitude
+    slower on this hardware) and one gather pass keeps the layout's positions."""
+    grads = list(_linear_bwd(ctx, grad_outputs, input_sparsifiers))
+    if grads[1] is not None:
+        weight = ctx.saved_tensors[1]
+        masked = weight.wrapped_tensor.clone_layout(grads[1])
+        grads[1] = sten.SparseTensorWrapper.wrapped_from_dense(masked, grads[1], None)
+    return tuple(grads)
+
+
 _DENSE_GRAD = (sten.KeepAll, torch.Tensor)
+_LAYOUT_GRAD = (WeightLayoutSparsifier, GroupedNMTensor)
 for _inp in ((torch.Tensor, GroupedNMTensor, torch.Tensor), (torch.Tensor, GroupedNMTensor)):
     sten.register_bwd_op_impl(operator=torch.nn.functional.linear, grad_out=(torch.Tensor,),
                               grad_inp=tuple(_DENSE_GRAD for _ in _inp), inp=_inp)(_linear_bwd)
+    sten.register_bwd_op_impl(operator=torch.nn.functional.linear, grad_out=(torch.Tensor,),
+                              grad_inp=tuple(_LAYOUT_GRAD if f is GroupedNMTensor else _DENSE_GRAD for f in _inp),
+                              inp=_inp)(_linear_bwd_weight_layout)
 
 
 def _mm_fwd(ctx, inputs, output_sparsifiers):

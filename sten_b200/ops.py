@@ -96,6 +96,25 @@ def sparsify(dense3, n, m, g):
     return val, idx
 
 
+def gather_layout(dense3, idx, n, m, g):
+    """Values of dense3 [B, M, K] at the positions the layout ``idx`` keeps: val [T, C, g, n] of dense3's dtype."""
+    assert dense3.dim() == 3
+    dev = _require_cuda(dense3, idx)
+    code = _dtype_code(dense3)
+    B, M, K = dense3.shape
+    if dense3.stride(2) != 1 or dense3.stride(1) < K or (B > 1 and dense3.stride(0) < M * dense3.stride(1)):
+        dense3 = dense3.contiguous()
+    ld, bs = (K, M * K) if dense3.is_contiguous() else (dense3.stride(1), dense3.stride(0))
+    C, cc, nb, nc = geometry(M, K, n, m, g)
+    idx = idx.contiguous()
+    if idx.numel() != B * nc * nb * cc:
+        raise ValueError("idx does not belong to a layout of this shape")
+    val = torch.empty((B * nc * nb, C, g, n), dtype=dense3.dtype, device=dev)
+    with torch.cuda.device(dev):
+        nat.check(nat.lib().nmg_gather(dense3.data_ptr(), idx.data_ptr(), B, M, K, ld, bs, n, m, g, code, val.data_ptr(), _stream(dev)))
+    return val
+
+
 def densify(val, idx, B, M, K, n, m, g):
     """Returns the dense [B, M, K] tensor of a (val, idx) pair."""
     dev = _require_cuda(val, idx)
@@ -106,6 +125,40 @@ def densify(val, idx, B, M, K, n, m, g):
         nat.check(nat.lib().nmg_densify(val.data_ptr(), idx.data_ptr(), B, M, K, n, m, g, code, out.data_ptr(), K,
                                         M * K, _stream(dev)))
     return out
+
+
+def perfect_nm_select(dense, n, m, sparse_dim):
+    """Top-n of every block of m along ``sparse_dim``: (val, idx) of shape [..., blocks, n, ...], idx int64."""
+    dev = _require_cuda(dense)
+    code = _dtype_code(dense)
+    dense = dense.contiguous()
+    shape = list(dense.shape)
+    size = shape[sparse_dim]
+    outer, inner = math.prod(shape[:sparse_dim]), math.prod(shape[sparse_dim + 1:])
+    blocks = -(-size // m)
+    out_shape = shape[:sparse_dim] + [blocks, n] + shape[sparse_dim + 1:]
+    val = torch.empty(out_shape, dtype=dense.dtype, device=dev)
+    idx = torch.empty(out_shape, dtype=torch.int64, device=dev)
+    if val.numel():
+        with torch.cuda.device(dev):
+            nat.check(nat.lib().nmg_perfect_nm_select(dense.data_ptr(), outer, size, inner, n, m, code, val.data_ptr(), idx.data_ptr(),
+                                                      _stream(dev)))
+    return val, idx
+
+
+def perfect_nm_densify(val, idx, n, m, sparse_dim, size):
+    """Inverse of perfect_nm_select: the dense tensor with ``size`` elements along ``sparse_dim``."""
+    dev = _require_cuda(val, idx)
+    code = _dtype_code(val)
+    val, idx = val.contiguous(), idx.contiguous()
+    shape = list(val.shape)
+    outer, inner = math.prod(shape[:sparse_dim]), math.prod(shape[sparse_dim + 2:])
+    dense = torch.empty(shape[:sparse_dim] + [size] + shape[sparse_dim + 2:], dtype=val.dtype, device=dev)
+    if dense.numel():
+        with torch.cuda.device(dev):
+            nat.check(nat.lib().nmg_perfect_nm_densify(val.data_ptr(), idx.data_ptr(), outer, size, inner, n, m, code, dense.data_ptr(),
+                                                       _stream(dev)))
+    return dense
 
 
 def _row_major_2d(t):

@@ -18,6 +18,7 @@ sparsifier / densifier never touch), runs the reference's own CPU sparsifier
   * ``reference_linear.pkl``  a pickle WRITTEN BY THE REFERENCE: a ``torch.nn.Linear`` whose weight is the reference's
                           ``SparseParameterWrapper`` around a ``GroupedNMTensor`` (made by its ``SparsityBuilder``), plus the
                           input and the dense weight it was made from in ``reference_linear.npz``;
+  * ``perfect_cases.npz`` ``val`` / ``idx`` / ``to_dense()`` of the reference's ``PerfectNMTensor`` on tie-free random tensors;
   * ``layout.json``       ``make_n_m`` tables and every key of ``compute_nm_strides`` for a list of shapes;
   * ``spmm_cases.npz``    outputs of the reference's AVX micro-kernels (built by oracle/build_ref.py) on small
                           problems with k-remainders.
@@ -53,7 +54,7 @@ def main(ref_root=None, *parts):
     ref_root = build_ref.reference_root(ref_root)
     if ref_root is None:
         raise SystemExit("no reference tree: pass its path or set NMG_REFERENCE_ROOT")
-    parts = set(parts) or {"small", "big", "layout", "spmm", "pickle"}
+    parts = set(parts) or {"small", "big", "layout", "spmm", "pickle", "perfect"}
     build_ref.import_reference(ref_root)
     import tempfile
     os.chdir(tempfile.gettempdir())  # the reference JIT writes ./.compile_cache
@@ -68,7 +69,32 @@ def main(ref_root=None, *parts):
         gen_spmm(GroupedNMTensor)
     if "pickle" in parts:
         gen_pickle()
+    if "perfect" in parts:
+        gen_perfect()
     print("done")
+
+
+def gen_perfect():
+    """PerfectNMTensor.from_dense / to_dense of the reference (grouped_nm_tensor.py:1010-1066) on tie-free random tensors:
+    every position of the sparse dimension, ragged block counts, n = m, and the 3-D shapes of its conversion test."""
+    from sten.grouped_nm.grouped_nm_tensor import PerfectNMTensor
+    out, meta = {}, []
+    seed = 900
+    for (shape, n, m, sd) in [((64, 100), 2, 4, 0), ((64, 100), 2, 4, 1), ((30, 50), 1, 4, 1), ((37, 120), 2, 8, 0),
+                              ((50, 64), 1, 16, 1), ((3, 5, 17), 5, 12, 2), ((3, 17, 5), 5, 12, 1), ((17, 3, 5), 2, 4, 0),
+                              ((9, 10), 4, 4, 1), ((7, 13), 3, 6, 1), ((2, 3, 16, 40), 1, 8, 2)]:
+        seed += 1
+        dense = seeded_normal(shape, seed)
+        t = PerfectNMTensor.from_dense(dense, n, m, sd)
+        name = f"perfect_{n}_{m}_{sd}_" + "x".join(map(str, shape))
+        out[name + "/dense"] = dense.numpy()
+        out[name + "/val"] = t.val.contiguous().numpy()
+        out[name + "/idx"] = t.idx.contiguous().numpy()
+        out[name + "/to_dense"] = t.to_dense().contiguous().numpy()
+        meta.append(dict(name=name, n=n, m=m, sparse_dim=sd, shape=list(shape)))
+    np.savez_compressed(os.path.join(HERE, "perfect_cases.npz"), **out)
+    with open(os.path.join(HERE, "perfect_cases.json"), "w") as f:
+        json.dump(meta, f, indent=1)
 
 
 def gen_pickle():

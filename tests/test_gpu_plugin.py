@@ -158,3 +158,40 @@ def test_row_shards_equal_slices_of_the_full_sparsified_weight():
     shard = sten.GroupedNMTensor.from_dense(w, n, m, sparse_dim=0, group_size=g, group_dim=1)
     layer = ShardedGroupedNMLinear(shard, None, M)
     assert torch.equal(layer(x), ops.spmm(full_val, full_idx, M, K, n, m, g, x))
+
+
+def test_weight_gradient_in_the_weight_layout_and_clone_layout():
+    """set_weight_grad(..., WeightLayoutSparsifier, GroupedNMTensor): dW comes back packed in the weight's own layout (same
+    idx object), equal to the dense dY^T X at the kept positions; clone_layout is the gather behind it."""
+    import sten_b200 as sten
+    sten.set_dispatch_failure("raise")
+    dev = cuda()
+    M, K, tokens, n, m, g = 96, 200, 64, 2, 4, 4
+    torch.manual_seed(5)
+    lin = torch.nn.Linear(K, M).to(dev)
+    sb = sten.SparsityBuilder()
+    sb.set_weight("weight", initial_sparsifier=sten.GroupedNMSparsifier(n, m, g), out_format=sten.GroupedNMTensor)
+    sb.set_weight_grad("weight", inline_sparsifier=sten.WeightLayoutSparsifier(), tmp_format=sten.GroupedNMTensor,
+                       external_sparsifier=sten.KeepAll(), out_format=sten.GroupedNMTensor)
+    sparse = sb.get_sparse_model(lin)
+    x = torch.randn(tokens, K, device=dev, requires_grad=True)
+    dy = torch.randn(tokens, M, device=dev)
+    sparse(x).backward(dy)
+    gw = sparse.weight.grad
+    assert isinstance(gw, sten.SparseTensorWrapper) and isinstance(gw.wrapped_tensor, sten.GroupedNMTensor)
+    w_gnm, g_gnm = sparse.weight.wrapped_tensor, gw.wrapped_tensor
+    assert g_gnm.idx is w_gnm.idx and g_gnm.val.shape == w_gnm.val.shape
+    dense_dw = dy.t() @ x.detach()
+    kept = w_gnm.clone_layout(torch.ones(M, K, device=dev)).to_dense() != 0      # the layout's positions
+    want = torch.where(kept, dense_dw, torch.zeros_like(dense_dw))
+    assert torch.allclose(g_gnm.to_dense(), want, rtol=1e-5, atol=1e-5)
+    # exactly n of every m rows per column are kept, and dX is unaffected by the gradient format
+    assert int(kept.sum()) == M * K * n // m
+    dx_ref = dy @ w_gnm.to_dense()
+    assert torch.allclose(x.grad, dx_ref, rtol=1e-4, atol=1e-4)
+    # clone_layout on a 3-D layout (n:m along dim 2, groups along dim 1)
+    t3 = sten.GroupedNMTensor.from_dense(torch.rand(3, 5, 17, device=dev), 2, 4, sparse_dim=2, group_size=2, group_dim=1)
+    other = torch.rand(3, 5, 17, device=dev)
+    cl = t3.clone_layout(other)
+    mask3 = t3.to_dense() != 0
+    assert torch.equal(cl.to_dense(), torch.where(mask3, other, torch.zeros_like(other)))
