@@ -133,6 +133,19 @@ int nmg_spmm(const void *val, const int16_t *idx, const void *packed, int64_t M,
              int dtype, const void *act, int64_t ld_act, int64_t tokens, const void *bias, void *out,
              int64_t ld_out, int layout, int algo, void *workspace, size_t workspace_bytes, void *stream);
 
+/* nmg_spmm followed by an activation and a residual add, in one call: out = activation(product + bias) + residual.
+ * The reference adds the bias in a separate pass over the output (src/sten/grouped_nm/sten_impls.py:172-173) and leaves
+ * activation and residual to the model code; here the two-pass tensor-core matmul applies all three in its epilogue
+ * (the output is written once), every other kernel is followed by one elementwise pass.
+ *   activation: NMG_EPI_NONE or NMG_EPI_GELU (exact: x/2 * (1 + erf(x / sqrt 2)))
+ *   residual:   NULL, or a tensor of the output's shape and orientation with row pitch ld_res.
+ * Everything else as nmg_spmm (same workspace query). */
+typedef enum { NMG_EPI_NONE = 0, NMG_EPI_GELU = 1 } nmg_epilogue_act;
+int nmg_spmm_fused(const void *val, const int16_t *idx, const void *packed, int64_t M, int64_t K, int n, int m, int g,
+                   int dtype, const void *act, int64_t ld_act, int64_t tokens, const void *bias, int activation,
+                   const void *residual, int64_t ld_res, void *out, int64_t ld_out, int layout, int algo, void *workspace,
+                   size_t workspace_bytes, void *stream);
+
 /* Transposed product for the backward pass: dX[tokens][ld_dx >= K] = dY[tokens][ld_dy >= M] * W.
  * The reference has no counterpart (its dispatcher installs a failing backward stub: src/sten/sten.py:1690-1693);
  * the registration shape follows the CSR linear backward (sten.py:2362-2383).

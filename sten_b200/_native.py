@@ -13,6 +13,7 @@ NMG_F32, NMG_F16, NMG_BF16 = 0, 1, 2
 NMG_ACT_TOKEN_MAJOR, NMG_ACT_K_MAJOR, NMG_ACT_TOKEN_MAJOR_OUT_ROWS = 0, 1, 2
 NMG_ALGO_AUTO, NMG_ALGO_SIMT, NMG_ALGO_TENSOR, NMG_ALGO_TENSOR_DENSE = 0, 1, 2, 3
 NMG_NOALLOC_SCRATCH_BYTES = 32 << 20
+NMG_EPI_NONE, NMG_EPI_GELU = 0, 1
 
 # name -> (restype, argtypes); must list every function of include/nmg_b200.h (checked by the test-suite)
 _i64, _int, _vp, _sz = ctypes.c_int64, ctypes.c_int, ctypes.c_void_p, ctypes.c_size_t
@@ -31,6 +32,8 @@ SIGNATURES = {
     "nmg_spmm_workspace_bytes": (_sz, [_i64, _i64, _i64, _int, _int, _int, _int, _int, _int, _int]),
     "nmg_spmm": (_int, [_vp, _vp, _vp, _i64, _i64, _int, _int, _int, _int, _vp, _i64, _i64, _vp, _vp, _i64, _int, _int,
                         _vp, _sz, _vp]),
+    "nmg_spmm_fused": (_int, [_vp, _vp, _vp, _i64, _i64, _int, _int, _int, _int, _vp, _i64, _i64, _vp, _int, _vp, _i64, _vp, _i64, _int,
+                              _int, _vp, _sz, _vp]),
     "nmg_spmm_t_workspace_bytes": (_sz, [_i64, _i64, _i64, _int, _int, _int, _int, _int, _int]),
     "nmg_spmm_t": (_int, [_vp, _vp, _vp, _i64, _i64, _int, _int, _int, _int, _vp, _i64, _i64, _vp, _i64, _int, _vp, _sz,
                           _vp]),

@@ -80,7 +80,8 @@ extern "C" size_t nmg_spmm_workspace_bytes(int64_t M, int64_t K, int64_t tokens,
 
 static int spmm_impl(const void *val, const int16_t *idx, const void *packed, int64_t M, int64_t K, int n, int m, int g, int dtype,
                      const void *act, int64_t ld_act, int64_t tokens, const void *bias, void *const *outs, int n_outs, int64_t ld_out,
-                     int layout, int algo, void *workspace, size_t workspace_bytes, void *stream, bool force_dense = false, void *mc_out = nullptr) {
+                     int layout, int algo, void *workspace, size_t workspace_bytes, void *stream, bool force_dense = false, void *mc_out = nullptr,
+                     const Epilogue &epi = Epilogue()) {
     Geo geo;
     int rc = make_geo(M, K, n, m, g, &geo);
     if (rc) return rc;
@@ -111,10 +112,11 @@ static int spmm_impl(const void *val, const int16_t *idx, const void *packed, in
         const void *nval = nullptr;
         const bool dense = force_dense || tc_use_dense(geo, dtype, tokens);
         if (!dense && (rc = resolve_packed(geo, dtype, val, idx, packed, &ws, &left, &pat, &nval, st))) return rc;
-        return tc_matmul(geo, dtype, false, dense, val, idx, pat, nval, act, ld_act, tokens, bias, outs, n_outs, mc_out, ld_out, out_tm ? 1 : 0, ws, left, st);
+        return tc_matmul(geo, dtype, false, dense, val, idx, pat, nval, act, ld_act, tokens, bias, outs, n_outs, mc_out, ld_out, out_tm ? 1 : 0, ws, left, st, epi);
     }
     if (n_outs > 1) NMG_FAIL(NMG_ERR_UNSUPPORTED, "several output buffers need the tensor-core path (aligned token-major activations, >= 64 tokens and rows)");
-    return simt_fwd(geo, dtype, val, idx, act, ld_act, tokens, bias, out, ld_out, layout, workspace, workspace_bytes, st);
+    if ((rc = simt_fwd(geo, dtype, val, idx, act, ld_act, tokens, bias, out, ld_out, layout, workspace, workspace_bytes, st))) return rc;
+    return out_tm ? launch_epilogue(dtype, out, tokens, M, ld_out, epi, st) : launch_epilogue(dtype, out, M, tokens, ld_out, epi, st);
 }
 
 extern "C" int nmg_spmm(const void *val, const int16_t *idx, const void *packed, int64_t M, int64_t K, int n, int m,
@@ -123,6 +125,20 @@ extern "C" int nmg_spmm(const void *val, const int16_t *idx, const void *packed,
     void *outs[1] = {out};
     return spmm_impl(val, idx, packed, M, K, n, m, g, dtype, act, ld_act, tokens, bias, outs, 1, ld_out, layout, algo, workspace,
                      workspace_bytes, stream);
+}
+
+extern "C" int nmg_spmm_fused(const void *val, const int16_t *idx, const void *packed, int64_t M, int64_t K, int n, int m, int g,
+                              int dtype, const void *act, int64_t ld_act, int64_t tokens, const void *bias, int activation,
+                              const void *residual, int64_t ld_res, void *out, int64_t ld_out, int layout, int algo, void *workspace,
+                              size_t workspace_bytes, void *stream) {
+    if (activation != NMG_EPI_NONE && activation != NMG_EPI_GELU) NMG_FAIL(NMG_ERR_INVALID, "unknown activation %d", activation);
+    const bool out_tm = layout == NMG_ACT_TOKEN_MAJOR;
+    if (residual && ld_res < (out_tm ? M : tokens)) NMG_FAIL(NMG_ERR_INVALID, "ld_res=%lld is smaller than the output row", (long long)ld_res);
+    Epilogue epi;
+    epi.act = activation; epi.residual = residual; epi.ld_res = ld_res;
+    void *outs[1] = {out};
+    return spmm_impl(val, idx, packed, M, K, n, m, g, dtype, act, ld_act, tokens, bias, outs, 1, ld_out, layout, algo, workspace,
+                     workspace_bytes, stream, false, nullptr, epi);
 }
 
 extern "C" int nmg_spmm_replicated(const void *val, const int16_t *idx, int64_t M, int64_t K, int n, int m, int g, int dtype,

@@ -153,7 +153,7 @@ static int expand_rows_per_item(const Geo &geo, size_t es, bool tr) {
 // =========================================================================================================
 constexpr int GEMM_DRAIN_WARPS = 8;   // two per TMEM lane quarter, each takes half of the accumulator's columns
 constexpr int GEMM_THREADS = 32 * (2 + GEMM_DRAIN_WARPS);  // TMA warp, MMA warp, drain warps
-constexpr int GEMM_STAGE_BYTES = TC_A_BYTES + TC_B_BYTES;
+constexpr int GEMM_RING_BYTES = TC_STAGES * (TC_A_BYTES + TC_B_BYTES);  // 192 KB of operand stages in either mode
 
 constexpr int GEMM_MAX_OUTS = 8;
 struct GemmParams {
@@ -161,71 +161,103 @@ struct GemmParams {
     void *outs[GEMM_MAX_OUTS];  // the result is written to every one of these (same shape and pitch): outs[0] is the
     int n_out;                  // caller's buffer, the others are typically the same buffer on peer GPUs
     void *mc_out;               // NVSwitch multicast address mapping onto all of outs[], or NULL: one multimem.st reaches every GPU
+    const void *residual;       // added after the activation, same orientation as the output, or NULL
+    int64_t ld_res;
+    int act;                    // NMG_EPI_NONE / NMG_EPI_GELU applied to (product + bias)
     int64_t out_feats, red, ntok, ld_out;
     int out_token_major;
     int out_staged;    // feature-major output whose rows are 16-byte aligned: go through the staging tile
-    int tiles_f, tiles_t;
+    int tiles_f, tiles_t;  // tiles_f counts tiles of 128 features (one CTA per tile) or 256 (CTA pairs)
     int *status;
 };
 constexpr int GEMM_STAGING_BYTES = GEMM_DRAIN_WARPS * 4096;  // per drain warp: 32 feature rows x 128 bytes
 
 struct GemmMaps {
     CUtensorMap a[3];  // weight planes, box 64 x 128, 128-byte swizzle
-    CUtensorMap b[3];  // activation planes, box 64 x 256
+    CUtensorMap b[3];  // activation planes, box 64 x 256 (64 x 128 for CTA pairs)
 };
 
-template <typename T>
+__device__ __forceinline__ float gelu_erf(float v) { return 0.5f * v * (1.f + erff(v * 0.70710678118654752f)); }
+
+// PAIR = false: one CTA per 128-feature x 256-token tile.
+// PAIR = true (16-bit operands): two CTAs of a cluster share a 256-feature x 256-token tile.  Each loads the weight rows
+// of its own 128 features and only half of the activation tile (128 tokens); the MMA (cta_group::2, M = 256, issued by the
+// even CTA) reads both halves from both shared memories.  An SM then takes in 32 KB per 64 reduction elements instead of
+// 48 KB, which is what keeps the tensor core fed from L2.  full[s] lives in the even ("leader") CTA and receives the TMA
+// bytes of both; empty[s] and acc_full[b] exist in both CTAs and are signalled by multicast commits; acc_free[b] lives in
+// the leader and collects the drain warps of both CTAs.  No load is multicast.
+template <typename T, bool PAIR>
 __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_tc_kernel(const GemmParams prm, const __grid_constant__ GemmMaps maps) {
     constexpr int TERMS = TcMode<T>::TERMS;
     using E = typename TcMode<T>::elem;
     constexpr bool SPLIT = TERMS > 1;
+    static_assert(!(PAIR && SPLIT), "CTA pairs serve the 16-bit mode");
     constexpr int NBUF = SPLIT ? 1 : 2;  // accumulator tiles in flight between the MMA issuer and the drain warps
     constexpr uint32_t TMEM_COLS = 2 * TC_ACC_COLS;
+    constexpr int B_BYTES = PAIR ? TC_B_BYTES / 2 : TC_B_BYTES;
+    constexpr int STAGE_BYTES = TC_A_BYTES + B_BYTES;
+    constexpr int STAGES = GEMM_RING_BYTES / STAGE_BYTES;  // 4, or 6 for pairs
+    constexpr int TILE_FEATS = PAIR ? 2 * TC_BM : TC_BM;
 
     extern __shared__ char smem_raw[];
     char *smem = reinterpret_cast<char *>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
-    char *staging = smem + TC_STAGES * GEMM_STAGE_BYTES;
+    char *staging = smem + GEMM_RING_BYTES;
     char *misc = staging + GEMM_STAGING_BYTES;
-    uint64_t *full = reinterpret_cast<uint64_t *>(misc);
-    uint64_t *empty = full + TC_STAGES;
-    uint64_t *acc_full = empty + TC_STAGES;  // [2] MMA issuer -> drain warps: unit complete in accumulator b
-    uint64_t *acc_free = acc_full + 2;       // [2] drain warps -> MMA issuer: accumulator b may be overwritten
-    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(misc + 128);
+    uint64_t *full = reinterpret_cast<uint64_t *>(misc);   // pairs: meaningful in the leader only
+    uint64_t *empty = full + STAGES;
+    uint64_t *acc_full = empty + STAGES;  // [2] MMA issuer -> drain warps: unit complete in accumulator b
+    uint64_t *acc_free = acc_full + 2;    // [2] drain warps -> MMA issuer: accumulator b may be overwritten (pairs: leader only)
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(misc + 192);
+    static_assert((2 * STAGES + 4) * 8 <= 192, "barrier block too small");
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const uint32_t rank = PAIR ? cluster_ctarank() : 0u;
+    const bool leader = rank == 0;
+    const int unit_id = PAIR ? (int)(blockIdx.x >> 1) : (int)blockIdx.x;      // CTA (or pair) index
+    const int nunits = PAIR ? (int)(gridDim.x >> 1) : (int)gridDim.x;
     // A "unit" is what the MMA issuer hands to the drain warps: a whole tile (16-bit) or a chunk of k-blocks (fp32).
     const int ntiles = prm.tiles_f * prm.tiles_t;
-    const int my_tiles = ((int)blockIdx.x < ntiles) ? (ntiles - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x : 0;
+    const int my_tiles = (unit_id < ntiles) ? (ntiles - unit_id + nunits - 1) / nunits : 0;
     const int nkb = (int)((prm.red + TC_BK - 1) / TC_BK) * TERMS;  // iterations per tile: k-blocks x split terms (term fastest)
     const int chunk_it = SPLIT ? TC_CHUNK_KB * TERMS : nkb;
     const int nchunks = (nkb + chunk_it - 1) / chunk_it;
 
     if (tid == 0) {
-        for (int s = 0; s < TC_STAGES; s++) {
+        for (int s = 0; s < STAGES; s++) {
             mbar_init(&full[s], 1);
             mbar_init(&empty[s], 1);
         }
         for (int b = 0; b < 2; b++) {
             mbar_init(&acc_full[b], 1);
-            mbar_init(&acc_free[b], GEMM_DRAIN_WARPS);  // lane 0 of each drain warp
+            mbar_init(&acc_free[b], GEMM_DRAIN_WARPS * (PAIR ? 2 : 1));  // lane 0 of each drain warp (of both CTAs)
         }
         mbar_fence_init();
     }
-    if (warp == 1) tmem_alloc(tmem_slot, TMEM_COLS);
+    if (warp == 1) {
+        if constexpr (PAIR) tmem_alloc_pair(tmem_slot, TMEM_COLS);
+        else tmem_alloc(tmem_slot, TMEM_COLS);
+    }
     tc_fence_before();
     __syncthreads();
+    if constexpr (PAIR) cluster_sync_all();  // barriers of both CTAs are initialised before anyone arrives remotely
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
+    const uint32_t full_leader = PAIR ? map_to_rank(smem_u32(&full[0]), 0) : 0u;
+    const uint32_t acc_free_leader = PAIR ? map_to_rank(smem_u32(&acc_free[0]), 0) : 0u;
 
-    auto tile_origin = [&](int ti, int &feat0, int &tok0) {
+    auto wait = [&](uint64_t *bar, uint32_t parity, int code) -> bool {
+        if constexpr (PAIR) return mbar_wait_cluster_bounded(bar, parity, prm.status, code);
+        else return mbar_wait_bounded(bar, parity, prm.status, code);
+    };
+    auto tile_origin = [&](int ti, int &feat0, int &tok0) {  // feat0: first feature of THIS CTA's 128 rows
         int tile_f, tile_t;
-        tile_of_cta((int)blockIdx.x + ti * (int)gridDim.x, prm.tiles_f, prm.tiles_t, tile_f, tile_t);
-        feat0 = tile_f * TC_BM;
+        tile_of_cta(unit_id + ti * nunits, prm.tiles_f, prm.tiles_t, tile_f, tile_t);
+        feat0 = tile_f * TILE_FEATS + (int)rank * TC_BM;
         tok0 = tile_t * TC_BN;
     };
 
     if (warp == 0) {
-        // ------------------------------------------------------------------ TMA producer (one lane)
+        // ------------------------------------------------------------------ TMA producer (one lane per CTA)
         if (lane == 0) {
             int it = 0;
             bool ok = true;
@@ -236,46 +268,58 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_tc_kernel(const GemmPara
                 int feat0, tok0;
                 tile_origin(ti, feat0, tok0);
                 for (int kb = 0; kb < nkb; kb++, it++) {
-                    const int s = it % TC_STAGES;
-                    const uint32_t ph = (uint32_t)((it / TC_STAGES) & 1);
-                    if (!(ok = mbar_wait_bounded(&empty[s], ph ^ 1, prm.status, 21))) break;
-                    mbar_expect_tx(&full[s], GEMM_STAGE_BYTES);
+                    const int s = it % STAGES;
+                    const uint32_t ph = (uint32_t)((it / STAGES) & 1);
+                    if (!(ok = wait(&empty[s], ph ^ 1, 21))) break;
                     const int term = kb % TERMS;
                     const int wc = TERMS == 1 ? 0 : kSplitW[term], xc = TERMS == 1 ? 0 : kSplitX[term];
-                    char *stage = smem + s * GEMM_STAGE_BYTES;
-                    tma_load_2d(stage, &maps.a[wc], (kb / TERMS) * TC_BK, feat0, &full[s]);
-                    tma_load_2d(stage + TC_A_BYTES, &maps.b[xc], (kb / TERMS) * TC_BK, tok0, &full[s]);
+                    char *stage = smem + s * STAGE_BYTES;
+                    if constexpr (PAIR) {
+                        if (leader) mbar_expect_tx(&full[s], 2 * STAGE_BYTES);  // both CTAs report to this barrier
+                        tma_load_2d_pair(stage, &maps.a[wc], (kb / TERMS) * TC_BK, feat0, full_leader + s * 8);
+                        tma_load_2d_pair(stage + TC_A_BYTES, &maps.b[xc], (kb / TERMS) * TC_BK, tok0 + (int)rank * 128, full_leader + s * 8);
+                    } else {
+                        mbar_expect_tx(&full[s], STAGE_BYTES);
+                        tma_load_2d(stage, &maps.a[wc], (kb / TERMS) * TC_BK, feat0, &full[s]);
+                        tma_load_2d(stage + TC_A_BYTES, &maps.b[xc], (kb / TERMS) * TC_BK, tok0, &full[s]);
+                    }
                 }
             }
         }
     } else if (warp == 1) {
-        // ------------------------------------------------------------------ MMA issuer (one lane)
-        if (lane == 0) {
-            const uint32_t idesc = make_idesc<E>();
+        // ------------------------------------------------------------------ MMA issuer (one lane; of the leader for pairs)
+        if (lane == 0 && leader) {
+            uint32_t idesc = make_idesc<E>();
+            if constexpr (PAIR) idesc = (idesc & ~(0x1fu << 24)) | ((uint32_t)(256 >> 4) << 24);  // M = 256 across the pair
             bool ok = true;
             int it = 0, unit = 0;
             for (int ti = 0; ti < my_tiles && ok; ti++) {
                 int kb = 0;
                 for (int c = 0; c < nchunks && ok; c++, unit++) {
                     const int b = unit % NBUF, use = unit / NBUF;
-                    if (use > 0) ok = mbar_wait_bounded(&acc_free[b], (uint32_t)((use - 1) & 1), prm.status, 26);
+                    if (use > 0) ok = wait(&acc_free[b], (uint32_t)((use - 1) & 1), 26);
                     if (!ok) break;
                     tc_fence_after();
                     const uint32_t d_tmem = tmem_base + (uint32_t)(b * TC_ACC_COLS);
                     const int kend = (kb + chunk_it < nkb) ? kb + chunk_it : nkb;
                     for (bool first = true; kb < kend; kb++, it++, first = false) {
-                        const int s = it % TC_STAGES;
-                        const uint32_t ph = (uint32_t)((it / TC_STAGES) & 1);
-                        if (!(ok = mbar_wait_bounded(&full[s], ph, prm.status, 22))) break;
+                        const int s = it % STAGES;
+                        const uint32_t ph = (uint32_t)((it / STAGES) & 1);
+                        if (!(ok = wait(&full[s], ph, 22))) break;
                         tc_fence_after();
-                        const uint64_t adesc = make_sw128_desc(smem_u32(smem + s * GEMM_STAGE_BYTES));
-                        const uint64_t bdesc = make_sw128_desc(smem_u32(smem + s * GEMM_STAGE_BYTES + TC_A_BYTES));
+                        const uint64_t adesc = make_sw128_desc(smem_u32(smem + s * STAGE_BYTES));
+                        const uint64_t bdesc = make_sw128_desc(smem_u32(smem + s * STAGE_BYTES + TC_A_BYTES));
 #pragma unroll
-                        for (int k = 0; k < TC_BK / 16; k++)  // 16 elements = 32 bytes = 2 descriptor units per step
-                            tc_mma_f16(d_tmem, adesc + 2 * k, bdesc + 2 * k, idesc, (first && k == 0) ? 0u : 1u);
-                        tc_commit(&empty[s]);  // arrives when the MMAs above have read the stage
+                        for (int k = 0; k < TC_BK / 16; k++) {  // 16 elements = 32 bytes = 2 descriptor units per step
+                            if constexpr (PAIR) tc2_mma_f16(d_tmem, adesc + 2 * k, bdesc + 2 * k, idesc, (first && k == 0) ? 0u : 1u);
+                            else tc_mma_f16(d_tmem, adesc + 2 * k, bdesc + 2 * k, idesc, (first && k == 0) ? 0u : 1u);
+                        }
+                        if constexpr (PAIR) tc2_commit_both(&empty[s]);
+                        else tc_commit(&empty[s]);  // arrives when the MMAs above have read the stage
                     }
-                    tc_commit(&acc_full[b]);   // arrives when the unit's MMAs have written TMEM (also on the error path)
+                    // arrives when the unit's MMAs have written TMEM (also on the error path)
+                    if constexpr (PAIR) tc2_commit_both(&acc_full[b]);
+                    else tc_commit(&acc_full[b]);
                 }
             }
         }
@@ -293,6 +337,16 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_tc_kernel(const GemmPara
         const int sl0 = ((warp - 2) >> 2) * SLICES;                    // this warp's first slice
         const uint32_t lane_base = tmem_base + ((uint32_t)(q * 32) << 16);
         char *stage_w = staging + (warp - 2) * 4096;
+        const T *res = static_cast<const T *>(prm.residual);
+        const bool gelu = prm.act == NMG_EPI_GELU;
+        // value of one output element: activation(product + bias) + residual[off], off = the element's offset in a
+        // tensor of the output's orientation with row pitch ld_res
+        auto finish = [&](uint32_t acc, float bias, int64_t res_off) -> float {
+            float v = __uint_as_float(acc) + bias;
+            if (gelu) v = gelu_erf(v);
+            if (res) v += DT<T>::to_f32(res[res_off]);
+            return v;
+        };
         int unit = 0;
         bool ok = true;
         for (int ti = 0; ti < my_tiles && ok; ti++) {
@@ -303,9 +357,17 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_tc_kernel(const GemmPara
             const float bias = (prm.bias && feat_ok) ? DT<T>::to_f32(static_cast<const T *>(prm.bias)[feat]) : 0.f;
             for (int c = 0; c < nchunks; c++, unit++) {
                 const int b = unit % NBUF, use = unit / NBUF;
-                if (!(ok = mbar_wait_bounded(&acc_full[b], (uint32_t)(use & 1), prm.status, 25))) break;
+                if (!(ok = wait(&acc_full[b], (uint32_t)(use & 1), 25))) break;
                 tc_fence_after();
                 const bool last = c == nchunks - 1;
+                auto release = [&]() {  // this warp's TMEM reads of the unit are done: the issuer may reuse the accumulator once all warps say so
+                    tc_fence_before();
+                    __syncwarp();
+                    if (lane == 0) {
+                        if constexpr (PAIR) mbar_arrive_remote(acc_free_leader + b * 8);
+                        else mbar_arrive(&acc_free[b]);
+                    }
+                };
                 // handle(sl, r): slice sl of the unit is in registers r (this lane's feature row, 32 tokens)
                 auto handle = [&](int sl, uint32_t (&r)[32]) {
                     if (SPLIT && c > 0) {
@@ -318,19 +380,16 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_tc_kernel(const GemmPara
                         tmem_st32(lane_base + (uint32_t)(TC_ACC_COLS + sl * 32), r);
                         return;
                     }
-                    if (sl == sl0 + SLICES - 1) {  // this warp's TMEM reads of the unit are done: the issuer may reuse the accumulator once all warps say so
-                        tc_fence_before();
-                        __syncwarp();
-                        if (lane == 0) mbar_arrive(&acc_free[b]);
-                    }
+                    if (sl == sl0 + SLICES - 1) release();
                     const int64_t tokc = (int64_t)tok0 + sl * 32;
                     if (!prm.out_staged) {
                         if (tokc >= prm.ntok || !feat_ok) return;
                         if (prm.out_token_major && prm.n_out == 1 && tokc + 32 <= prm.ntok) {
                             // full slice of the F.linear layout: one conversion, one pointer step and one store per element
                             T *p = static_cast<T *>(prm.outs[0]) + tokc * prm.ld_out + feat;
+                            int64_t ro = tokc * prm.ld_res + feat;
 #pragma unroll
-                            for (int j = 0; j < 32; j++, p += prm.ld_out) *p = DT<T>::from_f32(__uint_as_float(r[j]) + bias);
+                            for (int j = 0; j < 32; j++, p += prm.ld_out, ro += prm.ld_res) *p = DT<T>::from_f32(finish(r[j], bias, ro));
                             return;
                         }
                         for (int d = 0; d < prm.n_out; d++) {
@@ -339,7 +398,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_tc_kernel(const GemmPara
                             for (int j = 0; j < 32; j++) {
                                 const int64_t tok = tokc + j;
                                 if (tok < prm.ntok) {
-                                    const T o = DT<T>::from_f32(__uint_as_float(r[j]) + bias);
+                                    const T o = DT<T>::from_f32(finish(r[j], bias, prm.out_token_major ? tok * prm.ld_res + feat : feat * prm.ld_res + tok));
                                     if (prm.out_token_major) out[tok * prm.ld_out + feat] = o;
                                     else out[feat * prm.ld_out + tok] = o;
                                 }
@@ -350,17 +409,28 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_tc_kernel(const GemmPara
                     // registers -> staging row `lane`
                     constexpr int CH = 32 / CHUNK_TOK;  // chunks per slice: 4 (16-bit) or 8 (fp32)
                     const int ch0 = (sl % GROUP_SLICES) * CH;
+                    const bool plain = !gelu && !res;   // the common case keeps its short path
+                    const int64_t ro0 = feat * prm.ld_res + tokc;  // staged output is feature-major
 #pragma unroll
                     for (int v = 0; v < CH; v++) {
                         uint4 w;
                         if constexpr (sizeof(T) == 4) {
-                            w = make_uint4(__float_as_uint(__uint_as_float(r[4 * v]) + bias), __float_as_uint(__uint_as_float(r[4 * v + 1]) + bias),
-                                           __float_as_uint(__uint_as_float(r[4 * v + 2]) + bias), __float_as_uint(__uint_as_float(r[4 * v + 3]) + bias));
+                            float f[4];
+#pragma unroll
+                            for (int k = 0; k < 4; k++)
+                                f[k] = plain ? __uint_as_float(r[4 * v + k]) + bias
+                                             : finish(r[4 * v + k], bias, (feat_ok && tokc + 4 * v + k < prm.ntok) ? ro0 + 4 * v + k : 0);
+                            w = make_uint4(__float_as_uint(f[0]), __float_as_uint(f[1]), __float_as_uint(f[2]), __float_as_uint(f[3]));
                         } else {
                             uint32_t h[4];
 #pragma unroll
-                            for (int k = 0; k < 4; k++)  // one packed conversion per pair
-                                h[k] = pack2<T>(__uint_as_float(r[8 * v + 2 * k]) + bias, __uint_as_float(r[8 * v + 2 * k + 1]) + bias);
+                            for (int k = 0; k < 4; k++) {  // one packed conversion per pair
+                                const int e0 = 8 * v + 2 * k;
+                                const float lo = plain ? __uint_as_float(r[e0]) + bias : finish(r[e0], bias, (feat_ok && tokc + e0 < prm.ntok) ? ro0 + e0 : 0);
+                                const float hi = plain ? __uint_as_float(r[e0 + 1]) + bias
+                                                       : finish(r[e0 + 1], bias, (feat_ok && tokc + e0 + 1 < prm.ntok) ? ro0 + e0 + 1 : 0);
+                                h[k] = pack2<T>(lo, hi);
+                            }
                             w = make_uint4(h[0], h[1], h[2], h[3]);
                         }
                         *reinterpret_cast<uint4 *>(stage_w + lane * 128 + (((ch0 + v) ^ (lane & 7)) << 4)) = w;
@@ -405,18 +475,16 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_tc_kernel(const GemmPara
                     if (sl + 2 < sl0 + SLICES) tmem_ld32_issue(acc_addr + (uint32_t)((sl + 2) * 32), ra);
                     handle(sl + 1, rb);
                 }
-                if (!last) {  // promotion finished: hand the accumulator back
-                    tc_fence_before();
-                    __syncwarp();
-                    if (lane == 0) mbar_arrive(&acc_free[b]);
-                }
+                if (!last) release();  // promotion finished: hand the accumulator back
             }
         }
     }
     __syncthreads();
+    if constexpr (PAIR) cluster_sync_all();  // the peer no longer reads this CTA's shared memory or signals its barriers
     if (warp == 1) {
         tc_fence_after();
-        tmem_dealloc(tmem_base, TMEM_COLS);
+        if constexpr (PAIR) tmem_dealloc_pair(tmem_base, TMEM_COLS);
+        else tmem_dealloc(tmem_base, TMEM_COLS);
     }
 }
 
@@ -453,33 +521,43 @@ template <typename T, bool TR> static int expand_launch(const ExpandParams &p, s
     return expand_launch_n<T, TR, 0>(p, smem, items, st);
 }
 
-template <typename T> static int gemm_launch(const GemmParams &p, const GemmMaps &maps, cudaStream_t st) {
-    const size_t smem = (size_t)TC_STAGES * GEMM_STAGE_BYTES + GEMM_STAGING_BYTES + 256 + 1024;
+template <typename T, bool PAIR> static int gemm_launch(const GemmParams &p, const GemmMaps &maps, cudaStream_t st) {
+    const size_t smem = (size_t)GEMM_RING_BYTES + GEMM_STAGING_BYTES + 256 + 1024;
     int dev = 0, sms = 148;
     NMG_CUDA(cudaGetDevice(&dev));
     NMG_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
     const int64_t tiles = (int64_t)p.tiles_f * p.tiles_t;
     if (tiles > 0x3fffffff) NMG_FAIL(NMG_ERR_UNSUPPORTED, "too many output tiles for one launch");
-    NMG_CUDA(cudaFuncSetAttribute(gemm_tc_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    NMG_CUDA(cudaFuncSetAttribute(gemm_tc_kernel<T, PAIR>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3((unsigned)(tiles < sms ? tiles : sms));  // persistent
+    const int64_t units = PAIR ? sms / 2 : sms;  // persistent CTAs, or CTA pairs
+    cfg.gridDim = dim3((unsigned)((tiles < units ? tiles : units) * (PAIR ? 2 : 1)));
     cfg.blockDim = dim3(GEMM_THREADS);
     cfg.dynamicSmemBytes = smem;
     cfg.stream = st;
-    cudaLaunchAttribute attr[1];
+    cudaLaunchAttribute attr[2];
     attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;  // overlap the prologue with the expansion pass's tail
     attr[0].val.programmaticStreamSerializationAllowed = 1;
+    attr[1].id = cudaLaunchAttributeClusterDimension;
+    attr[1].val.clusterDim.x = 2;
+    attr[1].val.clusterDim.y = 1;
+    attr[1].val.clusterDim.z = 1;
     cfg.attrs = attr;
-    cfg.numAttrs = 1;
-    NMG_CUDA(cudaLaunchKernelEx(&cfg, gemm_tc_kernel<T>, p, maps));
+    cfg.numAttrs = PAIR ? 2 : 1;
+    NMG_CUDA(cudaLaunchKernelEx(&cfg, gemm_tc_kernel<T, PAIR>, p, maps));
     return NMG_OK;
 }
 
-// act_maps: tensor maps of the activation planes (box 64 x 256, 128-byte swizzle), one for 16-bit data, three for
-// the fp32 split.  ws holds the expanded weight for the duration of the call.
+// CTA pairs serve 16-bit operands when the output has at least two 128-feature tiles (a pair covers 256 features).
+bool tc_dense_uses_pair(const Geo &geo, int dtype, bool transposed) {
+    return dtype != NMG_F32 && (transposed ? geo.K : geo.M) > TC_BM;
+}
+
+// act_maps: tensor maps of the activation planes (128-byte swizzle; box 64 x 128 when tc_dense_uses_pair, else 64 x 256),
+// one for 16-bit data, three for the fp32 split.  ws holds the expanded weight for the duration of the call.
 int tc_dense_matmul(const Geo &geo, int dtype, bool transposed, const void *val, const int16_t *idx, const CUtensorMap *act_maps,
                     int64_t tokens, const void *bias, void *const *outs, int n_outs, void *mc_out, int64_t ld_out, int out_token_major,
-                    void *ws, size_t ws_bytes, cudaStream_t st) {
+                    void *ws, size_t ws_bytes, cudaStream_t st, const Epilogue &epi) {
     if (n_outs < 1 || n_outs > GEMM_MAX_OUTS) NMG_FAIL(NMG_ERR_INVALID, "between 1 and %d output buffers, got %d", GEMM_MAX_OUTS, n_outs);
     const int64_t rows = transposed ? geo.K : geo.M, red = transposed ? geo.M : geo.K;
     const size_t need = tc_dense_workspace_bytes(geo, dtype, transposed);
@@ -530,12 +608,15 @@ int tc_dense_matmul(const Geo &geo, int dtype, bool transposed, const void *val,
     gp.out_token_major = out_token_major;
     gp.out_staged = vec ? 1 : 0;
     gp.mc_out = (vec && mc_out && (reinterpret_cast<uintptr_t>(mc_out) & 15) == 0) ? mc_out : nullptr;
-    gp.tiles_f = (int)((rows + TC_BM - 1) / TC_BM);
+    const bool pair = tc_dense_uses_pair(geo, dtype, transposed);
+    const int tile_feats = pair ? 2 * TC_BM : TC_BM;
+    gp.tiles_f = (int)((rows + tile_feats - 1) / tile_feats);
     gp.tiles_t = (int)((tokens + TC_BN - 1) / TC_BN);
     gp.status = status;
-    if (dtype == NMG_F16) return gemm_launch<__half>(gp, maps, st);
-    if (dtype == NMG_BF16) return gemm_launch<__nv_bfloat16>(gp, maps, st);
-    return gemm_launch<float>(gp, maps, st);
+    gp.act = epi.act; gp.residual = epi.residual; gp.ld_res = epi.ld_res;
+    if (dtype == NMG_F32) return gemm_launch<float, false>(gp, maps, st);
+    if (dtype == NMG_F16) return pair ? gemm_launch<__half, true>(gp, maps, st) : gemm_launch<__half, false>(gp, maps, st);
+    return pair ? gemm_launch<__nv_bfloat16, true>(gp, maps, st) : gemm_launch<__nv_bfloat16, false>(gp, maps, st);
 }
 
 }  // namespace nmg

@@ -38,6 +38,17 @@ int simt_bwd(const Geo &geo, int dtype, const uint16_t *pat, const void *nval, c
 // inside the matmul; the two-pass variant (nmg_gemm_tc.cu, `dense` = true) first expands (val, idx) into a dense 16-bit
 // matrix in `ws` (tc_dense_workspace_bytes, after the split activation) and multiplies that.  tc_use_dense is the
 // policy: two passes from 1280 tokens on (256 for fp32), and for every (n, m) the fused kernel has no instantiation for.
+// What follows the product: out = activation(product + bias) + residual.  The two-pass tensor-core matmul applies it in its
+// epilogue; every other kernel is followed by one elementwise pass (launch_epilogue).
+struct Epilogue {
+    int act = NMG_EPI_NONE;
+    const void *residual = nullptr;  // same orientation as the output
+    int64_t ld_res = 0;
+    bool any() const { return act != NMG_EPI_NONE || residual != nullptr; }
+};
+int launch_epilogue(int dtype, void *out, int64_t rows, int64_t cols, int64_t ld_out, const Epilogue &epi, cudaStream_t st);
+bool tc_dense_uses_pair(const Geo &geo, int dtype, bool transposed);
+
 bool tc_supported(const Geo &geo, int dtype);        // fused kernel
 bool tc_dense_supported(const Geo &geo, int dtype);  // two-pass variant
 bool tc_use_dense(const Geo &geo, int dtype, int64_t tokens);
@@ -50,10 +61,10 @@ size_t tc_ksplit_workspace_bytes(const Geo &geo, int dtype, bool transposed, int
 // not NULL, is an NVSwitch multicast address that maps onto all of them: full 16-byte chunks are then stored once.
 int tc_matmul(const Geo &geo, int dtype, bool transposed, bool dense, const void *val, const int16_t *idx, const uint16_t *pat,
               const void *nval, const void *act, int64_t ld_act, int64_t tokens, const void *bias, void *const *outs, int n_outs,
-              void *mc_out, int64_t ld_out, int out_token_major, void *ws, size_t ws_bytes, cudaStream_t st);
+              void *mc_out, int64_t ld_out, int out_token_major, void *ws, size_t ws_bytes, cudaStream_t st, const Epilogue &epi = Epilogue());
 int tc_dense_matmul(const Geo &geo, int dtype, bool transposed, const void *val, const int16_t *idx, const CUtensorMap *act_maps,
                     int64_t tokens, const void *bias, void *const *outs, int n_outs, void *mc_out, int64_t ld_out, int out_token_major,
-                    void *ws, size_t ws_bytes, cudaStream_t st);
+                    void *ws, size_t ws_bytes, cudaStream_t st, const Epilogue &epi);
 
 // Structured-sparse tensor-core path of the transposed product (nmg_gemm_sp.cu): tcgen05.mma.sp on W^T compressed along
 // the reduction axis (the weight's rows).  16-bit weights with n <= 2 and m in {4, 8, 16, 32, 64}; taken from the token

@@ -614,11 +614,12 @@ bool tc_use_dense(const Geo &geo, int dtype, int64_t tokens) {
 // act: [tokens][ld_act] with the reduction axis contiguous (X for the forward, dY for the transposed product).
 int tc_matmul(const Geo &geo, int dtype, bool transposed, bool dense, const void *val, const int16_t *idx, const uint16_t *pat,
               const void *nval, const void *act, int64_t ld_act, int64_t tokens, const void *bias, void *const *outs, int n_outs,
-              void *mc_out, int64_t ld_out, int out_token_major, void *ws, size_t ws_bytes, cudaStream_t st) {
+              void *mc_out, int64_t ld_out, int out_token_major, void *ws, size_t ws_bytes, cudaStream_t st, const Epilogue &epi) {
     if (n_outs < 1 || (n_outs > 1 && !dense)) NMG_FAIL(NMG_ERR_UNSUPPORTED, "several output buffers need the two-pass tensor-core variant");
     void *out = outs[0];
     const int64_t red = transposed ? geo.M : geo.K;
-    const uint32_t box_tok = TC_BN;
+    // the two-pass variant on CTA pairs loads the activation tile in two halves of 128 tokens
+    const uint32_t box_tok = (dense && tc_dense_uses_pair(geo, dtype, transposed)) ? 128 : TC_BN;
     CUtensorMap tm[3];
     int rc;
     const void *planes[3] = {nval, nval, nval};
@@ -652,7 +653,7 @@ int tc_matmul(const Geo &geo, int dtype, bool transposed, bool dense, const void
     if (dense) {
         const ProfileEvents pe = take_profile_events();
         if (pe.start) NMG_CUDA(cudaEventRecord(pe.start, st));
-        rc = tc_dense_matmul(geo, dtype, transposed, val, idx, tm, tokens, bias, outs, n_outs, mc_out, ld_out, out_token_major, ws, ws_bytes, st);
+        rc = tc_dense_matmul(geo, dtype, transposed, val, idx, tm, tokens, bias, outs, n_outs, mc_out, ld_out, out_token_major, ws, ws_bytes, st, epi);
         if (rc == NMG_OK && pe.stop) NMG_CUDA(cudaEventRecord(pe.stop, st));
         return rc;
     }
@@ -701,8 +702,34 @@ int tc_matmul(const Geo &geo, int dtype, bool transposed, bool dense, const void
                                                                        out_token_major);
         NMG_CUDA(cudaGetLastError());
     }
+    if (rc == NMG_OK && epi.any()) {
+        const int64_t feats_out = transposed ? geo.K : geo.M;
+        rc = out_token_major ? launch_epilogue(dtype, out, tokens, feats_out, ld_out, epi, st) : launch_epilogue(dtype, out, feats_out, tokens, ld_out, epi, st);
+    }
     if (rc == NMG_OK && pe.stop) NMG_CUDA(cudaEventRecord(pe.stop, st));
     return rc;
+}
+
+// ---- activation / residual after kernels that do not fuse them --------------------------------------------------------
+template <typename T>
+__global__ void __launch_bounds__(256) epilogue_kernel(T *out, int64_t rows, int64_t cols, int64_t ld_out, int act, const T *res, int64_t ld_res) {
+    for (int64_t r = blockIdx.y; r < rows; r += gridDim.y)
+        for (int64_t c = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; c < cols; c += (int64_t)gridDim.x * blockDim.x) {
+            float v = DT<T>::to_f32(out[r * ld_out + c]);
+            if (act == NMG_EPI_GELU) v = 0.5f * v * (1.f + erff(v * 0.70710678118654752f));
+            if (res) v += DT<T>::to_f32(res[r * ld_res + c]);
+            out[r * ld_out + c] = DT<T>::from_f32(v);
+        }
+}
+
+int launch_epilogue(int dtype, void *out, int64_t rows, int64_t cols, int64_t ld_out, const Epilogue &epi, cudaStream_t st) {
+    if (!epi.any() || rows < 1 || cols < 1) return NMG_OK;
+    dim3 grid((unsigned)((cols + 255) / 256 < 64 ? (cols + 255) / 256 : 64), (unsigned)(rows < 65535 ? rows : 65535));
+    NMG_DISPATCH_DTYPE(dtype, T, {
+        epilogue_kernel<T><<<grid, 256, 0, st>>>(static_cast<T *>(out), rows, cols, ld_out, epi.act, static_cast<const T *>(epi.residual), epi.ld_res);
+    });
+    NMG_CUDA(cudaGetLastError());
+    return NMG_OK;
 }
 
 }  // namespace nmg

@@ -197,10 +197,12 @@ def _spmm_workspace_bytes(M, K, tokens, n, m, g, code, layout, algo, have_packed
 
 
 def spmm(val, idx, M, K, n, m, g, act, bias=None, layout=nat.NMG_ACT_TOKEN_MAJOR, algo=nat.NMG_ALGO_AUTO, out=None,
-         packed=None):
+         packed=None, activation=None, residual=None):
     """layout TOKEN_MAJOR:          act [tokens, K] -> out [tokens, M] = act @ W^T (+ bias)
        layout K_MAJOR:              act [K, tokens] -> out [M, tokens] = W @ act   (+ bias per row)
-       layout TOKEN_MAJOR_OUT_ROWS: act [tokens, K] -> out [M, tokens] = W @ act^T (+ bias per row)"""
+       layout TOKEN_MAJOR_OUT_ROWS: act [tokens, K] -> out [M, tokens] = W @ act^T (+ bias per row)
+    ``activation="gelu"`` and ``residual`` (a tensor of the output's shape) make it out = activation(product + bias) + residual
+    in the same call (fused into the matmul's epilogue on the two-pass tensor-core path)."""
     dev = _require_cuda(val, idx, act, bias)
     code = _dtype_code(val)
     if act.dtype != val.dtype or (bias is not None and bias.dtype != val.dtype):
@@ -230,12 +232,27 @@ def spmm(val, idx, M, K, n, m, g, act, bias=None, layout=nat.NMG_ACT_TOKEN_MAJOR
     if bias is not None:
         bias = bias.contiguous()
     L = nat.lib()
+    if activation not in (None, "gelu"):
+        raise ValueError("activation must be None or 'gelu'")
+    fused = activation is not None or residual is not None
+    if residual is not None:
+        _require_cuda(residual)
+        if residual.dtype != val.dtype or tuple(residual.shape) != out_shape or (out_shape[1] > 1 and residual.stride(1) != 1):
+            raise ValueError(f"residual must be a {val.dtype} tensor of shape {out_shape} with contiguous rows")
     with _on_device(dev):
         ws, nbytes = _workspace(_spmm_workspace_bytes(M, K, tokens, n, m, g, code, layout, algo, 1 if packed is not None else 0), dev)
-        nat.check(L.nmg_spmm(val.data_ptr(), idx.data_ptr(), packed.data_ptr() if packed is not None else None, M, K, n,
-                             m, g, code, act.data_ptr(), ld_act, tokens,
-                             bias.data_ptr() if bias is not None else None, out.data_ptr(), ld_out, layout, algo,
-                             ws.data_ptr() if ws is not None else None, nbytes, _stream(dev)))
+        if fused:
+            nat.check(L.nmg_spmm_fused(val.data_ptr(), idx.data_ptr(), packed.data_ptr() if packed is not None else None, M, K, n,
+                                       m, g, code, act.data_ptr(), ld_act, tokens, bias.data_ptr() if bias is not None else None,
+                                       nat.NMG_EPI_GELU if activation == "gelu" else nat.NMG_EPI_NONE,
+                                       residual.data_ptr() if residual is not None else None,
+                                       (residual.stride(0) if out_shape[0] > 1 else out_shape[1]) if residual is not None else 0,
+                                       out.data_ptr(), ld_out, layout, algo, ws.data_ptr() if ws is not None else None, nbytes, _stream(dev)))
+        else:
+            nat.check(L.nmg_spmm(val.data_ptr(), idx.data_ptr(), packed.data_ptr() if packed is not None else None, M, K, n,
+                                 m, g, code, act.data_ptr(), ld_act, tokens,
+                                 bias.data_ptr() if bias is not None else None, out.data_ptr(), ld_out, layout, algo,
+                                 ws.data_ptr() if ws is not None else None, nbytes, _stream(dev)))
     return out
 
 

@@ -305,3 +305,30 @@ def test_workspace_and_argument_errors():
     ops.spmm(val, idx, M, K, n, m, g, x, out=wide[:, :M])                         # a column slice is fine: ld_out = stride(0)
     assert torch.equal(wide[:, :M], ops.spmm(val, idx, M, K, n, m, g, x)) and float(wide[:, M:].abs().max()) == 0
     assert ops.read_status() == 0
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16, torch.float32])
+@pytest.mark.parametrize("tokens,algo", [(1536, "tensor"), (200, "tensor"), (200, "simt")])
+def test_fused_activation_and_residual(dtype, tokens, algo):
+    """out = gelu(x W^T + b) + residual in one call, on the two-pass tensor-core path (fused into the epilogue; CTA pairs
+    for 16-bit), the fused-expansion kernel and the SIMT kernel (each followed by one elementwise pass)."""
+    from sten_b200 import _native as nat, ops
+    M, K, n, m, g = 392, 520, 2, 4, 16
+    tol = TOL_F32 if dtype == torch.float32 else TOL_HALF
+    val, idx, x, dense = _problem(M, K, n, m, g, tokens, 123, dtype)
+    bias = seeded_normal((M,), 7).to(dtype).to(cuda())
+    res = seeded_normal((tokens, M), 8).to(dtype).to(cuda())
+    a = nat.NMG_ALGO_TENSOR if algo == "tensor" else nat.NMG_ALGO_SIMT
+    pre = np_of(x).astype(np.float64) @ np_of(dense).astype(np.float64).T + np_of(bias).astype(np.float64)
+    gelu = torch.nn.functional.gelu(torch.from_numpy(pre)).numpy()
+    y = ops.spmm(val, idx, M, K, n, m, g, x, bias=bias, algo=a, activation="gelu", residual=res)
+    assert rel_fro(np_of(y), gelu + np_of(res).astype(np.float64)) <= tol
+    y2 = ops.spmm(val, idx, M, K, n, m, g, x, bias=bias, algo=a, activation="gelu")
+    assert rel_fro(np_of(y2), gelu) <= tol
+    y3 = ops.spmm(val, idx, M, K, n, m, g, x, bias=bias, algo=a, residual=res)
+    assert rel_fro(np_of(y3), pre + np_of(res).astype(np.float64)) <= tol
+    # feature-major output with a feature-major residual (the staged epilogue)
+    c = ops.spmm(val, idx, M, K, n, m, g, x, bias=bias, algo=a, layout=nat.NMG_ACT_TOKEN_MAJOR_OUT_ROWS, activation="gelu",
+                 residual=res.t().contiguous())
+    assert rel_fro(np_of(c), (gelu + np_of(res).astype(np.float64)).T) <= tol
+    assert ops.read_status() == 0
