@@ -12,6 +12,7 @@ from .dispatch import (  # noqa: F401  (names with a leading capital are covered
 )
 from .grouped_nm_tensor import GroupedNMTensor, PerfectNMTensor
 from .nmg_impls import GroupedNMSparsifier, WeightLayoutSparsifier
+from .fusion import fuse_linear_epilogues, sparse_linear_fused
 from .patches import patch, patch_ddp, sparse_ddp_all_reduce_hook
 
 __version__ = "0.1.0"

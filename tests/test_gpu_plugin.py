@@ -195,3 +195,47 @@ def test_weight_gradient_in_the_weight_layout_and_clone_layout():
     cl = t3.clone_layout(other)
     mask3 = t3.to_dense() != 0
     assert torch.equal(cl.to_dense(), torch.where(mask3, other, torch.zeros_like(other)))
+
+
+def test_fused_epilogues_in_a_small_bert_encoder():
+    """fuse_linear_epilogues: dense+GELU and dense+residual+LayerNorm modules of a 2-layer BERT-shaped encoder with grouped
+    n:m weights run through nmg_spmm_fused; the output equals the unfused sparse model's up to fp16 rounding, and the
+    densified model's within the 16-bit tolerance."""
+    import copy
+    transformers = pytest.importorskip("transformers")
+    import sten_b200 as sten
+    sten.set_dispatch_failure("raise")
+    dev = cuda()
+    cfg = transformers.BertConfig(hidden_size=128, num_hidden_layers=2, num_attention_heads=4, intermediate_size=512,
+                                  vocab_size=1000, max_position_embeddings=128)
+    torch.manual_seed(0)
+    model = transformers.BertModel(cfg, add_pooling_layer=False).half().to(dev).eval()
+    names = [n + ".weight" for n, mod in model.named_modules() if isinstance(mod, torch.nn.Linear) and "encoder.layer" in n]
+    sb = sten.SparsityBuilder()
+    for w in names:
+        sb.set_weight(name=w, initial_sparsifier=sten.GroupedNMSparsifier(n=2, m=4, g=16), out_format=sten.GroupedNMTensor)
+    sparse = sb.sparsify_model_inplace(copy.deepcopy(model))
+    densified = copy.deepcopy(model)
+    sp = dict(sparse.named_parameters())
+    with torch.no_grad():
+        for name, prm in densified.named_parameters():
+            if name in names:
+                prm.copy_(sp[name].wrapped_tensor.to_dense())
+    ids = torch.randint(0, 1000, (12, 128), generator=torch.Generator().manual_seed(1)).to(dev)  # 1536 tokens: two-pass path
+
+    def fwd(m):
+        with torch.no_grad():
+            return m.encoder(m.embeddings(input_ids=ids), attention_mask=None).last_hidden_state
+
+    plain = fwd(sparse)
+    assert sten.fuse_linear_epilogues(sparse) == 3 * cfg.num_hidden_layers  # attention output, intermediate, output per layer
+    assert sten.fuse_linear_epilogues(sparse) == 0                          # idempotent
+    fused = fwd(sparse)
+    ref = fwd(densified)
+    rel = lambda a, b: float((a.double() - b.double()).norm() / b.double().norm())
+    assert rel(fused, plain) <= 5e-3 and rel(fused, ref) <= 1e-2 and rel(plain, ref) <= 1e-2
+    # with gradients enabled the modules fall back to their own forward (the fused call has no autograd)
+    x = model.embeddings(input_ids=ids).detach().requires_grad_(True)
+    y = sparse.encoder(x, attention_mask=None).last_hidden_state
+    y.float().sum().backward()
+    assert x.grad is not None and bool(torch.isfinite(x.grad.float()).all())
