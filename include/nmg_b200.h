@@ -173,6 +173,19 @@ int nmg_pack_sp24(const void *val, const int16_t *idx, int64_t M, int64_t K, int
 int nmg_spmm_t_sp24(const void *sp24, int64_t M, int64_t K, int n, int m, int g, int dtype, const void *dy, int64_t ld_dy,
                     int64_t tokens, void *dx, int64_t ld_dx, void *stream);
 
+/* Opt-in for compute-bound serving: keep the EXPANDED 16-bit weight across calls.  From 1280 tokens on nmg_spmm expands
+ * the weight into its workspace on every call (about M * K * 2.5 bytes of HBM traffic); a caller that prefers speed over
+ * the format's memory saving expands once (nmg_expand: M * round_up(K, 8) * 2 bytes) and calls nmg_spmm_expanded, which
+ * runs the tensor-core matmul and the fused epilogue of nmg_spmm_fused alone.  The counterpart of the kernel-choice knob
+ * of GroupedNMTensor.set_spmm_opt (src/sten/grouped_nm/grouped_nm_tensor.py:892-902); off unless asked for.
+ * 16-bit dtypes, token-major activations with 16-byte aligned rows; `expanded` 256-byte aligned. */
+size_t nmg_expanded_bytes(int64_t M, int64_t K, int n, int m, int g, int dtype);
+int nmg_expand(const void *val, const int16_t *idx, int64_t M, int64_t K, int n, int m, int g, int dtype, void *expanded,
+               size_t expanded_bytes, void *stream);
+int nmg_spmm_expanded(const void *expanded, int64_t M, int64_t K, int dtype, const void *act, int64_t ld_act, int64_t tokens,
+                      const void *bias, int activation, const void *residual, int64_t ld_res, void *out, int64_t ld_out,
+                      int layout, void *stream);
+
 /* Whether nmg_spmm (transposed = 0) or nmg_spmm_t (transposed = 1) would read the packed copy for this problem under
  * `algo`, assuming aligned operands: 1 or 0.  Lets a host build and keep packed copies only for the weights and batch
  * sizes that use them (the two-pass tensor-core variant and the SIMT forward kernel do not).  `layout` is ignored for

@@ -40,6 +40,9 @@ SIGNATURES = {
     "nmg_sp24_bytes": (_sz, [_i64, _i64, _int, _int, _int, _int]),
     "nmg_pack_sp24": (_int, [_vp, _vp, _i64, _i64, _int, _int, _int, _int, _vp, _sz, _vp]),
     "nmg_spmm_t_sp24": (_int, [_vp, _i64, _i64, _int, _int, _int, _int, _vp, _i64, _i64, _vp, _i64, _vp]),
+    "nmg_expanded_bytes": (_sz, [_i64, _i64, _int, _int, _int, _int]),
+    "nmg_expand": (_int, [_vp, _vp, _i64, _i64, _int, _int, _int, _int, _vp, _sz, _vp]),
+    "nmg_spmm_expanded": (_int, [_vp, _i64, _i64, _int, _vp, _i64, _i64, _vp, _int, _vp, _i64, _vp, _i64, _int, _vp]),
     "nmg_spmm_uses_packed": (_int, [_i64, _i64, _i64, _int, _int, _int, _int, _int, _int, _int]),
     "nmg_spmm_replicated_workspace_bytes": (_sz, [_i64, _i64, _i64, _int, _int, _int, _int]),
     "nmg_spmm_replicated": (_int, [_vp, _vp, _i64, _i64, _int, _int, _int, _int, _vp, _i64, _i64, _vp, _vp, _int, _vp, _i64, _vp, _sz, _vp]),

@@ -266,3 +266,51 @@ extern "C" int nmg_spmm_t_sp24(const void *sp24, int64_t M, int64_t K, int n, in
     if (rc == NMG_OK && pe.stop) NMG_CUDA(cudaEventRecord(pe.stop, st));
     return rc;
 }
+
+// ---- expanded weight kept by the caller (opt-in) ----------------------------------------------------------------------
+extern "C" size_t nmg_expanded_bytes(int64_t M, int64_t K, int n, int m, int g, int dtype) {
+    Geo geo;
+    if (make_geo(M, K, n, m, g, &geo) || (dtype != NMG_F16 && dtype != NMG_BF16) || !tc_dense_supported(geo, dtype)) return 0;
+    return tc_dense_workspace_bytes(geo, dtype, false);
+}
+
+extern "C" int nmg_expand(const void *val, const int16_t *idx, int64_t M, int64_t K, int n, int m, int g, int dtype, void *expanded,
+                          size_t expanded_bytes, void *stream) {
+    Geo geo;
+    int rc = make_geo(M, K, n, m, g, &geo);
+    if (rc) return rc;
+    if ((rc = check_common(dtype, 1, val, idx, expanded, expanded))) return rc;
+    if (dtype == NMG_F32 || !tc_dense_supported(geo, dtype)) NMG_FAIL(NMG_ERR_UNSUPPORTED, "the expanded copy exists for 16-bit weights whose chunk fits shared memory");
+    if (expanded_bytes < tc_dense_workspace_bytes(geo, dtype, false) || (reinterpret_cast<uintptr_t>(expanded) & 255))
+        NMG_FAIL(NMG_ERR_WORKSPACE, "the expanded copy needs %zu bytes, 256-byte aligned", tc_dense_workspace_bytes(geo, dtype, false));
+    return tc_dense_expand(geo, dtype, false, val, idx, static_cast<char *>(expanded), (cudaStream_t)stream);
+}
+
+extern "C" int nmg_spmm_expanded(const void *expanded, int64_t M, int64_t K, int dtype, const void *act, int64_t ld_act, int64_t tokens,
+                                 const void *bias, int activation, const void *residual, int64_t ld_res, void *out, int64_t ld_out,
+                                 int layout, void *stream) {
+    int rc;
+    if ((rc = check_common(dtype, tokens, expanded, expanded, act, out))) return rc;
+    if (dtype == NMG_F32) NMG_FAIL(NMG_ERR_UNSUPPORTED, "the expanded copy exists for 16-bit weights");
+    if (M < 1 || K < 1) NMG_FAIL(NMG_ERR_INVALID, "weight shape must be positive");
+    if (layout != NMG_ACT_TOKEN_MAJOR && layout != NMG_ACT_TOKEN_MAJOR_OUT_ROWS) NMG_FAIL(NMG_ERR_UNSUPPORTED, "token-major activations only");
+    if (activation != NMG_EPI_NONE && activation != NMG_EPI_GELU) NMG_FAIL(NMG_ERR_INVALID, "unknown activation %d", activation);
+    const bool out_tm = layout == NMG_ACT_TOKEN_MAJOR;
+    if (ld_act < K || ld_out < (out_tm ? M : tokens) || (residual && ld_res < (out_tm ? M : tokens))) NMG_FAIL(NMG_ERR_INVALID, "leading dimension smaller than the row");
+    if ((reinterpret_cast<uintptr_t>(expanded) & 255) || (reinterpret_cast<uintptr_t>(act) & 15) || (ld_act % 8))
+        NMG_FAIL(NMG_ERR_UNSUPPORTED, "the expanded copy must be 256-byte aligned and the activation rows 16-byte aligned");
+    const bool pair = M > 128;
+    CUtensorMap tm[3];
+    if ((rc = encode_tmap_2d(&tm[0], dtype, act, (uint64_t)K, (uint64_t)tokens, (uint64_t)ld_act, 64, pair ? 128 : 256, 1))) return rc;
+    tm[1] = tm[0];
+    tm[2] = tm[0];
+    Epilogue epi;
+    epi.act = activation; epi.residual = residual; epi.ld_res = ld_res;
+    void *outs[1] = {out};
+    cudaStream_t st = (cudaStream_t)stream;
+    const ProfileEvents pe = take_profile_events();
+    if (pe.start) NMG_CUDA(cudaEventRecord(pe.start, st));
+    rc = tc_dense_gemm(M, K, dtype, pair, static_cast<const char *>(expanded), tm, tokens, bias, outs, 1, nullptr, ld_out, out_tm ? 1 : 0, st, epi);
+    if (rc == NMG_OK && pe.stop) NMG_CUDA(cudaEventRecord(pe.stop, st));
+    return rc;
+}

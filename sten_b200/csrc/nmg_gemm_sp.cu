@@ -142,8 +142,11 @@ constexpr int SP_THREADS = 32 * (2 + SP_DRAIN_WARPS);
 constexpr uint32_t SP_TMEM_COLS = 512;
 constexpr uint32_t SP_E_COL = 256;                         // metadata columns: two sets of four, used alternately
 
+constexpr int SP_STAGING_BYTES = SP_DRAIN_WARPS * 2048;  // per drain warp: 32 tokens x 32 features, 16-bit
+
 struct SpGemmParams {
     void *out;            // [tokens][ld_out]
+    int out_vec;          // output rows are 16-byte aligned: transposed in shared memory, 16-byte stores
     int64_t out_feats, red, ntok, ld_out, n_rt;
     int tiles_f, tiles_t; // tiles_f counts 256-feature tiles
     int *status;
@@ -181,7 +184,8 @@ template <typename T>
 __global__ void __launch_bounds__(SP_THREADS, 1) gemm_sp_kernel(const SpGemmParams prm, const __grid_constant__ SpGemmMaps maps) {
     extern __shared__ char smem_raw[];
     char *smem = reinterpret_cast<char *>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
-    char *misc = smem + SP_STAGES * SP_STAGE;
+    char *staging = smem + SP_STAGES * SP_STAGE;
+    char *misc = staging + SP_STAGING_BYTES;
     uint64_t *full = reinterpret_cast<uint64_t *>(misc);     // meaningful in the leader only
     uint64_t *empty = full + SP_STAGES;
     uint64_t *acc_full = empty + SP_STAGES;
@@ -293,6 +297,36 @@ __global__ void __launch_bounds__(SP_THREADS, 1) gemm_sp_kernel(const SpGemmPara
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive_remote(acc_free_leader);
+            if (prm.out_vec) {
+                // TMEM hands every lane one feature and 32 tokens per slice; the token-major output wants neighbouring
+                // lanes on neighbouring features.  Transpose the slice in shared memory and store 16 bytes per lane.
+                char *stage_w = staging + (warp - 2) * 2048;
+                T *st = reinterpret_cast<T *>(stage_w);
+                const int64_t fbase = (int64_t)tile_f * SP_PAIR_FEATS + (int64_t)rank * TC_BM + q * 32 + (lane & 3) * 8;
+#pragma unroll
+                for (int s = 0; s < SLICES; s++) {
+                    const int64_t tokc = (int64_t)tok0 + (sl0 + s) * 32;
+                    if (tokc >= prm.ntok) break;  // warp-uniform
+#pragma unroll
+                    for (int j = 0; j < 32; j++) st[j * 32 + lane] = DT<T>::from_f32(__uint_as_float(r[s][j]));
+                    __syncwarp();
+#pragma unroll
+                    for (int i = 0; i < 4; i++) {
+                        const int row = i * 8 + (lane >> 2);
+                        const int64_t tok = tokc + row;
+                        if (tok >= prm.ntok || fbase >= prm.out_feats) continue;
+                        const uint4 w = *reinterpret_cast<const uint4 *>(stage_w + row * 64 + (lane & 3) * 16);
+                        T *dst = out + tok * prm.ld_out + fbase;
+                        if (fbase + 8 <= prm.out_feats) *reinterpret_cast<uint4 *>(dst) = w;
+                        else {
+                            const T *e = reinterpret_cast<const T *>(&w);
+                            for (int k = 0; k < 8 && fbase + k < prm.out_feats; k++) dst[k] = e[k];
+                        }
+                    }
+                    __syncwarp();
+                }
+                continue;
+            }
             if (feat >= prm.out_feats) continue;
 #pragma unroll
             for (int s = 0; s < SLICES; s++) {
@@ -356,7 +390,7 @@ template <typename T, int N_> static int sp_expand_launch(const SpExpandParams &
 }
 
 template <typename T> static int sp_gemm_launch(const SpGemmParams &p, const SpGemmMaps &maps, cudaStream_t st) {
-    const size_t smem = (size_t)SP_STAGES * SP_STAGE + 256 + 1024;
+    const size_t smem = (size_t)SP_STAGES * SP_STAGE + SP_STAGING_BYTES + 256 + 1024;
     int dev = 0, sms = 148;
     NMG_CUDA(cudaGetDevice(&dev));
     NMG_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
@@ -434,6 +468,7 @@ int tc_sp_matmul_t(const Geo &geo, int dtype, const void *sp_copy, const void *d
     if ((rc = get_status_word(&status))) return rc;
     SpGemmParams gp{};
     gp.out = dx;
+    gp.out_vec = ((ld_dx * 2) % 16 == 0 && (reinterpret_cast<uintptr_t>(dx) & 15) == 0) ? 1 : 0;
     gp.out_feats = geo.K; gp.red = geo.M; gp.ntok = tokens; gp.ld_out = ld_dx; gp.n_rt = lay.n_rt;
     gp.tiles_f = (int)(lay.n_ft / 2);
     gp.tiles_t = (int)((tokens + TC_BN - 1) / TC_BN);

@@ -167,6 +167,7 @@ struct GemmParams {
     int64_t out_feats, red, ntok, ld_out;
     int out_token_major;
     int out_staged;    // feature-major output whose rows are 16-byte aligned: go through the staging tile
+    int out_tm_vec;    // token-major output (and residual) whose rows are 16-byte aligned: transposed in the staging tile, 16-byte stores
     int tiles_f, tiles_t;  // tiles_f counts tiles of 128 features (one CTA per tile) or 256 (CTA pairs)
     int *status;
 };
@@ -177,7 +178,17 @@ struct GemmMaps {
     CUtensorMap b[3];  // activation planes, box 64 x 256 (64 x 128 for CTA pairs)
 };
 
-__device__ __forceinline__ float gelu_erf(float v) { return 0.5f * v * (1.f + erff(v * 0.70710678118654752f)); }
+// Exact (erf) GELU with a short erf: 1 - (a1 t + ... + a5 t^5) exp(-x^2), t = 1 / (1 + p |x|) (Abramowitz & Stegun 7.1.26,
+// absolute error 1.5e-7, i.e. below fp32 rounding of the result for |v| of order one).  About a dozen instructions
+// against erff's thirty: the drain warps apply it to 128 x 256 values per tile, and with the library erf that takes longer
+// than the tile's MMAs when the reduction is short.
+__device__ __forceinline__ float erf_short(float x) {
+    const float ax = fabsf(x);
+    const float t = __frcp_rn(fmaf(0.3275911f, ax, 1.f));
+    const float poly = fmaf(fmaf(fmaf(fmaf(1.061405429f, t, -1.453152027f), t, 1.421413741f), t, -0.284496736f), t, 0.254829592f) * t;
+    return copysignf(fmaf(-poly, __expf(-ax * ax), 1.f), x);
+}
+__device__ __forceinline__ float gelu_erf(float v) { return 0.5f * v * (1.f + erf_short(v * 0.70710678118654752f)); }
 
 // PAIR = false: one CTA per 128-feature x 256-token tile.
 // PAIR = true (16-bit operands): two CTAs of a cluster share a 256-feature x 256-token tile.  Each loads the weight rows
@@ -382,6 +393,48 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_tc_kernel(const GemmPara
                     }
                     if (sl == sl0 + SLICES - 1) release();
                     const int64_t tokc = (int64_t)tok0 + sl * 32;
+                    if (prm.out_tm_vec) {
+                        // Token-major output through the staging tile.  TMEM hands every lane one feature and 32 tokens;
+                        // out[token][feature] wants neighbouring lanes on neighbouring features, which scalar stores
+                        // give only 2 bytes at a time.  The slice is transposed in shared memory ([token][32 features])
+                        // and leaves -- after the residual, fetched the same way, is added -- in 16-byte pieces.
+                        T *st = reinterpret_cast<T *>(stage_w);
+#pragma unroll
+                        for (int j = 0; j < 32; j++) {
+                            float v = __uint_as_float(r[j]) + bias;
+                            if (gelu) v = gelu_erf(v);
+                            st[j * 32 + lane] = DT<T>::from_f32(v);
+                        }
+                        __syncwarp();
+                        constexpr int CPR = 32 * (int)sizeof(T) / 16;  // 16-byte chunks per staged row: 4 (16-bit) or 8 (fp32)
+                        const int64_t fbase = (int64_t)feat0 + q * 32 + (lane % CPR) * CHUNK_TOK;  // CHUNK_TOK = elements per chunk
+#pragma unroll
+                        for (int i = 0; i < CPR; i++) {
+                            const int row = i * (32 / CPR) + lane / CPR;
+                            const int64_t tok = tokc + row;
+                            if (tok >= prm.ntok || fbase >= prm.out_feats) continue;
+                            uint4 w = *reinterpret_cast<const uint4 *>(stage_w + row * 32 * (int)sizeof(T) + (lane % CPR) * 16);
+                            const bool whole = fbase + CHUNK_TOK <= prm.out_feats;
+                            if (res) {
+                                __align__(16) T a[CHUNK_TOK], b[CHUNK_TOK];
+                                *reinterpret_cast<uint4 *>(a) = w;
+                                if (whole) *reinterpret_cast<uint4 *>(b) = __ldg(reinterpret_cast<const uint4 *>(res + tok * prm.ld_res + fbase));
+                                else
+                                    for (int k = 0; k < CHUNK_TOK; k++) b[k] = fbase + k < prm.out_feats ? res[tok * prm.ld_res + fbase + k] : DT<T>::from_f32(0.f);
+#pragma unroll
+                                for (int k = 0; k < CHUNK_TOK; k++) a[k] = DT<T>::from_f32(DT<T>::to_f32(a[k]) + DT<T>::to_f32(b[k]));
+                                w = *reinterpret_cast<const uint4 *>(a);
+                            }
+                            T *dst = static_cast<T *>(prm.outs[0]) + tok * prm.ld_out + fbase;
+                            if (whole) *reinterpret_cast<uint4 *>(dst) = w;
+                            else {
+                                const T *e = reinterpret_cast<const T *>(&w);
+                                for (int k = 0; k < CHUNK_TOK && fbase + k < prm.out_feats; k++) dst[k] = e[k];
+                            }
+                        }
+                        __syncwarp();  // the staging rows are free for the next slice
+                        return;
+                    }
                     if (!prm.out_staged) {
                         if (tokc >= prm.ntok || !feat_ok) return;
                         if (prm.out_token_major && prm.n_out == 1 && tokc + 32 <= prm.ntok) {
@@ -553,23 +606,14 @@ bool tc_dense_uses_pair(const Geo &geo, int dtype, bool transposed) {
     return dtype != NMG_F32 && (transposed ? geo.K : geo.M) > TC_BM;
 }
 
-// act_maps: tensor maps of the activation planes (128-byte swizzle; box 64 x 128 when tc_dense_uses_pair, else 64 x 256),
-// one for 16-bit data, three for the fp32 split.  ws holds the expanded weight for the duration of the call.
-int tc_dense_matmul(const Geo &geo, int dtype, bool transposed, const void *val, const int16_t *idx, const CUtensorMap *act_maps,
-                    int64_t tokens, const void *bias, void *const *outs, int n_outs, void *mc_out, int64_t ld_out, int out_token_major,
-                    void *ws, size_t ws_bytes, cudaStream_t st, const Epilogue &epi) {
-    if (n_outs < 1 || n_outs > GEMM_MAX_OUTS) NMG_FAIL(NMG_ERR_INVALID, "between 1 and %d output buffers, got %d", GEMM_MAX_OUTS, n_outs);
+// (val, idx) -> dense 16-bit weight (three bf16 planes for fp32) at `dense` (256-byte aligned, tc_dense_workspace_bytes).
+int tc_dense_expand(const Geo &geo, int dtype, bool transposed, const void *val, const int16_t *idx, char *dense, cudaStream_t st) {
     const int64_t rows = transposed ? geo.K : geo.M, red = transposed ? geo.M : geo.K;
-    const size_t need = tc_dense_workspace_bytes(geo, dtype, transposed);
-    if (!ws || ws_bytes < need) NMG_FAIL(NMG_ERR_WORKSPACE, "workspace of %zu bytes required for the expanded weight, got %zu", need, ws_bytes);
-    char *dense = reinterpret_cast<char *>(((uintptr_t)ws + 255) & ~(uintptr_t)255);
     const int64_t ld = dense_ld(red);
-    const int planes = dtype == NMG_F32 ? 3 : 1;
     const size_t es = dtype == NMG_F32 ? 4 : 2;
     int rc;
     PatternTable tab;
     if ((rc = get_pattern_table(geo.n, geo.m, &tab))) return rc;
-
     ExpandParams ep{};
     ep.val = val; ep.idx = idx; ep.order = tab.order; ep.dst = dense;
     ep.ld = ld; ep.plane_elems = rows * ld;
@@ -580,16 +624,25 @@ int tc_dense_matmul(const Geo &geo, int dtype, bool transposed, const void *val,
     const size_t esmem = expand_smem_bytes(geo, es, transposed, ep.R);
     if (esmem > 200 * 1024) NMG_FAIL(NMG_ERR_UNSUPPORTED, "chunk of %d columns does not fit the expansion pass", geo.cc);
     const int64_t items = ((geo.nb + ep.R - 1) / ep.R) * geo.nc;
-    if (dtype == NMG_F16) rc = transposed ? expand_launch<__half, true>(ep, esmem, items, st) : expand_launch<__half, false>(ep, esmem, items, st);
-    else if (dtype == NMG_BF16) rc = transposed ? expand_launch<__nv_bfloat16, true>(ep, esmem, items, st) : expand_launch<__nv_bfloat16, false>(ep, esmem, items, st);
-    else rc = transposed ? expand_launch<float, true>(ep, esmem, items, st) : expand_launch<float, false>(ep, esmem, items, st);
-    if (rc) return rc;
+    if (dtype == NMG_F16) return transposed ? expand_launch<__half, true>(ep, esmem, items, st) : expand_launch<__half, false>(ep, esmem, items, st);
+    if (dtype == NMG_BF16) return transposed ? expand_launch<__nv_bfloat16, true>(ep, esmem, items, st) : expand_launch<__nv_bfloat16, false>(ep, esmem, items, st);
+    return transposed ? expand_launch<float, true>(ep, esmem, items, st) : expand_launch<float, false>(ep, esmem, items, st);
+}
 
+// out = dense[rows][round_up(red, 8)] (16-bit, or three bf16 planes for fp32) x activations.  act_maps: tensor maps of the
+// activation planes (128-byte swizzle; box 64 x 128 when `pair`, else 64 x 256), one for 16-bit data, three for the fp32 split.
+int tc_dense_gemm(int64_t rows, int64_t red, int dtype, bool pair, const char *dense, const CUtensorMap *act_maps, int64_t tokens,
+                  const void *bias, void *const *outs, int n_outs, void *mc_out, int64_t ld_out, int out_token_major, cudaStream_t st,
+                  const Epilogue &epi) {
+    if (n_outs < 1 || n_outs > GEMM_MAX_OUTS) NMG_FAIL(NMG_ERR_INVALID, "between 1 and %d output buffers, got %d", GEMM_MAX_OUTS, n_outs);
+    const int64_t ld = dense_ld(red);
+    const int planes = dtype == NMG_F32 ? 3 : 1;
+    int rc;
     GemmMaps maps;
     const int edt = dtype == NMG_F32 ? NMG_BF16 : dtype;
     for (int c = 0; c < 3; c++) {
         const int pc = c < planes ? c : 0;
-        if ((rc = encode_tmap_2d(&maps.a[c], edt, dense + (size_t)pc * ep.plane_elems * 2, (uint64_t)red, (uint64_t)rows, (uint64_t)ld, TC_BK, TC_BM, 1))) return rc;
+        if ((rc = encode_tmap_2d(&maps.a[c], edt, dense + (size_t)pc * rows * ld * 2, (uint64_t)red, (uint64_t)rows, (uint64_t)ld, TC_BK, TC_BM, 1))) return rc;
         maps.b[c] = act_maps[c];
     }
     int *status = nullptr;
@@ -607,8 +660,10 @@ int tc_dense_matmul(const Geo &geo, int dtype, bool transposed, const void *val,
     gp.out_feats = rows; gp.red = red; gp.ntok = tokens; gp.ld_out = ld_out;
     gp.out_token_major = out_token_major;
     gp.out_staged = vec ? 1 : 0;
+    gp.out_tm_vec = (out_token_major && n_outs == 1 && (ld_out * osz) % 16 == 0 && (reinterpret_cast<uintptr_t>(outs[0]) & 15) == 0 &&
+                     (!epi.residual || ((epi.ld_res * osz) % 16 == 0 && (reinterpret_cast<uintptr_t>(epi.residual) & 15) == 0)))
+                        ? 1 : 0;
     gp.mc_out = (vec && mc_out && (reinterpret_cast<uintptr_t>(mc_out) & 15) == 0) ? mc_out : nullptr;
-    const bool pair = tc_dense_uses_pair(geo, dtype, transposed);
     const int tile_feats = pair ? 2 * TC_BM : TC_BM;
     gp.tiles_f = (int)((rows + tile_feats - 1) / tile_feats);
     gp.tiles_t = (int)((tokens + TC_BN - 1) / TC_BN);
@@ -617,6 +672,20 @@ int tc_dense_matmul(const Geo &geo, int dtype, bool transposed, const void *val,
     if (dtype == NMG_F32) return gemm_launch<float, false>(gp, maps, st);
     if (dtype == NMG_F16) return pair ? gemm_launch<__half, true>(gp, maps, st) : gemm_launch<__half, false>(gp, maps, st);
     return pair ? gemm_launch<__nv_bfloat16, true>(gp, maps, st) : gemm_launch<__nv_bfloat16, false>(gp, maps, st);
+}
+
+// Two passes: expansion into `ws`, then the matmul on the expanded weight.
+int tc_dense_matmul(const Geo &geo, int dtype, bool transposed, const void *val, const int16_t *idx, const CUtensorMap *act_maps,
+                    int64_t tokens, const void *bias, void *const *outs, int n_outs, void *mc_out, int64_t ld_out, int out_token_major,
+                    void *ws, size_t ws_bytes, cudaStream_t st, const Epilogue &epi) {
+    const int64_t rows = transposed ? geo.K : geo.M, red = transposed ? geo.M : geo.K;
+    const size_t need = tc_dense_workspace_bytes(geo, dtype, transposed);
+    if (!ws || ws_bytes < need) NMG_FAIL(NMG_ERR_WORKSPACE, "workspace of %zu bytes required for the expanded weight, got %zu", need, ws_bytes);
+    char *dense = reinterpret_cast<char *>(((uintptr_t)ws + 255) & ~(uintptr_t)255);
+    int rc;
+    if ((rc = tc_dense_expand(geo, dtype, transposed, val, idx, dense, st))) return rc;
+    return tc_dense_gemm(rows, red, dtype, tc_dense_uses_pair(geo, dtype, transposed), dense, act_maps, tokens, bias, outs, n_outs, mc_out,
+                         ld_out, out_token_major, st, epi);
 }
 
 }  // namespace nmg

@@ -75,6 +75,13 @@ int tc_sp_pack(const Geo &geo, int dtype, const void *val, const int16_t *idx, v
 int tc_sp_matmul_t(const Geo &geo, int dtype, const void *sp_copy, const void *dy, int64_t ld_dy, int64_t tokens, void *dx, int64_t ld_dx,
                    cudaStream_t st);
 
+// The two halves of the two-pass variant on their own: a caller may keep the expanded weight across calls (opt-in: it
+// trades the format's memory saving for skipping the expansion pass of every call).
+int tc_dense_expand(const Geo &geo, int dtype, bool transposed, const void *val, const int16_t *idx, char *dense, cudaStream_t st);
+int tc_dense_gemm(int64_t rows, int64_t red, int dtype, bool pair, const char *dense, const CUtensorMap *act_maps, int64_t tokens,
+                  const void *bias, void *const *outs, int n_outs, void *mc_out, int64_t ld_out, int out_token_major, cudaStream_t st,
+                  const Epilogue &epi);
+
 // ---- specialised forward kernel: parameters, shared-memory plan, per-(n, m) launchers
 struct FwdParams {
     const void *val;

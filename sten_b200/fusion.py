@@ -38,6 +38,11 @@ def sparse_linear_fused(x, gnm, bias=None, activation=None, residual=None):
     x2d = x.reshape(-1, K)
     tokens = x2d.shape[0]
     res2d = residual.reshape(-1, M) if residual is not None else None
+    from .nmg_impls import _wants_expanded
+    if x2d.stride(-1) != 1:
+        x2d = x2d.contiguous()
+    if _wants_expanded(gnm, x2d, tokens):
+        return ops.spmm_expanded(gnm.expanded(), M, K, x2d, bias=bias, activation=activation, residual=res2d).reshape(*x.shape[:-1], M)
     packed = gnm.packed() if tokens and ops.uses_packed(M, K, tokens, n, m, g, gnm.val.dtype, nat.NMG_ACT_TOKEN_MAJOR) else None
     y = ops.spmm(gnm.val, gnm.idx, M, K, n, m, g, x2d, bias=bias, packed=packed, activation=activation, residual=res2d)
     return y.reshape(*x.shape[:-1], M)

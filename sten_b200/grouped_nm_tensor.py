@@ -80,10 +80,13 @@ class GroupedNMTensor:
         return ten
 
     def set_spmm_opt(self, tile_a=None, acc_width=None, tile_b=None, kernel=None):
-        """Kept for API compatibility (reference :892-902 tunes its CPU micro-kernel with these knobs).
+        """The reference tunes its CPU micro-kernel with these knobs (:892-902); the CUDA kernels choose their own tiling,
+        so ``tile_a`` / ``acc_width`` / ``tile_b`` are only recorded (pickles carry the same keys as reference pickles).
 
-        The CUDA kernels choose their own tiling; the values are only recorded so that pickles carry the same
-        keys as reference pickles.  ``kernel`` names the kernel family: ``"sm100"`` here."""
+        ``kernel`` names the kernel family: ``"sm100"`` (default: the weight stays compressed, large batches expand it into
+        a transient workspace on every call) or ``"sm100-expanded"`` (opt-in for compute-bound serving of 16-bit weights:
+        the expanded weight is kept after first use, which skips the per-call expansion pass and gives up the format's
+        memory saving)."""
         self.nm_strides["tile_a"] = tile_a or 3
         self.nm_strides["acc_width"] = acc_width or 4
         self.nm_strides["tile_b"] = tile_b or 16
@@ -130,6 +133,20 @@ class GroupedNMTensor:
             M, K = s["dense_shape"]
             cache = (key, ops.pack(self.val, self.idx, int(M), int(K), s["n"], s["m"], s["group_size"]))
             self.__dict__["_packed_cache"] = cache
+        return cache[1]
+
+    def expanded(self):
+        """Kept dense 16-bit copy for ``kernel="sm100-expanded"`` (``nmg_expand``), or None when there is none (fp32,
+        weights that are not 2-D with n:m blocks along dim 0).  Cached like ``packed()``; never pickled."""
+        s = self.nm_strides
+        if len(s["dense_shape"]) != 2 or s["sparse_dim"] != 0 or not self.val.is_cuda or self.val.dtype == torch.float32:
+            return None
+        key = (self.val.data_ptr(), self.val._version, self.idx.data_ptr(), self.idx._version, self.val.dtype)
+        cache = self.__dict__.get("_expanded_cache")
+        if cache is None or cache[0] != key:
+            M, K = (int(v) for v in s["dense_shape"])
+            cache = (key, ops.expand(self.val, self.idx, M, K, s["n"], s["m"], s["group_size"]))
+            self.__dict__["_expanded_cache"] = cache
         return cache[1]
 
     def packed_sp24(self):

@@ -81,10 +81,20 @@ def _sp24_or_none(gnm, tokens):
     return gnm.packed_sp24() if tokens >= ops.SP24_MIN_TOKENS else None
 
 
+def _wants_expanded(gnm, x2d, tokens, layout=nat.NMG_ACT_TOKEN_MAJOR):
+    """The opt-in of ``set_spmm_opt(kernel="sm100-expanded")`` applies: 16-bit weight, token-major activation whose rows TMA
+    can read, and a batch large enough for the two-pass regime (fewer tokens stay on the compressed-weight kernel)."""
+    return (gnm.nm_strides.get("kernel") == "sm100-expanded" and layout == nat.NMG_ACT_TOKEN_MAJOR and tokens >= ops.SP24_MIN_TOKENS
+            and gnm.val.dtype != torch.float32 and x2d.stride(-1) == 1 and x2d.data_ptr() % 16 == 0 and x2d.stride(0) % 8 == 0
+            and gnm.expanded() is not None)
+
+
 def sparse_dense_mul_dispatch(weight, dense2d, bias, layout):
     """One C-ABI call; replaces the compile-or-load + ctypes call of the reference (sten_impls.py:44-140)."""
     gnm, M, K, n, m, g = _weight_geometry(weight)
     tokens = dense2d.shape[1] if layout == nat.NMG_ACT_K_MAJOR else dense2d.shape[0]
+    if _wants_expanded(gnm, dense2d, tokens, layout):
+        return ops.spmm_expanded(gnm.expanded(), M, K, dense2d, bias=bias)
     packed = _packed_or_none(gnm, (M, K, n, m, g), tokens, layout) if tokens else None
     return ops.spmm(gnm.val, gnm.idx, M, K, n, m, g, dense2d, bias=bias, layout=layout, packed=packed)
 

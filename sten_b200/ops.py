@@ -256,6 +256,42 @@ def spmm(val, idx, M, K, n, m, g, act, bias=None, layout=nat.NMG_ACT_TOKEN_MAJOR
     return out
 
 
+def expand(val, idx, M, K, n, m, g):
+    """Dense 16-bit copy of a weight for ``spmm_expanded`` (opaque uint8 buffer); None when the weight has none (fp32)."""
+    dev = _require_cuda(val, idx)
+    code = _dtype_code(val)
+    nbytes = nat.lib().nmg_expanded_bytes(M, K, n, m, g, code)
+    if nbytes == 0:
+        return None
+    val, idx = val.contiguous(), idx.contiguous()
+    buf = torch.empty(nbytes, dtype=torch.uint8, device=dev)
+    with torch.cuda.device(dev):
+        nat.check(nat.lib().nmg_expand(val.data_ptr(), idx.data_ptr(), M, K, n, m, g, code, buf.data_ptr(), nbytes, _stream(dev)))
+    return buf
+
+
+def spmm_expanded(expanded, M, K, act, bias=None, activation=None, residual=None, out=None):
+    """act [tokens, K] -> out [tokens, M] = activation(act @ W^T + bias) + residual from a kept expanded weight."""
+    dev = _require_cuda(expanded, act, bias, residual)
+    code = _dtype_code(act)
+    act, ld_act = _row_major_2d(act)
+    tokens = act.shape[0]
+    if out is None:
+        out = torch.empty((tokens, M), dtype=act.dtype, device=dev)
+    if tokens == 0:
+        return out
+    if residual is not None and (tuple(residual.shape) != (tokens, M) or residual.stride(1) != 1 or residual.dtype != act.dtype):
+        raise ValueError("residual must match the output's shape and dtype, with contiguous rows")
+    with _on_device(dev):
+        nat.check(nat.lib().nmg_spmm_expanded(expanded.data_ptr(), M, K, code, act.data_ptr(), ld_act, tokens,
+                                              bias.contiguous().data_ptr() if bias is not None else None,
+                                              nat.NMG_EPI_GELU if activation == "gelu" else nat.NMG_EPI_NONE,
+                                              residual.data_ptr() if residual is not None else None,
+                                              residual.stride(0) if residual is not None and tokens > 1 else M,
+                                              out.data_ptr(), out.stride(0) if tokens > 1 else M, nat.NMG_ACT_TOKEN_MAJOR, _stream(dev)))
+    return out
+
+
 def spmm_replicated(val, idx, M, K, n, m, g, act, out_ptrs, ld_out, bias=None, multicast_ptr=None):
     """C = W @ act^T (+ bias per row) written into every buffer of ``out_ptrs`` (device addresses of [M, ld_out] row
     panels: this GPU's and the peers' mapped copies) by the matmul kernel itself.  The caller keeps the buffers alive and

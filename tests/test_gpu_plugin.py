@@ -239,3 +239,37 @@ def test_fused_epilogues_in_a_small_bert_encoder():
     y = sparse.encoder(x, attention_mask=None).last_hidden_state
     y.float().sum().backward()
     assert x.grad is not None and bool(torch.isfinite(x.grad.float()).all())
+
+
+def test_kept_expanded_weight_is_an_opt_in_with_the_same_numbers():
+    """set_spmm_opt(kernel="sm100-expanded"): F.linear of a large batch multiplies the kept expanded weight (no expansion
+    pass); same bits as the default two-pass call, which expands into its workspace first.  Small batches and fp32 weights
+    are unaffected."""
+    import sten_b200 as sten
+    from sten_b200 import ops
+    sten.set_dispatch_failure("raise")
+    dev = cuda()
+    M, K, tokens, n, m, g = 384, 520, 1536, 2, 4, 16
+    torch.manual_seed(3)
+    lin = torch.nn.Linear(K, M, device=dev, dtype=torch.float16)
+    sb = sten.SparsityBuilder()
+    sb.set_weight("weight", initial_sparsifier=sten.GroupedNMSparsifier(n, m, g), out_format=sten.GroupedNMTensor)
+    sparse = sb.get_sparse_model(lin)
+    gnm = sparse.weight.wrapped_tensor
+    x = torch.randn(tokens, K, device=dev, dtype=torch.float16)
+    with torch.no_grad():
+        default = sparse(x)
+        assert gnm.__dict__.get("_expanded_cache") is None
+        gnm.set_spmm_opt(kernel="sm100-expanded")
+        kept = sparse(x)
+        assert gnm.__dict__.get("_expanded_cache") is not None
+        assert torch.equal(kept, default)
+        small = sparse(x[:100])
+    ref = x.double() @ gnm.to_dense().double().t() + sparse.bias.double()
+    assert float((kept.double() - ref).norm() / ref.norm()) <= 1e-2
+    assert float((small.double() - ref[:100]).norm() / ref[:100].norm()) <= 1e-2
+    res = torch.randn(tokens, M, device=dev, dtype=torch.float16)
+    fused = sten.sparse_linear_fused(x, gnm, sparse.bias, activation="gelu", residual=res)
+    want = torch.nn.functional.gelu(ref) + res.double()
+    assert float((fused.double() - want).norm() / want.norm()) <= 1e-2
+    assert set(gnm.__getstate__()) == {"val", "idx", "nm_strides"} and ops.read_status() == 0
