@@ -62,6 +62,12 @@ static int resolve_packed(const Geo &geo, int dtype, const void *val, const int1
     return launch_build_natural(geo, dtype, val, idx, reinterpret_cast<uint16_t *>(base), base + pat_bytes, st);
 }
 
+// K-major activations (B[K][tokens], the torch.mm orientation) reach the tensor cores through one same-dtype transpose
+// into the workspace: X[tokens][round_up(K, 8)], after which the call is the token-major one with row-major output.
+static size_t kmajor_transpose_bytes(const Geo &geo, int dtype, int64_t tokens) {
+    return (size_t)tokens * (size_t)round_up(geo.K, 8) * dtype_size(dtype) + 512;
+}
+
 extern "C" size_t nmg_spmm_workspace_bytes(int64_t M, int64_t K, int64_t tokens, int n, int m, int g, int dtype,
                                            int layout, int algo, int have_packed) {
     Geo geo;
@@ -69,11 +75,11 @@ extern "C" size_t nmg_spmm_workspace_bytes(int64_t M, int64_t K, int64_t tokens,
     size_t simt = simt_fwd_workspace_bytes(geo, tokens, dtype, layout);
     size_t tensor = 0;
     if (algo == NMG_ALGO_TENSOR_DENSE) algo = NMG_ALGO_TENSOR;
-    if (algo != NMG_ALGO_SIMT && (tc_supported(geo, dtype) || tc_dense_supported(geo, dtype)) && layout != NMG_ACT_K_MAJOR)
+    if (algo != NMG_ALGO_SIMT && (tc_supported(geo, dtype) || tc_dense_supported(geo, dtype)))
         tensor = (tc_use_dense(geo, dtype, tokens) ? tc_dense_workspace_bytes(geo, dtype, false)
                                                    : (have_packed ? 0 : natural_bytes(geo, dtype, nullptr) + 512) +
                                                          tc_ksplit_workspace_bytes(geo, dtype, false, tokens)) +
-                 tc_split_workspace_bytes(geo, dtype, false, tokens);
+                 tc_split_workspace_bytes(geo, dtype, false, tokens) + (layout == NMG_ACT_K_MAJOR ? kmajor_transpose_bytes(geo, dtype, tokens) : 0);
     if (algo == NMG_ALGO_TENSOR) return tensor;
     return simt > tensor ? simt : tensor;  // AUTO may take either path depending on operand alignment
 }
@@ -98,9 +104,23 @@ static int spmm_impl(const void *val, const int16_t *idx, const void *packed, in
         NMG_FAIL(NMG_ERR_INVALID, "unknown algo %d", algo);
     if (algo == NMG_ALGO_TENSOR_DENSE) algo = NMG_ALGO_TENSOR;  // the forward product has no structured-sparse variant
     cudaStream_t st = (cudaStream_t)stream;
+    // K-major activations take the tensor cores when the weight is large enough to pay for the transpose pre-pass
+    const bool kmajor_tensor = !tm && n_outs == 1 && (tc_supported(geo, dtype) || tc_dense_supported(geo, dtype)) &&
+                               (algo == NMG_ALGO_TENSOR || (algo == NMG_ALGO_AUTO && M >= 64 && tokens >= 64));
+    if (kmajor_tensor) {
+        const size_t need = kmajor_transpose_bytes(geo, dtype, tokens);
+        if (!workspace || workspace_bytes < need) NMG_FAIL(NMG_ERR_WORKSPACE, "workspace of %zu bytes required for the transposed activation, got %zu", need, workspace_bytes);
+        char *xt = align256(workspace);
+        const int64_t ld_xt = round_up(K, 8);
+        if ((rc = launch_transpose(act, dtype, K, tokens, ld_act, xt, ld_xt, st))) return rc;
+        char *rest = xt + (size_t)tokens * ld_xt * dtype_size(dtype);
+        const size_t used = (size_t)(rest - static_cast<char *>(workspace));
+        return spmm_impl(val, idx, packed, M, K, n, m, g, dtype, xt, ld_xt, tokens, bias, outs, n_outs, ld_out, NMG_ACT_TOKEN_MAJOR_OUT_ROWS,
+                         NMG_ALGO_TENSOR, rest, workspace_bytes - used, stream, force_dense, mc_out, epi);
+    }
     const bool can_tensor = tm && tensor_ok(geo, dtype, act, ld_act);
     if (algo == NMG_ALGO_TENSOR && !can_tensor)
-        NMG_FAIL(NMG_ERR_UNSUPPORTED, "tensor-core path needs token-major activations whose rows are 16-byte aligned (16-bit dtypes) and a chunk that fits shared memory");
+        NMG_FAIL(NMG_ERR_UNSUPPORTED, "tensor-core path needs activation rows that are 16-byte aligned (16-bit dtypes) and a chunk that fits shared memory");
     // AUTO: tensor cores whenever the operands allow it and the weight has at least 64 rows, at every token count (measured
     // at 16 tokens on a 4096^2 bf16 weight: 0.05 ms against 0.71 ms on the SIMT kernel, which is built for wide token
     // tiles); unsupported layouts / alignments and tiny weights stay on the SIMT kernels.  fp32 on tensor cores means exact bf16 splitting with
@@ -168,7 +188,7 @@ extern "C" int nmg_spmm_uses_packed(int64_t M, int64_t K, int64_t tokens, int n,
     if (make_geo(M, K, n, m, g, &geo) || tokens < 1 || n < 1) return 0;
     const bool any_tc = tc_supported(geo, dtype) || tc_dense_supported(geo, dtype);
     const bool wants = algo == NMG_ALGO_TENSOR || algo == NMG_ALGO_TENSOR_DENSE || (algo == NMG_ALGO_AUTO && (transposed ? K : M) >= 64);
-    const bool tensor = any_tc && wants && (transposed || layout != NMG_ACT_K_MAJOR);
+    const bool tensor = any_tc && wants && (transposed || layout != NMG_ACT_K_MAJOR || tokens >= 64 || algo == NMG_ALGO_TENSOR);
     if (tensor) return tc_use_dense(geo, dtype, tokens) ? 0 : 1;
     return transposed ? 1 : 0;  // SIMT: the transposed kernel reads the packed copy, the forward kernel val / idx
 }

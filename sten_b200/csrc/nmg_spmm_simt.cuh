@@ -9,6 +9,8 @@ inline int64_t round_up(int64_t a, int64_t b) { return (a + b - 1) / b * b; }
 // Activation re-layout pre-pass: src[rows][ld_src] (dtype) -> dst[cols][ld_dst] fp32, i.e. transpose + widen.
 int launch_transpose_to_f32(const void *src, int dtype, int64_t rows, int64_t cols, int64_t ld_src, float *dst,
                             int64_t ld_dst, cudaStream_t st);
+// Same-dtype transpose: src[rows][ld_src] -> dst[cols][ld_dst]; columns of dst beyond `rows` (up to ld_dst) are zeroed.
+int launch_transpose(const void *src, int dtype, int64_t rows, int64_t cols, int64_t ld_src, void *dst, int64_t ld_dst, cudaStream_t st);
 // Copy + widen without transposing: src[rows][ld_src] (dtype) -> dst[rows][ld_dst] fp32.
 int launch_widen_to_f32(const void *src, int dtype, int64_t rows, int64_t cols, int64_t ld_src, float *dst,
                         int64_t ld_dst, cudaStream_t st);

@@ -82,7 +82,10 @@ def test_kernel_choice_queries_are_pure_host_arithmetic():
     assert L.nmg_spmm_uses_packed(4096, 4096, 2048, 2, 4, 16, BF, TM, AUTO, 0) == 0
     # SIMT forward reads val / idx; SIMT transposed reads the packed copy
     assert L.nmg_spmm_uses_packed(4096, 4096, 256, 2, 4, 16, BF, TM, SIMT, 0) == 0
-    assert L.nmg_spmm_uses_packed(4096, 4096, 256, 2, 4, 16, BF, KM, AUTO, 0) == 0
+    # K-major activations (torch.mm) are transposed into the workspace and then take the same tensor-core kernels
+    assert L.nmg_spmm_uses_packed(4096, 4096, 256, 2, 4, 16, BF, KM, AUTO, 0) == 1
+    assert L.nmg_spmm_uses_packed(4096, 4096, 8, 2, 4, 16, BF, KM, AUTO, 0) == 0   # a handful of columns stays on the SIMT kernel
+    assert L.nmg_spmm_workspace_bytes(4096, 4096, 4096, 2, 4, 16, BF, KM, TENSOR, 0) >= 2 * 4096 * 4096 * 2
     assert L.nmg_spmm_uses_packed(4096, 4096, 16, 2, 4, 16, F32, TM, AUTO, 1) == 1
     assert L.nmg_spmm_uses_packed(4096, 4096, 4096, 2, 4, 16, F32, TM, AUTO, 1) == 0
     # 3:6 has no fused kernel: the tensor-core path is always the two-pass variant

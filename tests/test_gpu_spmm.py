@@ -332,3 +332,27 @@ def test_fused_activation_and_residual(dtype, tokens, algo):
                  residual=res.t().contiguous())
     assert rel_fro(np_of(c), (gelu + np_of(res).astype(np.float64)).T) <= tol
     assert ops.read_status() == 0
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+@pytest.mark.parametrize("n,m,g,M,K,tokens", [TC_CASES[1], TC_CASES[4], TWO_PASS_CASES[1], TWO_PASS_CASES[7], (2, 4, 16, 2176, 512, 1536)])
+def test_k_major_activations_on_tensor_cores(dtype, n, m, g, M, K, tokens):
+    """C = W B with B[K][tokens] (the torch.mm orientation): one transpose pre-pass, then the token-major tensor-core kernels
+    with row-major output.  Against float64, and the default (AUTO) takes this path."""
+    from sten_b200 import _native as nat, ops
+    tol = TOL_F32 if dtype == torch.float32 else TOL_HALF
+    val, idx, x, dense = _problem(M, K, n, m, g, tokens, 222 + n + m, dtype)
+    b = x.t().contiguous()  # [K, tokens]
+    bias = seeded_normal((M,), 9).to(dtype).to(cuda())
+    c = ops.spmm(val, idx, M, K, n, m, g, b, bias=bias, layout=nat.NMG_ACT_K_MAJOR, algo=nat.NMG_ALGO_TENSOR)
+    ref64 = np_of(dense).astype(np.float64) @ np_of(b).astype(np.float64) + np_of(bias).astype(np.float64)[:, None]
+    assert c.shape == (M, tokens) and rel_fro(np_of(c), ref64) <= tol
+    assert torch.equal(c, ops.spmm(val, idx, M, K, n, m, g, b, bias=bias, layout=nat.NMG_ACT_K_MAJOR))
+    # a strided B (column slice of a wider matrix) and the SIMT kernel agree
+    wide = torch.zeros(K, tokens + 24, dtype=dtype, device=cuda())
+    wide[:, 8:8 + tokens] = b
+    c2 = ops.spmm(val, idx, M, K, n, m, g, wide[:, 8:8 + tokens], bias=bias, layout=nat.NMG_ACT_K_MAJOR)
+    assert torch.equal(c2, c)
+    c_simt = ops.spmm(val, idx, M, K, n, m, g, b, bias=bias, layout=nat.NMG_ACT_K_MAJOR, algo=nat.NMG_ALGO_SIMT)
+    assert rel_fro(np_of(c_simt), ref64) <= tol
+    assert ops.read_status() == 0
