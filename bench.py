@@ -575,6 +575,31 @@ def run_ours(args):
                         "unit": "TFLOP/s", "frac": achieved / fma.value if fma.value else None,
                         "peak_source": "fp32 FFMA loop measured in this run (nmg_measure_fma_peak)", "traffic": None,
                         "ms_per_launch": kms, "algorithmic_flops_per_launch": alg}
+        # format conversion of the step's weight (N = 1: the whole 16384^2 bf16 matrix): sparsifier and densifier against the
+        # HBM roofline on their algorithmic bytes (dense read + val / idx written, resp. val / idx read + dense written)
+        convert = None
+        if world == 1 and args.workload == "sharded":
+            def timed_ms(fn, reps=5):
+                fn()
+                torch.cuda.synchronize()
+                a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                a.record()
+                for _ in range(reps):
+                    fn()
+                b.record()
+                torch.cuda.synchronize()
+                return a.elapsed_time(b) / reps
+            wd = check_dense.unsqueeze(0)
+            val_c, idx_c = ops.sparsify(wd, n, m, G)
+            nbytes = wd.numel() * 2 + val_c.numel() * 2 + idx_c.numel() * 2
+            ms_s = timed_ms(lambda: ops.sparsify(wd, n, m, G))
+            ms_d = timed_ms(lambda: ops.densify(val_c, idx_c, 1, rp, K, n, m, G))
+            hbm = peaks["hbm_gbs"]
+            convert = {"weight": f"{rp}x{K} bf16 {n}:{m} g={G}", "algorithmic_bytes": nbytes,
+                       "sparsify": {"ms": ms_s, "gbs": nbytes / ms_s / 1e6, "frac": nbytes / ms_s / 1e6 / hbm},
+                       "densify": {"ms": ms_d, "gbs": nbytes / ms_d / 1e6, "frac": nbytes / ms_d / 1e6 / hbm},
+                       "peak_gbs": hbm, "peak_source": f"{peaks_src} hbm_gbs, of measured"}
+            del val_c, idx_c, wd
         sweep = transposed = None
         if world == 1 and not args.no_sweep:
             if args.workload == "sharded":
@@ -592,7 +617,7 @@ def run_ours(args):
             "dtype": dtype_name, "data": "synthetic", "config": config_dict(args.workload, world, exchange_used if args.workload == "sharded" else "none", rounds if args.workload == "sharded" else 1),
             "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
             "gpu_launches": args.steps * launches_per_step, "clocks": clocks, "roofline": roofline, "cpu_baseline": cpu,
-            "fp32_fma_peak_tflops": fma.value, "sweep": sweep, "transposed": transposed, "check": check, "encoder": encoder,
+            "fp32_fma_peak_tflops": fma.value, "sweep": sweep, "transposed": transposed, "check": check, "encoder": encoder, "convert": convert,
         }
     if world > 1:
         dist.barrier()

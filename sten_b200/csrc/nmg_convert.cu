@@ -237,12 +237,31 @@ __global__ void __launch_bounds__(256) sparsify_kernel(SparsifyParams prm) {
     }
 }
 
+// Shared memory of one warp in the (n, m)-specialised kernel: no copy of the tile (its values are re-read through L1),
+// lists as separate score / column arrays, proposals as column indices.  7.4 KB for a 448-column tile, so that about thirty
+// warps are resident per SM: the selection is a chain of dependent shared-memory accesses, and residency is what hides it.
+struct SparsifyLean { size_t lscore, park, lcol, inbox, state, prop_p, cnt, total; };
+__host__ __device__ inline SparsifyLean sparsify_lean(int cc, int C) {
+    SparsifyLean l;
+    size_t o = 0;
+    l.lscore = o; o += (size_t)cc * 4;   // [C][g] score bits of the kept proposers, descending by (score, column)
+    l.park = o;   o += (size_t)cc * 4;   // [cc] score of the column's current proposal / match
+    l.lcol = o;   o += (size_t)cc * 2;   // [C][g] their columns
+    l.inbox = o;  o += (size_t)cc * 2;   // [cc] this round's proposing columns, grouped by pattern
+    l.state = o;  o += (size_t)cc * 2;   // [cc] pattern the column is held by, -1 = free
+    l.prop_p = o; o += (size_t)cc * 2;   // [cc] pattern proposed to this round, -1 = none
+    o = (o + 3) & ~(size_t)3;
+    l.cnt = o;    o += (size_t)C * 4 * 3;
+    l.total = (o + 15) & ~(size_t)15;
+    return l;
+}
+
 // Specialisation on (n, m): the pattern table is a compile-time constant, so a column's |w| values sit in registers and
 // all C scores are straight-line adds; which patterns are full is one bit mask (C <= 32), so the first round -- where
 // nothing is full -- touches no shared state at all.  The first round's proposals are placed by rank (every proposal
 // counts the larger proposals of its own pattern, all lanes busy) instead of by one lane per pattern inserting in turn.
 template <int N_, int M_, typename T>
-__global__ void __launch_bounds__(256) sparsify_nm_kernel(SparsifyParams prm) {
+__global__ void __launch_bounds__(256, 4) sparsify_nm_kernel(SparsifyParams prm) {
     extern __shared__ __align__(16) char smem[];
     constexpr Order<N_, M_> ORD{};
     constexpr int C = Order<N_, M_>::C;
@@ -257,14 +276,13 @@ __global__ void __launch_bounds__(256) sparsify_nm_kernel(SparsifyParams prm) {
     __syncthreads();
 
     char *slab = smem + ord_bytes + (size_t)warp * prm.slab_bytes;
-    const SparsifySlab lay = sparsify_slab(M_, cc, C, sizeof(T));
-    uint64_t *list = reinterpret_cast<uint64_t *>(slab + lay.list);
-    uint64_t *inbox = reinterpret_cast<uint64_t *>(slab + lay.inbox);
-    T *x = reinterpret_cast<T *>(slab + lay.x);
+    const SparsifyLean lay = sparsify_lean(cc, C);
+    uint32_t *lscore = reinterpret_cast<uint32_t *>(slab + lay.lscore);
     uint32_t *park = reinterpret_cast<uint32_t *>(slab + lay.park);
+    int16_t *lcol = reinterpret_cast<int16_t *>(slab + lay.lcol);
+    int16_t *inbox = reinterpret_cast<int16_t *>(slab + lay.inbox);
     int16_t *state = reinterpret_cast<int16_t *>(slab + lay.state);
     int16_t *prop_p = reinterpret_cast<int16_t *>(slab + lay.prop_p);
-    int16_t *prop_i = reinterpret_cast<int16_t *>(slab + lay.prop_i);
     int *cnt = reinterpret_cast<int *>(slab + lay.cnt);
     int *icnt = cnt + C;
     int *ioff = icnt + C;
@@ -273,29 +291,24 @@ __global__ void __launch_bounds__(256) sparsify_nm_kernel(SparsifyParams prm) {
     T *val = static_cast<T *>(prm.val);
     const bool g_pow2 = (g & (g - 1)) == 0;
     const int g_shift = 31 - __clz(g);
+    // (score, column) order of the format: larger score first, on equal scores the larger column
+    auto above = [](uint32_t s1, int c1, uint32_t s2, int c2) { return s1 > s2 || (s1 == s2 && c1 > c2); };
 
     for (int64_t tile = (int64_t)blockIdx.x * nwarps + warp; tile < prm.tiles; tile += (int64_t)gridDim.x * nwarps) {
         const int64_t mb = tile % prm.nb, kc = (tile / prm.nb) % prm.nc, b = tile / (prm.nb * prm.nc);
         const int64_t row0 = mb * M_, col0 = kc * cc;
-        const T *src = dense + b * prm.batch_stride;
-        const bool full_cols = col0 + cc <= prm.K;
-#pragma unroll
-        for (int r = 0; r < M_; r++) {
-            const bool row_ok = row0 + r < prm.M;
-            const T *srow = src + (row0 + r) * prm.ld + col0;
-            T *xr = x + r * cc;
-            if (row_ok && full_cols && (cc % V) == 0 && (reinterpret_cast<uintptr_t>(srow) & 15) == 0) {
-                for (int c = lane * V; c < cc; c += 32 * V)
-                    *reinterpret_cast<uint4 *>(xr + c) = __ldg(reinterpret_cast<const uint4 *>(srow + c));
-            } else {
-                for (int c = lane; c < cc; c += 32) xr[c] = (row_ok && col0 + c < prm.K) ? srow[c] : DT<T>::from_f32(0.f);
-            }
-        }
+        const T *src = dense + b * prm.batch_stride + row0 * prm.ld + col0;  // element (r, c) of the tile at src[r * ld + c]
+        const int rows_ok = (int)(prm.M - row0 < M_ ? prm.M - row0 : M_);    // rows beyond M and columns beyond K read as zero
+        const int cols_ok = (int)(prm.K - col0 < cc ? prm.K - col0 : cc);
+        auto tile_at = [&](int r, int c) -> T { return (r < rows_ok && c < cols_ok) ? __ldg(src + (int64_t)r * prm.ld + c) : DT<T>::from_f32(0.f); };
+
         for (int c = lane; c < cc; c += 32) state[c] = -1;
         if (lane < C) cnt[lane] = 0;
         uint32_t full_mask = 0;  // bit p: pattern p holds g columns (warp-uniform)
         __syncwarp();
 
+        // Deferred acceptance.  Every round with a proposal makes at least one (column, pattern) proposal that was never
+        // made before, so cc * C rounds cannot be exceeded; real weights settle in a handful.
         for (int round = 0; round < cc * C + 2; round++) {
             if (lane < C) icnt[lane] = 0;
             __syncwarp();
@@ -305,7 +318,7 @@ __global__ void __launch_bounds__(256) sparsify_nm_kernel(SparsifyParams prm) {
                 if (state[c] >= 0) continue;
                 float a[M_];
 #pragma unroll
-                for (int r = 0; r < M_; r++) a[r] = fabsf(DT<T>::to_f32(x[r * cc + c]));
+                for (int r = 0; r < M_; r++) a[r] = fabsf(DT<T>::to_f32(tile_at(r, c)));
                 uint32_t best_s = 0;  // a score of zero never wins: zero scores are placed by the closed form after the rounds
                 int best_p = -1;
                 if (full_mask == 0) {  // first round(s): every pattern is open, nothing but registers
@@ -326,19 +339,20 @@ __global__ void __launch_bounds__(256) sparsify_nm_kernel(SparsifyParams prm) {
                         const uint32_t sb = __float_as_uint(sc);
                         bool open = sb != 0 && sb >= best_s;
                         // full pattern: only a proposer that ranks above its weakest kept one gets in
-                        if (open && ((full_mask >> p) & 1u)) open = sp_key(sb, c) > list[p * g + g - 1];
+                        if (open && ((full_mask >> p) & 1u)) open = above(sb, c, lscore[p * g + g - 1], lcol[p * g + g - 1]);
                         if (open) { best_s = sb; best_p = p; }
                     }
                 }
                 if (best_p < 0) continue;  // nothing above zero is open to this column: it waits for the zero phase
                 proposed = true;
                 prop_p[c] = (int16_t)best_p;
-                prop_i[c] = (int16_t)atomicAdd(&icnt[best_p], 1);
                 park[c] = best_s;
+                atomicAdd(&icnt[best_p], 1);
             }
             if (!__any_sync(0xffffffffu, proposed)) break;
             __syncwarp();
-            {   // exclusive prefix sum over the patterns (one per lane)
+            int total;
+            {   // exclusive prefix sum over the patterns (one per lane) -> start of every pattern's inbox segment
                 const int mine = lane < C ? icnt[lane] : 0;
                 int incl = mine;
 #pragma unroll
@@ -346,43 +360,49 @@ __global__ void __launch_bounds__(256) sparsify_nm_kernel(SparsifyParams prm) {
                     const int t = __shfl_up_sync(0xffffffffu, incl, d);
                     if (lane >= d) incl += t;
                 }
-                if (lane < C) ioff[lane] = incl - mine;
+                if (lane < C) { ioff[lane] = incl - mine; icnt[lane] = 0; }  // icnt becomes the fill cursor of the segment
+                total = __shfl_sync(0xffffffffu, incl, 31);
             }
             __syncwarp();
-            int total = 0;  // proposals of this round (warp-uniform)
-            for (int c = lane; c < cc; c += 32)
-                if (prop_p[c] >= 0) { inbox[ioff[prop_p[c]] + prop_i[c]] = sp_key(park[c], c); total++; }
-#pragma unroll
-            for (int d = 16; d > 0; d >>= 1) total += __shfl_xor_sync(0xffffffffu, total, d);
+            for (int c = lane; c < cc; c += 32) {
+                const int p = prop_p[c];
+                if (p >= 0) inbox[ioff[p] + atomicAdd(&icnt[p], 1)] = (int16_t)c;
+            }
             __syncwarp();
             if (round == 0) {
                 // all lists are empty: a proposal's place is its rank among the proposals of its pattern
                 for (int e = lane; e < total; e += 32) {
-                    const uint64_t key = inbox[e];
-                    const int c = (int)(key & 0xffffu), p = prop_p[c];
+                    const int c = inbox[e], p = prop_p[c];
+                    const uint32_t sc = park[c];
                     const int e0 = ioff[p], e1 = e0 + icnt[p];
                     int rank = 0;
-                    for (int j = e0; j < e1; j++) rank += inbox[j] > key ? 1 : 0;
-                    if (rank < g) { list[p * g + rank] = key; state[c] = (int16_t)p; }
+                    for (int j = e0; j < e1; j++) {
+                        const int c2 = inbox[j];
+                        rank += above(park[c2], c2, sc, c) ? 1 : 0;
+                    }
+                    if (rank < g) { lscore[p * g + rank] = sc; lcol[p * g + rank] = (int16_t)c; state[c] = (int16_t)p; }
                 }
                 if (lane < C) cnt[lane] = min(icnt[lane], g);
             } else if (lane < C) {
                 const int p = lane;
-                uint64_t *lp = list + p * g;
+                uint32_t *ls = lscore + p * g;
+                int16_t *lc = lcol + p * g;
                 int L = cnt[p];
                 const int e0 = ioff[p], e1 = e0 + icnt[p];
                 for (int e = e0; e < e1; e++) {
-                    const uint64_t key = inbox[e];
+                    const int c = inbox[e];
+                    const uint32_t sc = park[c];
                     if (L == g) {
-                        if (key <= lp[g - 1]) continue;
-                        state[(int)(lp[g - 1] & 0xffffu)] = -1;
+                        if (!above(sc, c, ls[g - 1], lc[g - 1])) continue;  // stays free
+                        state[lc[g - 1]] = -1;                                  // the weakest kept proposer is released
                         L = g - 1;
                     }
                     int j = L;
-                    while (j > 0 && lp[j - 1] < key) { lp[j] = lp[j - 1]; j--; }
-                    lp[j] = key;
+                    while (j > 0 && above(sc, c, ls[j - 1], lc[j - 1])) { ls[j] = ls[j - 1]; lc[j] = lc[j - 1]; j--; }
+                    ls[j] = sc;
+                    lc[j] = (int16_t)c;
                     L++;
-                    state[(int)(key & 0xffffu)] = (int16_t)p;
+                    state[c] = (int16_t)p;
                 }
                 cnt[p] = L;
             }
@@ -390,19 +410,40 @@ __global__ void __launch_bounds__(256) sparsify_nm_kernel(SparsifyParams prm) {
             full_mask = __ballot_sync(0xffffffffu, lane < C && cnt[lane] == g);
         }
         __syncwarp();
-        sparsify_zero_phase(lane, cc, C, g, list, state, cnt, icnt, ioff);
+        // zero phase on the split lists: same closed form as sparsify_zero_phase, columns only
+        {
+            const int mine = lane < C ? g - cnt[lane] : 0;  // free places of pattern `lane`
+            int incl = mine;                                 // inclusive suffix sum over lanes
+#pragma unroll
+            for (int d = 1; d < 32; d <<= 1) {
+                const int t = __shfl_down_sync(0xffffffffu, incl, d);
+                if (lane + d < 32) incl += t;
+            }
+            if (lane < C) { icnt[lane] = mine; ioff[lane] = incl - mine; }  // rem[p], cum[p] = free places in larger patterns
+            __syncwarp();
+            int above_cnt = 0;
+            for (int k = (cc - 1) / 32; k >= 0; k--) {
+                const int c = k * 32 + lane;
+                const bool is_free = c < cc && state[c] < 0;
+                const uint32_t mask = __ballot_sync(0xffffffffu, is_free);
+                if (is_free) {
+                    const int i = above_cnt + __popc(lane == 31 ? 0u : (mask >> (lane + 1)));  // free columns with a larger index
+                    int p = C - 1;
+                    while (p > 0 && ioff[p] + icnt[p] <= i) p--;  // largest pattern whose range of places contains i
+                    lcol[p * g + cnt[p] + (i - ioff[p])] = (int16_t)c;
+                    state[c] = (int16_t)p;
+                }
+                above_cnt += __popc(mask);
+            }
+            __syncwarp();
+        }
 
         int16_t *idx_out = prm.idx + tile * cc;
         T *val_out = val + tile * (int64_t)cc * N_;
         if ((cc & 7) == 0 && (reinterpret_cast<uintptr_t>(idx_out) & 15) == 0) {
-            for (int s0 = lane * 8; s0 < cc; s0 += 256) {
-                uint32_t w[4];
-#pragma unroll
-                for (int u = 0; u < 4; u++) w[u] = (uint32_t)(list[s0 + 2 * u] & 0xffffu) | ((uint32_t)(list[s0 + 2 * u + 1] & 0xffffu) << 16);
-                *reinterpret_cast<uint4 *>(idx_out + s0) = make_uint4(w[0], w[1], w[2], w[3]);
-            }
+            for (int s0 = lane * 8; s0 < cc; s0 += 256) *reinterpret_cast<uint4 *>(idx_out + s0) = *reinterpret_cast<const uint4 *>(lcol + s0);
         } else {
-            for (int s0 = lane; s0 < cc; s0 += 32) idx_out[s0] = (int16_t)(list[s0] & 0xffffu);
+            for (int s0 = lane; s0 < cc; s0 += 32) idx_out[s0] = lcol[s0];
         }
         const int nvals = cc * N_;
         if ((nvals % V) == 0 && (reinterpret_cast<uintptr_t>(val_out) & 15) == 0) {
@@ -411,16 +452,16 @@ __global__ void __launch_bounds__(256) sparsify_nm_kernel(SparsifyParams prm) {
 #pragma unroll
                 for (int u = 0; u < V; u++) {
                     const int e = v + u, s0 = e / N_, t = e % N_;
-                    const int c = (int)(list[s0] & 0xffffu), p = g_pow2 ? (s0 >> g_shift) : s0 / g;
-                    out[u] = x[(int)ord[p * N_ + t] * cc + c];
+                    const int c = lcol[s0], p = g_pow2 ? (s0 >> g_shift) : s0 / g;
+                    out[u] = tile_at((int)ord[p * N_ + t], c);
                 }
                 *reinterpret_cast<uint4 *>(val_out + v) = *reinterpret_cast<const uint4 *>(out);
             }
         } else {
             for (int e = lane; e < nvals; e += 32) {
                 const int s0 = e / N_, t = e % N_;
-                const int c = (int)(list[s0] & 0xffffu), p = s0 / g;
-                val_out[e] = x[(int)ord[p * N_ + t] * cc + c];
+                const int c = lcol[s0], p = s0 / g;
+                val_out[e] = tile_at((int)ord[p * N_ + t], c);
             }
         }
         __syncwarp();
@@ -457,16 +498,56 @@ __global__ void __launch_bounds__(128) densify_kernel(DensifyParams prm) {
         const int64_t mb = tile % prm.nb, kc = (tile / prm.nb) % prm.nc, b = tile / (prm.nb * prm.nc);
         __syncthreads();
         for (int c = threadIdx.x; c < cc; c += blockDim.x) pos[c] = -1;
+        constexpr int V = 16 / (int)sizeof(T);  // elements per 16-byte access
         const T *vsrc = val + tile * (int64_t)cc * n;
-        for (int e = threadIdx.x; e < cc * n; e += blockDim.x) sval[e] = vsrc[e];
+        if (((cc * n) % V) == 0 && (reinterpret_cast<uintptr_t>(vsrc) & 15) == 0) {
+            for (int e = threadIdx.x * V; e < cc * n; e += blockDim.x * V)
+                *reinterpret_cast<uint4 *>(sval + e) = __ldg(reinterpret_cast<const uint4 *>(vsrc + e));
+        } else {
+            for (int e = threadIdx.x; e < cc * n; e += blockDim.x) sval[e] = vsrc[e];
+        }
         __syncthreads();
         const int16_t *isrc = prm.idx + tile * cc;
-        for (int s = threadIdx.x; s < cc; s += blockDim.x) {
-            const int c = isrc[s];
-            if (c >= 0 && c < cc) pos[c] = (int16_t)s;  // a malformed index is ignored, never dereferenced
+        if ((cc & 7) == 0 && (reinterpret_cast<uintptr_t>(isrc) & 15) == 0) {
+            for (int s8 = threadIdx.x * 8; s8 < cc; s8 += blockDim.x * 8) {
+                const uint4 iv = __ldg(reinterpret_cast<const uint4 *>(isrc + s8));
+                const int16_t *ci = reinterpret_cast<const int16_t *>(&iv);
+#pragma unroll
+                for (int u = 0; u < 8; u++)
+                    if (ci[u] >= 0 && ci[u] < cc) pos[ci[u]] = (int16_t)(s8 + u);  // a malformed index is ignored, never dereferenced
+            }
+        } else {
+            for (int s = threadIdx.x; s < cc; s += blockDim.x) {
+                const int c = isrc[s];
+                if (c >= 0 && c < cc) pos[c] = (int16_t)s;
+            }
         }
         __syncthreads();
         T *dst = dense + b * prm.batch_stride;
+        const int64_t col0 = kc * cc;
+        // 16-byte stores where the row piece allows it: every thread assembles V consecutive columns of one row
+        const bool vec = (cc % V) == 0 && col0 + cc <= prm.K && (prm.ld % V) == 0 && (reinterpret_cast<uintptr_t>(dst) & 15) == 0;
+        if (vec) {
+            const int per_row = cc / V;
+            for (int v = threadIdx.x; v < m * per_row; v += blockDim.x) {
+                const int r = v / per_row, c0 = (v - r * per_row) * V;
+                const int64_t row = mb * m + r;
+                if (row >= prm.M) continue;
+                __align__(16) T out[V];
+#pragma unroll
+                for (int u = 0; u < V; u++) {
+                    const int sl = pos[c0 + u];
+                    T val_u = DT<T>::from_f32(0.f);
+                    if (sl >= 0) {
+                        const int t = sor[(sl / g) * m + r];
+                        if (t >= 0) val_u = sval[sl * n + t];
+                    }
+                    out[u] = val_u;
+                }
+                *reinterpret_cast<uint4 *>(dst + row * prm.ld + col0 + c0) = *reinterpret_cast<const uint4 *>(out);
+            }
+            continue;
+        }
         for (int r = 0; r < m; r++) {
             const int64_t row = mb * m + r;
             if (row >= prm.M) break;
@@ -558,7 +639,8 @@ extern "C" int nmg_sparsify(const void *dense, int64_t batch, int64_t M, int64_t
     p.M = M; p.K = K; p.ld = ld_dense; p.batch_stride = batch_stride;
     p.nb = geo.nb; p.nc = geo.nc; p.tiles = batch * geo.nb * geo.nc;
     p.n = n; p.m = m; p.g = g; p.C = geo.C; p.cc = geo.cc;
-    const size_t slab = sparsify_slab(m, geo.cc, geo.C, dtype_size(dtype)).total;
+    const bool specialised = (n == 1 && (m == 4 || m == 8 || m == 16)) || (n == 2 && (m == 4 || m == 8));
+    const size_t slab = specialised ? sparsify_lean(geo.cc, geo.C).total : sparsify_slab(m, geo.cc, geo.C, dtype_size(dtype)).total;
     const size_t ord_bytes = ((size_t)geo.C * n + 15) & ~(size_t)15;
     const size_t budget = 200 * 1024;
     if (ord_bytes + slab > budget)

@@ -46,31 +46,41 @@ int launch_transpose_to_f32(const void *src, int dtype, int64_t rows, int64_t co
     return NMG_OK;
 }
 
-// Same-dtype transpose: src[rows][ld_src] -> dst[cols][ld_dst], 32 x 32 tiles through shared memory (both sides coalesced).
+// Same-dtype transpose: src[rows][ld_src] -> dst[cols][ld_dst], 64 x 64 tiles through shared memory.  Both sides move
+// 128 bytes (fp32: 256) per warp instruction: a thread reads two neighbouring elements of a source row and writes two
+// neighbouring elements of a destination row.  Columns of dst beyond `rows` (up to ld_dst) are zero.
 template <typename T>
 __global__ void __launch_bounds__(256) transpose_kernel(const T *__restrict__ src, int64_t rows, int64_t cols, int64_t ld_src,
                                                         T *__restrict__ dst, int64_t ld_dst) {
-    __shared__ T tile[32][33];
-    const int64_t c0 = (int64_t)blockIdx.x * 32, r0 = (int64_t)blockIdx.y * 32;
-    for (int i = threadIdx.y; i < 32; i += 8) {
-        const int64_t r = r0 + i, c = c0 + threadIdx.x;
-        tile[i][threadIdx.x] = (r < rows && c < cols) ? src[r * ld_src + c] : DT<T>::from_f32(0.f);
+    __shared__ T tile[64][66];
+    const int tx = threadIdx.x, ty = threadIdx.y;  // 32 x 8
+    const int64_t c0 = (int64_t)blockIdx.x * 64, r0 = (int64_t)blockIdx.y * 64;
+    for (int i = ty; i < 64; i += 8) {
+        const int64_t r = r0 + i;
+#pragma unroll
+        for (int h = 0; h < 2; h++) {
+            const int64_t c = c0 + 2 * tx + h;
+            tile[i][2 * tx + h] = (r < rows && c < cols) ? src[r * ld_src + c] : DT<T>::from_f32(0.f);
+        }
     }
     __syncthreads();
-    for (int i = threadIdx.y; i < 32; i += 8) {
-        const int64_t c = c0 + i, r = r0 + threadIdx.x;
-        if (c < cols && r < ld_dst) dst[c * ld_dst + r] = r < rows ? tile[threadIdx.x][i] : DT<T>::from_f32(0.f);
+    for (int i = ty; i < 64; i += 8) {
+        const int64_t c = c0 + i;
+        if (c >= cols) continue;
+#pragma unroll
+        for (int h = 0; h < 2; h++) {
+            const int64_t r = r0 + 2 * tx + h;
+            if (r < ld_dst) dst[c * ld_dst + r] = tile[2 * tx + h][i];
+        }
     }
 }
 
 int launch_transpose(const void *src, int dtype, int64_t rows, int64_t cols, int64_t ld_src, void *dst, int64_t ld_dst, cudaStream_t st) {
     dim3 block(32, 8);
-    for (int64_t r0 = 0; r0 < ld_dst; r0 += 65535ll * 32) {  // grid.y limit
-        const int64_t nr = ld_dst - r0 < 65535ll * 32 ? ld_dst - r0 : 65535ll * 32;
-        dim3 grid((unsigned)((cols + 31) / 32), (unsigned)((nr + 31) / 32));
-        NMG_DISPATCH_DTYPE(dtype, T, (transpose_kernel<T><<<grid, block, 0, st>>>(static_cast<const T *>(src) + r0 * ld_src, rows - r0 > 0 ? rows - r0 : 0, cols,
-                                                                                 ld_src, static_cast<T *>(dst) + r0, ld_dst)));
-    }
+    const int64_t gy = (ld_dst + 63) / 64;
+    if (gy > 65535) NMG_FAIL(NMG_ERR_UNSUPPORTED, "reduction axis too long for the transpose pre-pass");
+    dim3 grid((unsigned)((cols + 63) / 64), (unsigned)gy);
+    NMG_DISPATCH_DTYPE(dtype, T, (transpose_kernel<T><<<grid, block, 0, st>>>(static_cast<const T *>(src), rows, cols, ld_src, static_cast<T *>(dst), ld_dst)));
     NMG_CUDA(cudaGetLastError());
     return NMG_OK;
 }
