@@ -164,6 +164,9 @@ struct GemmParams {
     const void *residual;       // added after the activation, same orientation as the output, or NULL
     int64_t ld_res;
     int act;                    // NMG_EPI_NONE / NMG_EPI_GELU applied to (product + bias)
+    int bias_cols;              // bias runs along the accumulator's columns ("tokens" below) instead of its rows
+    int out_tma;                // staged output with one destination: the staging tile leaves as one tiled bulk store per group
+    int res_vec;                // staged output: the residual is read in the same 16-byte pieces as the output is written
     int64_t out_feats, red, ntok, ld_out;
     int out_token_major;
     int out_staged;    // feature-major output whose rows are 16-byte aligned: go through the staging tile
@@ -176,19 +179,22 @@ constexpr int GEMM_STAGING_BYTES = GEMM_DRAIN_WARPS * 4096;  // per drain warp: 
 struct GemmMaps {
     CUtensorMap a[3];  // weight planes, box 64 x 128, 128-byte swizzle
     CUtensorMap b[3];  // activation planes, box 64 x 256 (64 x 128 for CTA pairs)
+    CUtensorMap out;   // out_tma: the output, box 128 bytes x 32 rows, 128-byte swizzle
 };
 
-// Exact (erf) GELU with a short erf: 1 - (a1 t + ... + a5 t^5) exp(-x^2), t = 1 / (1 + p |x|) (Abramowitz & Stegun 7.1.26,
-// absolute error 1.5e-7, i.e. below fp32 rounding of the result for |v| of order one).  About a dozen instructions
-// against erff's thirty: the drain warps apply it to 128 x 256 values per tile, and with the library erf that takes longer
-// than the tile's MMAs when the reduction is short.
-__device__ __forceinline__ float erf_short(float x) {
-    const float ax = fabsf(x);
-    const float t = __fdividef(1.f, fmaf(0.3275911f, ax, 1.f));  // reciprocal approximation: 1 ulp, far below the formula's own error
-    const float poly = fmaf(fmaf(fmaf(fmaf(1.061405429f, t, -1.453152027f), t, 1.421413741f), t, -0.284496736f), t, 0.254829592f) * t;
-    return copysignf(fmaf(-poly, __expf(-ax * ax), 1.f), x);
+// Exact (erf) GELU with a short erf: erf(x) = 1 - (a1 t + ... + a5 t^5) exp(-x^2), t = 1 / (1 + p x) for x >= 0 (Abramowitz &
+// Stegun 7.1.26, absolute error 1.5e-7, i.e. below fp32 rounding of the result for |v| of order one).  With x = |v| / sqrt(2)
+// and v * sign(v) = |v|, gelu(v) = v (1 + erf(v / sqrt 2)) / 2 collapses to max(v, 0) - |v| q(t) 2^(-v^2 log2(e) / 2) where q
+// carries the halved coefficients: fourteen instructions, two of them on the special-function unit (flush-to-zero forms, which
+// need no range fix-up), against the library erf's thirty.  The drain warps apply it to 128 x 256 values per tile.
+__device__ __forceinline__ float gelu_erf(float v) {
+    const float av = fabsf(v);
+    float t, e;
+    asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(t) : "f"(fmaf(0.23164189f, av, 1.f)));   // p / sqrt(2)
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"((v * -0.72134752f) * v));          // log2(e) / 2
+    const float q = fmaf(fmaf(fmaf(fmaf(0.5307027145f, t, -0.7265760135f), t, 0.7107068705f), t, -0.142248368f), t, 0.127414796f) * t;
+    return fmaf(-(av * q), e, fmaxf(v, 0.f));
 }
-__device__ __forceinline__ float gelu_erf(float v) { return 0.5f * v * (1.f + erf_short(v * 0.70710678118654752f)); }
 
 // PAIR = false: one CTA per 128-feature x 256-token tile.
 // PAIR = true (16-bit operands): two CTAs of a cluster share a 256-feature x 256-token tile.  Each loads the weight rows
@@ -197,7 +203,9 @@ __device__ __forceinline__ float gelu_erf(float v) { return 0.5f * v * (1.f + er
 // 48 KB, which is what keeps the tensor core fed from L2.  full[s] lives in the even ("leader") CTA and receives the TMA
 // bytes of both; empty[s] and acc_full[b] exist in both CTAs and are signalled by multicast commits; acc_free[b] lives in
 // the leader and collects the drain warps of both CTAs.  No load is multicast.
-template <typename T, bool PAIR>
+// TMA_OUT = true: the one-destination staged output, leaving as tiled bulk stores; only that output path is compiled,
+// which keeps the drain warps' code and register needs small.  TMA_OUT = false: every other output form.
+template <typename T, bool PAIR, bool TMA_OUT>
 __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_tc_kernel(const GemmParams prm, const __grid_constant__ GemmMaps maps) {
     constexpr int TERMS = TcMode<T>::TERMS;
     using E = typename TcMode<T>::elem;
@@ -343,6 +351,8 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_tc_kernel(const GemmPara
         constexpr int CHUNK_TOK = 16 / (int)sizeof(T);         // tokens per 16-byte chunk
         constexpr int GROUP_TOK = 128 / (int)sizeof(T);        // tokens per staged row: 64 (16-bit) or 32 (fp32)
         constexpr int GROUP_SLICES = GROUP_TOK / 32;           // 32-column TMEM slices per staged group
+        constexpr bool RES_AHEAD = TMA_OUT && sizeof(T) == 2;  // residual fetched one slice ahead (fp32 rows would take 2 x 32 registers)
+        constexpr int RQ = RES_AHEAD ? 4 : 1;                  // 16-byte pieces of one slice row of the residual
         const int q = warp & 3;  // TMEM lane quarter this warp may access
         constexpr int SLICES = (TC_BN / 32) / (GEMM_DRAIN_WARPS / 4);  // 32-column slices per warp
         const int sl0 = ((warp - 2) >> 2) * SLICES;                    // this warp's first slice
@@ -350,14 +360,6 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_tc_kernel(const GemmPara
         char *stage_w = staging + (warp - 2) * 4096;
         const T *res = static_cast<const T *>(prm.residual);
         const bool gelu = prm.act == NMG_EPI_GELU;
-        // value of one output element: activation(product + bias) + residual[off], off = the element's offset in a
-        // tensor of the output's orientation with row pitch ld_res
-        auto finish = [&](uint32_t acc, float bias, int64_t res_off) -> float {
-            float v = __uint_as_float(acc) + bias;
-            if (gelu) v = gelu_erf(v);
-            if (res) v += DT<T>::to_f32(res[res_off]);
-            return v;
-        };
         int unit = 0;
         bool ok = true;
         for (int ti = 0; ti < my_tiles && ok; ti++) {
@@ -365,7 +367,27 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_tc_kernel(const GemmPara
             tile_origin(ti, feat0, tok0);
             const int64_t feat = (int64_t)feat0 + q * 32 + lane;
             const bool feat_ok = feat < prm.out_feats;
-            const float bias = (prm.bias && feat_ok) ? DT<T>::to_f32(static_cast<const T *>(prm.bias)[feat]) : 0.f;
+            const float bias = (prm.bias && !prm.bias_cols && feat_ok) ? DT<T>::to_f32(static_cast<const T *>(prm.bias)[feat]) : 0.f;
+            // column bias: lane l keeps the value of column l of each of this warp's slices; the slice's loop fetches
+            // element j's value from lane j
+            float bcol[SLICES];
+#pragma unroll
+            for (int i = 0; i < SLICES; i++) {
+                const int64_t col = (int64_t)tok0 + (sl0 + i) * 32 + lane;
+                bcol[i] = (prm.bias && prm.bias_cols && col < prm.ntok) ? DT<T>::to_f32(static_cast<const T *>(prm.bias)[col]) : 0.f;
+            }
+            // The residual of a slice (this lane's row, 32 elements) is fetched in 16-byte pieces one slice ahead of its
+            // use, like the accumulator, when the bulk-store path runs and the residual's rows allow it.
+            auto res_vec_ok = [&](int64_t tokc) -> bool { return TMA_OUT && prm.res_vec && tokc + 32 <= prm.ntok; };
+            auto res_fetch = [&](int sl, uint4 (&qr)[RQ]) {
+                if constexpr (RES_AHEAD) {
+                    const int64_t tokc = (int64_t)tok0 + sl * 32;
+                    if (res && feat_ok && res_vec_ok(tokc)) {
+#pragma unroll
+                        for (int v = 0; v < RQ; v++) qr[v] = __ldg(reinterpret_cast<const uint4 *>(res + feat * prm.ld_res + tokc) + v);
+                    }
+                }
+            };
             for (int c = 0; c < nchunks; c++, unit++) {
                 const int b = unit % NBUF, use = unit / NBUF;
                 if (!(ok = wait(&acc_full[b], (uint32_t)(use & 1), 25))) break;
@@ -379,8 +401,9 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_tc_kernel(const GemmPara
                         else mbar_arrive(&acc_free[b]);
                     }
                 };
-                // handle(sl, r): slice sl of the unit is in registers r (this lane's feature row, 32 tokens)
-                auto handle = [&](int sl, uint32_t (&r)[32]) {
+                // handle(sl, r, qr): slice sl of the unit is in registers r (this lane's feature row, 32 tokens); qr holds the
+                // same 32 elements of the residual when res_fetch found them loadable in 16-byte pieces
+                auto handle = [&](int sl, uint32_t (&r)[32], const uint4 (&qr)[RQ]) {
                     if (SPLIT && c > 0) {
                         uint32_t run[32];
                         tmem_ld32(lane_base + (uint32_t)(TC_ACC_COLS + sl * 32), run);
@@ -393,33 +416,108 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_tc_kernel(const GemmPara
                     }
                     if (sl == sl0 + SLICES - 1) release();
                     const int64_t tokc = (int64_t)tok0 + sl * 32;
+                    // activation(product + bias), kept as fp32 bits in r.  The activation sits in one warp-uniform branch
+                    // around its own unrolled loop: the 32 evaluations are independent and interleave, where a test per
+                    // element would run them one after the other at full dependent latency.
+                    if (prm.bias_cols) {
+                        float bc = bcol[0];
+#pragma unroll
+                        for (int i = 1; i < SLICES; i++) bc = (sl - sl0 == i) ? bcol[i] : bc;
+#pragma unroll
+                        for (int j = 0; j < 32; j++) r[j] = __float_as_uint(__uint_as_float(r[j]) + __shfl_sync(0xffffffffu, bc, j));
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < 32; j++) r[j] = __float_as_uint(__uint_as_float(r[j]) + bias);
+                    }
+                    if (gelu) {
+#pragma unroll
+                        for (int j = 0; j < 32; j++) r[j] = __float_as_uint(gelu_erf(__uint_as_float(r[j])));
+                    }
+                    if constexpr (TMA_OUT) {
+                        if (res && feat_ok) {
+                            if (res_vec_ok(tokc)) {
+                                if constexpr (RES_AHEAD) {
+                                    const T *e = reinterpret_cast<const T *>(qr);
+#pragma unroll
+                                    for (int j = 0; j < 32; j++) r[j] = __float_as_uint(__uint_as_float(r[j]) + DT<T>::to_f32(e[j]));
+                                } else {
+                                    const uint4 *src = reinterpret_cast<const uint4 *>(res + feat * prm.ld_res + tokc);
+#pragma unroll
+                                    for (int v = 0; v < 8; v++) {
+                                        const uint4 w = __ldg(src + v);
+                                        r[4 * v] = __float_as_uint(__uint_as_float(r[4 * v]) + __uint_as_float(w.x));
+                                        r[4 * v + 1] = __float_as_uint(__uint_as_float(r[4 * v + 1]) + __uint_as_float(w.y));
+                                        r[4 * v + 2] = __float_as_uint(__uint_as_float(r[4 * v + 2]) + __uint_as_float(w.z));
+                                        r[4 * v + 3] = __float_as_uint(__uint_as_float(r[4 * v + 3]) + __uint_as_float(w.w));
+                                    }
+                                }
+                            } else {
+                                for (int j = 0; j < 32; j++)
+                                    if (tokc + j < prm.ntok) r[j] = __float_as_uint(__uint_as_float(r[j]) + DT<T>::to_f32(res[feat * prm.ld_res + tokc + j]));
+                            }
+                        }
+                        // registers -> staging row `lane` (16-byte chunks XOR-swizzled by row: the 128-byte swizzle of the
+                        // output's tensor map), once the previous group's bulk store has read the tile
+                        constexpr int CH = 32 / CHUNK_TOK;  // chunks per slice: 4 (16-bit) or 8 (fp32)
+                        const int ch0 = (sl % GROUP_SLICES) * CH;
+                        if ((sl % GROUP_SLICES) == 0) {
+                            if (lane == 0) tma_store_wait_read();
+                            __syncwarp();
+                        }
+#pragma unroll
+                        for (int v = 0; v < CH; v++) {
+                            uint4 w;
+                            if constexpr (sizeof(T) == 4) {
+                                w = make_uint4(r[4 * v], r[4 * v + 1], r[4 * v + 2], r[4 * v + 3]);
+                            } else {  // one packed conversion per pair
+                                w = make_uint4(pack2<T>(__uint_as_float(r[8 * v]), __uint_as_float(r[8 * v + 1])),
+                                               pack2<T>(__uint_as_float(r[8 * v + 2]), __uint_as_float(r[8 * v + 3])),
+                                               pack2<T>(__uint_as_float(r[8 * v + 4]), __uint_as_float(r[8 * v + 5])),
+                                               pack2<T>(__uint_as_float(r[8 * v + 6]), __uint_as_float(r[8 * v + 7])));
+                            }
+                            *reinterpret_cast<uint4 *>(stage_w + lane * 128 + (((ch0 + v) ^ (lane & 7)) << 4)) = w;
+                        }
+                        if ((sl % GROUP_SLICES) != GROUP_SLICES - 1) return;
+                        // The staging tile is exactly one swizzled box of 32 rows x 128 bytes: hand it to the copy engine,
+                        // which clips it at the tensor's edges, and go on with the next slice.
+                        fence_proxy_async_smem();
+                        __syncwarp();
+                        if (lane == 0) tma_store_2d(&maps.out, stage_w, tok0 + (sl / GROUP_SLICES) * GROUP_TOK, feat0 + q * 32);
+                        return;
+                    } else {
                     if (prm.out_tm_vec) {
                         // Token-major output through the staging tile.  TMEM hands every lane one feature and 32 tokens;
                         // out[token][feature] wants neighbouring lanes on neighbouring features, which scalar stores
                         // give only 2 bytes at a time.  The slice is transposed in shared memory ([token][32 features])
-                        // and leaves -- after the residual, fetched the same way, is added -- in 16-byte pieces.
-                        T *st = reinterpret_cast<T *>(stage_w);
-#pragma unroll
-                        for (int j = 0; j < 32; j++) {
-                            float v = __uint_as_float(r[j]) + bias;
-                            if (gelu) v = gelu_erf(v);
-                            st[j * 32 + lane] = DT<T>::from_f32(v);
-                        }
-                        __syncwarp();
+                        // and leaves -- after the residual, fetched in the same 16-byte pieces before the transposition
+                        // so that its latency is covered, is added -- in 16-byte stores.
                         constexpr int CPR = 32 * (int)sizeof(T) / 16;  // 16-byte chunks per staged row: 4 (16-bit) or 8 (fp32)
                         const int64_t fbase = (int64_t)feat0 + q * 32 + (lane % CPR) * CHUNK_TOK;  // CHUNK_TOK = elements per chunk
+                        const bool whole = fbase + CHUNK_TOK <= prm.out_feats;
+                        uint4 rv[CPR];
+                        if (res) {
+#pragma unroll
+                            for (int i = 0; i < CPR; i++) {
+                                const int64_t tok = tokc + i * (32 / CPR) + lane / CPR;
+                                rv[i] = make_uint4(0u, 0u, 0u, 0u);
+                                if (tok < prm.ntok && whole) rv[i] = __ldg(reinterpret_cast<const uint4 *>(res + tok * prm.ld_res + fbase));
+                            }
+                        }
+                        T *st = reinterpret_cast<T *>(stage_w);
+#pragma unroll
+                        for (int j = 0; j < 32; j++) st[j * 32 + lane] = DT<T>::from_f32(__uint_as_float(r[j]));
+                        __syncwarp();
 #pragma unroll
                         for (int i = 0; i < CPR; i++) {
                             const int row = i * (32 / CPR) + lane / CPR;
                             const int64_t tok = tokc + row;
                             if (tok >= prm.ntok || fbase >= prm.out_feats) continue;
                             uint4 w = *reinterpret_cast<const uint4 *>(stage_w + row * 32 * (int)sizeof(T) + (lane % CPR) * 16);
-                            const bool whole = fbase + CHUNK_TOK <= prm.out_feats;
                             if (res) {
                                 __align__(16) T a[CHUNK_TOK], b[CHUNK_TOK];
                                 *reinterpret_cast<uint4 *>(a) = w;
-                                if (whole) *reinterpret_cast<uint4 *>(b) = __ldg(reinterpret_cast<const uint4 *>(res + tok * prm.ld_res + fbase));
-                                else
+                                *reinterpret_cast<uint4 *>(b) = rv[i];
+                                if (!whole)  // ragged end of the feature axis
                                     for (int k = 0; k < CHUNK_TOK; k++) b[k] = fbase + k < prm.out_feats ? res[tok * prm.ld_res + fbase + k] : DT<T>::from_f32(0.f);
 #pragma unroll
                                 for (int k = 0; k < CHUNK_TOK; k++) a[k] = DT<T>::from_f32(DT<T>::to_f32(a[k]) + DT<T>::to_f32(b[k]));
@@ -435,14 +533,26 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_tc_kernel(const GemmPara
                         __syncwarp();  // the staging rows are free for the next slice
                         return;
                     }
+                    // the other output forms take the residual element by element, again under one uniform branch
+                    const bool res_late = prm.out_staged && prm.res_vec;
+                    if (res && feat_ok && !res_late) {
+                        if (prm.out_token_major) {
+#pragma unroll
+                            for (int j = 0; j < 32; j++)
+                                if (tokc + j < prm.ntok) r[j] = __float_as_uint(__uint_as_float(r[j]) + DT<T>::to_f32(res[(tokc + j) * prm.ld_res + feat]));
+                        } else {
+#pragma unroll
+                            for (int j = 0; j < 32; j++)
+                                if (tokc + j < prm.ntok) r[j] = __float_as_uint(__uint_as_float(r[j]) + DT<T>::to_f32(res[feat * prm.ld_res + tokc + j]));
+                        }
+                    }
                     if (!prm.out_staged) {
                         if (tokc >= prm.ntok || !feat_ok) return;
                         if (prm.out_token_major && prm.n_out == 1 && tokc + 32 <= prm.ntok) {
                             // full slice of the F.linear layout: one conversion, one pointer step and one store per element
                             T *p = static_cast<T *>(prm.outs[0]) + tokc * prm.ld_out + feat;
-                            int64_t ro = tokc * prm.ld_res + feat;
 #pragma unroll
-                            for (int j = 0; j < 32; j++, p += prm.ld_out, ro += prm.ld_res) *p = DT<T>::from_f32(finish(r[j], bias, ro));
+                            for (int j = 0; j < 32; j++, p += prm.ld_out) *p = DT<T>::from_f32(__uint_as_float(r[j]));
                             return;
                         }
                         for (int d = 0; d < prm.n_out; d++) {
@@ -451,7 +561,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_tc_kernel(const GemmPara
                             for (int j = 0; j < 32; j++) {
                                 const int64_t tok = tokc + j;
                                 if (tok < prm.ntok) {
-                                    const T o = DT<T>::from_f32(finish(r[j], bias, prm.out_token_major ? tok * prm.ld_res + feat : feat * prm.ld_res + tok));
+                                    const T o = DT<T>::from_f32(__uint_as_float(r[j]));
                                     if (prm.out_token_major) out[tok * prm.ld_out + feat] = o;
                                     else out[feat * prm.ld_out + tok] = o;
                                 }
@@ -462,29 +572,16 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_tc_kernel(const GemmPara
                     // registers -> staging row `lane`
                     constexpr int CH = 32 / CHUNK_TOK;  // chunks per slice: 4 (16-bit) or 8 (fp32)
                     const int ch0 = (sl % GROUP_SLICES) * CH;
-                    const bool plain = !gelu && !res;   // the common case keeps its short path
-                    const int64_t ro0 = feat * prm.ld_res + tokc;  // staged output is feature-major
 #pragma unroll
                     for (int v = 0; v < CH; v++) {
                         uint4 w;
                         if constexpr (sizeof(T) == 4) {
-                            float f[4];
-#pragma unroll
-                            for (int k = 0; k < 4; k++)
-                                f[k] = plain ? __uint_as_float(r[4 * v + k]) + bias
-                                             : finish(r[4 * v + k], bias, (feat_ok && tokc + 4 * v + k < prm.ntok) ? ro0 + 4 * v + k : 0);
-                            w = make_uint4(__float_as_uint(f[0]), __float_as_uint(f[1]), __float_as_uint(f[2]), __float_as_uint(f[3]));
-                        } else {
-                            uint32_t h[4];
-#pragma unroll
-                            for (int k = 0; k < 4; k++) {  // one packed conversion per pair
-                                const int e0 = 8 * v + 2 * k;
-                                const float lo = plain ? __uint_as_float(r[e0]) + bias : finish(r[e0], bias, (feat_ok && tokc + e0 < prm.ntok) ? ro0 + e0 : 0);
-                                const float hi = plain ? __uint_as_float(r[e0 + 1]) + bias
-                                                       : finish(r[e0 + 1], bias, (feat_ok && tokc + e0 + 1 < prm.ntok) ? ro0 + e0 + 1 : 0);
-                                h[k] = pack2<T>(lo, hi);
-                            }
-                            w = make_uint4(h[0], h[1], h[2], h[3]);
+                            w = make_uint4(r[4 * v], r[4 * v + 1], r[4 * v + 2], r[4 * v + 3]);
+                        } else {  // one packed conversion per pair
+                            w = make_uint4(pack2<T>(__uint_as_float(r[8 * v]), __uint_as_float(r[8 * v + 1])),
+                                           pack2<T>(__uint_as_float(r[8 * v + 2]), __uint_as_float(r[8 * v + 3])),
+                                           pack2<T>(__uint_as_float(r[8 * v + 4]), __uint_as_float(r[8 * v + 5])),
+                                           pack2<T>(__uint_as_float(r[8 * v + 6]), __uint_as_float(r[8 * v + 7])));
                         }
                         *reinterpret_cast<uint4 *>(stage_w + lane * 128 + (((ch0 + v) ^ (lane & 7)) << 4)) = w;
                     }
@@ -497,7 +594,17 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_tc_kernel(const GemmPara
                         const int row = i * 4 + (lane >> 3);
                         const int64_t f = (int64_t)feat0 + q * 32 + row;
                         if (f >= prm.out_feats || tokg >= prm.ntok) continue;
-                        const uint4 w = *reinterpret_cast<const uint4 *>(stage_w + row * 128 + (((lane & 7) ^ (row & 7)) << 4));
+                        uint4 w = *reinterpret_cast<const uint4 *>(stage_w + row * 128 + (((lane & 7) ^ (row & 7)) << 4));
+                        if (res && res_late) {  // the loads of the eight rows are independent of one another and of the staging tile
+                            __align__(16) T a[CHUNK_TOK], b[CHUNK_TOK];
+                            *reinterpret_cast<uint4 *>(a) = w;
+                            if (tokg + CHUNK_TOK <= prm.ntok) *reinterpret_cast<uint4 *>(b) = __ldg(reinterpret_cast<const uint4 *>(res + f * prm.ld_res + tokg));
+                            else
+                                for (int k = 0; k < CHUNK_TOK; k++) b[k] = tokg + k < prm.ntok ? res[f * prm.ld_res + tokg + k] : DT<T>::from_f32(0.f);
+#pragma unroll
+                            for (int k = 0; k < CHUNK_TOK; k++) a[k] = DT<T>::from_f32(DT<T>::to_f32(a[k]) + DT<T>::to_f32(b[k]));
+                            w = *reinterpret_cast<const uint4 *>(a);
+                        }
                         if (tokg + CHUNK_TOK <= prm.ntok) {
                             if (prm.mc_out) {  // the switch replicates the 16 bytes to every GPU of the multicast group
                                 multimem_st_v4(static_cast<T *>(prm.mc_out) + f * prm.ld_out + tokg, w);
@@ -513,24 +620,32 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_tc_kernel(const GemmPara
                         }
                     }
                     __syncwarp();  // the staging rows are free for the next group
+                    }  // !TMA_OUT
                 };
                 // TMEM reads are software-pipelined: the load of the next slice is in flight while this one is converted
                 // and stored; tmem_ld_fence ties the wait to the registers so no use can move above it.
                 uint32_t ra[32], rb[32];
+                uint4 qa[RQ], qb[RQ];
                 const uint32_t acc_addr = lane_base + (uint32_t)(b * TC_ACC_COLS);
                 tmem_ld32_issue(acc_addr + (uint32_t)(sl0 * 32), ra);
+                if (last) res_fetch(sl0, qa);
 #pragma unroll 1
                 for (int sl = sl0; sl < sl0 + SLICES; sl += 2) {
                     tmem_ld_fence(ra);
                     tmem_ld32_issue(acc_addr + (uint32_t)((sl + 1) * 32), rb);
-                    handle(sl, ra);
+                    if (last) res_fetch(sl + 1, qb);
+                    handle(sl, ra, qa);
                     tmem_ld_fence(rb);
-                    if (sl + 2 < sl0 + SLICES) tmem_ld32_issue(acc_addr + (uint32_t)((sl + 2) * 32), ra);
-                    handle(sl + 1, rb);
+                    if (sl + 2 < sl0 + SLICES) {
+                        tmem_ld32_issue(acc_addr + (uint32_t)((sl + 2) * 32), ra);
+                        if (last) res_fetch(sl + 2, qa);
+                    }
+                    handle(sl + 1, rb, qb);
                 }
                 if (!last) release();  // promotion finished: hand the accumulator back
             }
         }
+        if (TMA_OUT && lane == 0) tma_store_wait_all();
     }
     __syncthreads();
     if constexpr (PAIR) cluster_sync_all();  // the peer no longer reads this CTA's shared memory or signals its barriers
@@ -574,14 +689,14 @@ template <typename T, bool TR> static int expand_launch(const ExpandParams &p, s
     return expand_launch_n<T, TR, 0>(p, smem, items, st);
 }
 
-template <typename T, bool PAIR> static int gemm_launch(const GemmParams &p, const GemmMaps &maps, cudaStream_t st) {
+template <typename T, bool PAIR, bool TMA_OUT> static int gemm_launch_as(const GemmParams &p, const GemmMaps &maps, cudaStream_t st) {
     const size_t smem = (size_t)GEMM_RING_BYTES + GEMM_STAGING_BYTES + 256 + 1024;
     int dev = 0, sms = 148;
     NMG_CUDA(cudaGetDevice(&dev));
     NMG_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
     const int64_t tiles = (int64_t)p.tiles_f * p.tiles_t;
     if (tiles > 0x3fffffff) NMG_FAIL(NMG_ERR_UNSUPPORTED, "too many output tiles for one launch");
-    NMG_CUDA(cudaFuncSetAttribute(gemm_tc_kernel<T, PAIR>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    NMG_CUDA(cudaFuncSetAttribute(gemm_tc_kernel<T, PAIR, TMA_OUT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     cudaLaunchConfig_t cfg = {};
     const int64_t units = PAIR ? sms / 2 : sms;  // persistent CTAs, or CTA pairs
     cfg.gridDim = dim3((unsigned)((tiles < units ? tiles : units) * (PAIR ? 2 : 1)));
@@ -597,8 +712,11 @@ template <typename T, bool PAIR> static int gemm_launch(const GemmParams &p, con
     attr[1].val.clusterDim.z = 1;
     cfg.attrs = attr;
     cfg.numAttrs = PAIR ? 2 : 1;
-    NMG_CUDA(cudaLaunchKernelEx(&cfg, gemm_tc_kernel<T, PAIR>, p, maps));
+    NMG_CUDA(cudaLaunchKernelEx(&cfg, gemm_tc_kernel<T, PAIR, TMA_OUT>, p, maps));
     return NMG_OK;
+}
+template <typename T, bool PAIR> static int gemm_launch(const GemmParams &p, const GemmMaps &maps, cudaStream_t st) {
+    return p.out_tma ? gemm_launch_as<T, PAIR, true>(p, maps, st) : gemm_launch_as<T, PAIR, false>(p, maps, st);
 }
 
 // CTA pairs serve 16-bit operands when the output has at least two 128-feature tiles (a pair covers 256 features).
@@ -640,17 +758,32 @@ int tc_dense_gemm(int64_t rows, int64_t red, int dtype, bool pair, const char *d
     int rc;
     GemmMaps maps;
     const int edt = dtype == NMG_F32 ? NMG_BF16 : dtype;
+    const size_t osz = dtype == NMG_F32 ? 4 : 2;
+    // Token-major output of a CTA-pair product: exchange the operands' roles.  Both boxes are 64 x 128 in pair mode, so the
+    // activations can be the row operand (tokens on the accumulator's lanes) and the weight the column operand; the
+    // output is then "feature-major" in the kernel's terms -- accumulator rows are output rows -- and leaves through the
+    // staged 16-byte path with no transposition, the bias running along the columns.
+    const bool swap = pair && out_token_major && n_outs == 1 && !mc_out && tokens > TC_BM && (ld_out * osz) % 16 == 0 &&
+                      (reinterpret_cast<uintptr_t>(outs[0]) & 15) == 0;
     for (int c = 0; c < 3; c++) {
         const int pc = c < planes ? c : 0;
-        if ((rc = encode_tmap_2d(&maps.a[c], edt, dense + (size_t)pc * rows * ld * 2, (uint64_t)red, (uint64_t)rows, (uint64_t)ld, TC_BK, TC_BM, 1))) return rc;
-        maps.b[c] = act_maps[c];
+        CUtensorMap wmap;
+        if ((rc = encode_tmap_2d(&wmap, edt, dense + (size_t)pc * rows * ld * 2, (uint64_t)red, (uint64_t)rows, (uint64_t)ld, TC_BK, TC_BM, 1))) return rc;
+        maps.a[c] = swap ? act_maps[c] : wmap;
+        maps.b[c] = swap ? wmap : act_maps[c];
+    }
+    if (swap) {  // from here on "rows" are the accumulator's rows (tokens) and "tokens" its columns (output features)
+        const int64_t t = rows;
+        rows = tokens;
+        tokens = t;
+        out_token_major = 0;
     }
     int *status = nullptr;
     if ((rc = get_status_word(&status))) return rc;
     GemmParams gp{};
     gp.bias = bias;
     gp.n_out = n_outs;
-    const size_t osz = dtype == NMG_F32 ? 4 : 2;
+    gp.bias_cols = swap ? 1 : 0;
     bool vec = !out_token_major && (ld_out * osz) % 16 == 0;
     for (int d = 0; d < n_outs; d++) {
         if (!outs[d]) NMG_FAIL(NMG_ERR_INVALID, "output buffer %d is NULL", d);
@@ -663,12 +796,20 @@ int tc_dense_gemm(int64_t rows, int64_t red, int dtype, bool pair, const char *d
     gp.out_tm_vec = (out_token_major && n_outs == 1 && (ld_out * osz) % 16 == 0 && (reinterpret_cast<uintptr_t>(outs[0]) & 15) == 0 &&
                      (!epi.residual || ((epi.ld_res * osz) % 16 == 0 && (reinterpret_cast<uintptr_t>(epi.residual) & 15) == 0)))
                         ? 1 : 0;
+    gp.out_tma = (vec && n_outs == 1 && !mc_out) ? 1 : 0;
+    if (gp.out_tma) {
+        const uint32_t box_cols = (uint32_t)(128 / osz);
+        if ((rc = encode_tmap_2d(&maps.out, dtype, outs[0], (uint64_t)tokens, (uint64_t)rows, (uint64_t)ld_out, box_cols, 32, 1))) return rc;
+    } else {
+        maps.out = maps.a[0];  // never used; keeps the parameter defined
+    }
     gp.mc_out = (vec && mc_out && (reinterpret_cast<uintptr_t>(mc_out) & 15) == 0) ? mc_out : nullptr;
     const int tile_feats = pair ? 2 * TC_BM : TC_BM;
     gp.tiles_f = (int)((rows + tile_feats - 1) / tile_feats);
     gp.tiles_t = (int)((tokens + TC_BN - 1) / TC_BN);
     gp.status = status;
     gp.act = epi.act; gp.residual = epi.residual; gp.ld_res = epi.ld_res;
+    gp.res_vec = (epi.residual && (epi.ld_res * osz) % 16 == 0 && (reinterpret_cast<uintptr_t>(epi.residual) & 15) == 0) ? 1 : 0;
     if (dtype == NMG_F32) return gemm_launch<float, false>(gp, maps, st);
     if (dtype == NMG_F16) return pair ? gemm_launch<__half, true>(gp, maps, st) : gemm_launch<__half, false>(gp, maps, st);
     return pair ? gemm_launch<__nv_bfloat16, true>(gp, maps, st) : gemm_launch<__nv_bfloat16, false>(gp, maps, st);

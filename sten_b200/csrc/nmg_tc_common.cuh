@@ -122,8 +122,12 @@ __device__ __forceinline__ uint32_t map_to_rank(uint32_t local, uint32_t rank) {
     asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(local), "r"(rank));
     return r;
 }
+// Arrive on a barrier of the pair's other CTA (or this one) to say "my reads of the accumulator are done".  The reads are
+// tcgen05.ld whose values are already in registers (tcgen05.wait::ld) when this runs, so the signal carries no data and
+// needs no release: a release at cluster scope would first wait until every global store this thread has in flight --
+// the tile's output -- is acknowledged by L2, once per tile and warp, which is what bounded the drain.
 __device__ __forceinline__ void mbar_arrive_remote(uint32_t cluster_addr) {
-    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+    asm volatile("mbarrier.arrive.relaxed.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
 }
 __device__ __forceinline__ bool mbar_try_wait_cluster(uint64_t *bar, uint32_t parity) {
     uint32_t ok;
