@@ -87,6 +87,7 @@ ProfileEvents take_profile_events();
 
 // One int per device that kernels set to a non-zero code when a bounded wait runs out.
 int get_status_word(int **dev_ptr);
+int get_wave_counter(unsigned **dev_ptr);  // one of a few rotating 4-byte counters of the current device (spare bytes of the status block)
 // Status word of nmg_spmm_noalloc on device `dev` (start of the built-in scratch array), or NULL before its first call there.
 int *noalloc_status_word(int dev);
 
@@ -147,6 +148,17 @@ __device__ __forceinline__ uint64_t global_timer_ns() {
     uint64_t t;
     asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
     return t;
+}
+// Soft rendezvous of the persistent CTAs of one launch: count this CTA in and wait until `target` CTAs have been counted
+// or `limit_ns` have passed, whichever comes first.  It only keeps CTAs that share operand panels through L2 in step;
+// nothing depends on it having been reached, so a CTA that is late or absent costs the others at most the limit.
+__device__ __forceinline__ void soft_rendezvous(unsigned *ctr, unsigned target, uint64_t limit_ns) {
+    atomicAdd(ctr, 1u);
+    const uint64_t t0 = global_timer_ns();
+    while (*reinterpret_cast<volatile unsigned *>(ctr) < target) {
+        if (global_timer_ns() - t0 > limit_ns) break;
+        __nanosleep(40);
+    }
 }
 __device__ __forceinline__ bool mbar_wait_bounded(uint64_t *bar, uint32_t parity, int *status, int code,
                                                   uint64_t limit_ns = kWaitLimitNs) {

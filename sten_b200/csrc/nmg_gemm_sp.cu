@@ -146,14 +146,17 @@ constexpr int SP_STAGING_BYTES = SP_DRAIN_WARPS * 2048;  // per drain warp: 32 t
 
 struct SpGemmParams {
     void *out;            // [tokens][ld_out]
-    int out_vec;          // output rows are 16-byte aligned: transposed in shared memory, 16-byte stores
+    int out_vec;          // output rows are 16-byte aligned: transposed in shared memory, one tiled bulk store per slice
     int64_t out_feats, red, ntok, ld_out, n_rt;
     int tiles_f, tiles_t; // tiles_f counts 256-feature tiles
+    int band;             // width of the tile order's bands, in feature tiles
+    unsigned *wave_ctr;   // zeroed counter for the producers' soft rendezvous before every tile, or NULL
     int *status;
 };
 struct SpGemmMaps {
     CUtensorMap a;  // A_sp [K][R/2], box 64 x 128, 128-byte swizzle
     CUtensorMap b;  // dY [tokens][M], box 64 x 128
+    CUtensorMap out;  // dX [tokens][K], box 32 features x 32 tokens, no swizzle (out_vec)
     CUtensorMap e;  // metadata as [atoms * 2][256] 32-bit words, box 256 x 2 = one 2 KB atom
 };
 
@@ -218,7 +221,7 @@ __global__ void __launch_bounds__(SP_THREADS, 1) gemm_sp_kernel(const SpGemmPara
 
     auto tile_origin = [&](int ti, int &tile_f, int &tok0) {
         int tile_t;
-        tile_of_cta(pair + ti * npairs, prm.tiles_f, prm.tiles_t, tile_f, tile_t);
+        tile_of_cta(pair + ti * npairs, prm.tiles_f, prm.tiles_t, tile_f, tile_t, prm.band);
         tok0 = tile_t * TC_BN;
     };
 
@@ -228,10 +231,16 @@ __global__ void __launch_bounds__(SP_THREADS, 1) gemm_sp_kernel(const SpGemmPara
             int it = 0;
             bool ok = true;
             asm volatile("griddepcontrol.wait;" ::: "memory");  // the expansion pass's output arrives through the loads below
+            unsigned arrivals = 0;
             for (int ti = 0; ti < my_tiles && ok; ti++) {
                 int tile_f, tok0;
                 tile_origin(ti, tile_f, tok0);
                 const int half_f = tile_f * 2 + (int)rank;  // this CTA's 128-feature tile = its metadata atom row
+                if (prm.wave_ctr && ti > 0) {  // keep the CTAs that share operand panels through L2 in step (soft_rendezvous)
+                    const int left = ntiles - ti * npairs;
+                    arrivals += (unsigned)((left < npairs ? left : npairs) * 2);
+                    soft_rendezvous(prm.wave_ctr, arrivals, (uint64_t)nst * 80);
+                }
                 for (int j = 0; j < nst; j++, it++) {
                     const int s = it % SP_STAGES;
                     if (!(ok = mbar_wait_cluster_bounded(&empty[s], (uint32_t)(((it / SP_STAGES) & 1) ^ 1), prm.status, 31))) break;
@@ -299,31 +308,22 @@ __global__ void __launch_bounds__(SP_THREADS, 1) gemm_sp_kernel(const SpGemmPara
             if (lane == 0) mbar_arrive_remote(acc_free_leader);
             if (prm.out_vec) {
                 // TMEM hands every lane one feature and 32 tokens per slice; the token-major output wants neighbouring
-                // lanes on neighbouring features.  Transpose the slice in shared memory and store 16 bytes per lane.
+                // lanes on neighbouring features.  The slice is transposed into a [32 tokens][32 features] tile in shared
+                // memory and leaves as one tiled bulk store, clipped by the copy engine at the tensor's edges.
                 char *stage_w = staging + (warp - 2) * 2048;
                 T *st = reinterpret_cast<T *>(stage_w);
-                const int64_t fbase = (int64_t)tile_f * SP_PAIR_FEATS + (int64_t)rank * TC_BM + q * 32 + (lane & 3) * 8;
+                const int f0 = tile_f * SP_PAIR_FEATS + (int)rank * TC_BM + q * 32;
 #pragma unroll
                 for (int s = 0; s < SLICES; s++) {
-                    const int64_t tokc = (int64_t)tok0 + (sl0 + s) * 32;
+                    const int tokc = tok0 + (sl0 + s) * 32;
                     if (tokc >= prm.ntok) break;  // warp-uniform
+                    if (lane == 0) tma_store_wait_read();  // the previous store has read the tile
+                    __syncwarp();
 #pragma unroll
                     for (int j = 0; j < 32; j++) st[j * 32 + lane] = DT<T>::from_f32(__uint_as_float(r[s][j]));
+                    fence_proxy_async_smem();
                     __syncwarp();
-#pragma unroll
-                    for (int i = 0; i < 4; i++) {
-                        const int row = i * 8 + (lane >> 2);
-                        const int64_t tok = tokc + row;
-                        if (tok >= prm.ntok || fbase >= prm.out_feats) continue;
-                        const uint4 w = *reinterpret_cast<const uint4 *>(stage_w + row * 64 + (lane & 3) * 16);
-                        T *dst = out + tok * prm.ld_out + fbase;
-                        if (fbase + 8 <= prm.out_feats) *reinterpret_cast<uint4 *>(dst) = w;
-                        else {
-                            const T *e = reinterpret_cast<const T *>(&w);
-                            for (int k = 0; k < 8 && fbase + k < prm.out_feats; k++) dst[k] = e[k];
-                        }
-                    }
-                    __syncwarp();
+                    if (lane == 0 && f0 < prm.out_feats) tma_store_2d(&maps.out, stage_w, f0, tokc);
                 }
                 continue;
             }
@@ -344,6 +344,7 @@ __global__ void __launch_bounds__(SP_THREADS, 1) gemm_sp_kernel(const SpGemmPara
             }
         }
     }
+    if (warp >= 2 && lane == 0) tma_store_wait_all();
     __syncthreads();
     cluster_sync_all();  // the peer no longer reads this CTA's shared memory or signals its barriers
     if (warp == 1) {
@@ -469,9 +470,25 @@ int tc_sp_matmul_t(const Geo &geo, int dtype, const void *sp_copy, const void *d
     SpGemmParams gp{};
     gp.out = dx;
     gp.out_vec = ((ld_dx * 2) % 16 == 0 && (reinterpret_cast<uintptr_t>(dx) & 15) == 0) ? 1 : 0;
+    if (gp.out_vec) {
+        if ((rc = encode_tmap_2d(&maps.out, dtype, dx, (uint64_t)geo.K, (uint64_t)tokens, (uint64_t)ld_dx, 32, 32, 0))) return rc;
+    } else {
+        maps.out = maps.b;  // never used; keeps the parameter defined
+    }
     gp.out_feats = geo.K; gp.red = geo.M; gp.ntok = tokens; gp.ld_out = ld_dx; gp.n_rt = lay.n_rt;
     gp.tiles_f = (int)(lay.n_ft / 2);
     gp.tiles_t = (int)((tokens + TC_BN - 1) / TC_BN);
+    gp.band = TC_BAND_PAIR;
+    {
+        // many waves over a long reduction: keep the producers in step; the counter is zeroed in stream order
+        int dev = 0, sms = 148;
+        NMG_CUDA(cudaGetDevice(&dev));
+        NMG_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+        if ((int64_t)gp.tiles_f * gp.tiles_t >= 3 * (int64_t)(sms / 2) && geo.M >= 4096) {
+            if ((rc = get_wave_counter(&gp.wave_ctr))) return rc;
+            NMG_CUDA(cudaMemsetAsync(gp.wave_ctr, 0, sizeof(unsigned), st));
+        }
+    }
     gp.status = status;
     return dtype == NMG_F16 ? sp_gemm_launch<__half>(gp, maps, st) : sp_gemm_launch<__nv_bfloat16>(gp, maps, st);
 }

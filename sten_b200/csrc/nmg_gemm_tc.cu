@@ -172,6 +172,8 @@ struct GemmParams {
     int out_staged;    // feature-major output whose rows are 16-byte aligned: go through the staging tile
     int out_tm_vec;    // token-major output (and residual) whose rows are 16-byte aligned: transposed in the staging tile, 16-byte stores
     int tiles_f, tiles_t;  // tiles_f counts tiles of 128 features (one CTA per tile) or 256 (CTA pairs)
+    int band;              // width of the tile order's bands, in feature tiles
+    unsigned *wave_ctr;    // zeroed counter for the producers' soft rendezvous before every tile, or NULL
     int *status;
 };
 constexpr int GEMM_STAGING_BYTES = GEMM_DRAIN_WARPS * 4096;  // per drain warp: 32 feature rows x 128 bytes
@@ -270,7 +272,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_tc_kernel(const GemmPara
     };
     auto tile_origin = [&](int ti, int &feat0, int &tok0) {  // feat0: first feature of THIS CTA's 128 rows
         int tile_f, tile_t;
-        tile_of_cta(unit_id + ti * nunits, prm.tiles_f, prm.tiles_t, tile_f, tile_t);
+        tile_of_cta(unit_id + ti * nunits, prm.tiles_f, prm.tiles_t, tile_f, tile_t, prm.band);
         feat0 = tile_f * TILE_FEATS + (int)rank * TC_BM;
         tok0 = tile_t * TC_BN;
     };
@@ -283,9 +285,19 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_tc_kernel(const GemmPara
             // Everything this kernel reads that an earlier kernel of the stream wrote (the expanded weight, the
             // activations) arrives through the loads below: wait here for the preceding grid to complete and flush.
             asm volatile("griddepcontrol.wait;" ::: "memory");
+            unsigned arrivals = 0;
             for (int ti = 0; ti < my_tiles && ok; ti++) {
                 int feat0, tok0;
                 tile_origin(ti, feat0, tok0);
+                if (prm.wave_ctr && ti > 0) {
+                    // CTAs whose tiles share operand panels read them from HBM once only while they stream through the
+                    // reduction in step; left alone they drift apart over the waves (measured: 2.2 MB of DRAM reads per
+                    // 256 x 256 x 16384 tile in the first dozen waves, 3.9 MB averaged over 55).  So the producers meet,
+                    // softly, before each tile: everyone that has a tile ti counts in.
+                    const int left = ntiles - ti * nunits;
+                    arrivals += (unsigned)((left < nunits ? left : nunits) * (PAIR ? 2 : 1));
+                    soft_rendezvous(prm.wave_ctr, arrivals, (uint64_t)nkb * 40);
+                }
                 for (int kb = 0; kb < nkb; kb++, it++) {
                     const int s = it % STAGES;
                     const uint32_t ph = (uint32_t)((it / STAGES) & 1);
@@ -807,6 +819,18 @@ int tc_dense_gemm(int64_t rows, int64_t red, int dtype, bool pair, const char *d
     const int tile_feats = pair ? 2 * TC_BM : TC_BM;
     gp.tiles_f = (int)((rows + tile_feats - 1) / tile_feats);
     gp.tiles_t = (int)((tokens + TC_BN - 1) / TC_BN);
+    gp.band = pair ? TC_BAND_PAIR : TC_BAND;
+    {
+        // many waves over a long reduction: keep the producers in step (see the kernel); the counter is zeroed in stream order
+        int dev = 0, sms = 148;
+        NMG_CUDA(cudaGetDevice(&dev));
+        NMG_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+        const int64_t units = pair ? sms / 2 : sms;
+        if ((int64_t)gp.tiles_f * gp.tiles_t >= 3 * units && red >= 4096) {
+            if ((rc = get_wave_counter(&gp.wave_ctr))) return rc;
+            NMG_CUDA(cudaMemsetAsync(gp.wave_ctr, 0, sizeof(unsigned), st));
+        }
+    }
     gp.status = status;
     gp.act = epi.act; gp.residual = epi.residual; gp.ld_res = epi.ld_res;
     gp.res_vec = (epi.residual && (epi.ld_res * osz) % 16 == 0 && (reinterpret_cast<uintptr_t>(epi.residual) & 15) == 0) ? 1 : 0;

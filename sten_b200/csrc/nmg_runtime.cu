@@ -4,6 +4,7 @@
 #include <cstdio>
 #include <cstring>
 #include <map>
+#include <atomic>
 #include <mutex>
 #include <tuple>
 #include <vector>
@@ -85,6 +86,17 @@ int get_status_word(int **dev_ptr) {
         it = g_status.emplace(dev, p).first;
     }
     *dev_ptr = it->second;
+    return NMG_OK;
+}
+
+// Bytes 64..191 of the status block: 32 counters handed out in rotation, so that launches in flight on different streams
+// use different ones.  The caller zeroes its counter on its stream before the launch that uses it.
+int get_wave_counter(unsigned **dev_ptr) {
+    static std::atomic<unsigned> next{0};
+    int *status = nullptr;
+    int rc = get_status_word(&status);
+    if (rc) return rc;
+    *dev_ptr = reinterpret_cast<unsigned *>(status) + 16 + (next.fetch_add(1) % 32);
     return NMG_OK;
 }
 

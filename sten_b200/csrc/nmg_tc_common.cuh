@@ -15,16 +15,19 @@ constexpr int TC_A_BYTES = TC_BM * TC_BK * 2;  // 16 KB
 constexpr int TC_B_BYTES = TC_BN * TC_BK * 2;  // 32 KB
 constexpr int TC_ACC_COLS = 256;    // one fp32 accumulator tile: 128 lanes x 256 columns
 
-// Tile order: feature tiles are taken in bands of TC_BAND; inside a band the CTA index runs over the band's feature
-// tiles first, then over token tiles.  CTAs that are resident together then share a few activation tiles (the big
-// operand) through L2 while a band's compressed weight stays L2-resident across consecutive waves.
+// Tile order: feature tiles are taken in bands of `band_w`; inside a band the CTA index runs over the band's feature
+// tiles first, then over token tiles.  The CTAs that are resident together then cover a block of band_w x (CTAs / band_w)
+// tiles and share its operand panels through L2; a wave reads band_w weight panels and CTAs / band_w activation
+// panels from HBM, which is least when the block is square in bytes: 16 for one-CTA tiles (128 x 256, 148 CTAs), 8 for
+// the 256 x 256 tiles of CTA pairs (74 pairs).
 constexpr int TC_BAND = 16;
-__device__ __forceinline__ void tile_of_cta(int lin, int tiles_f, int tiles_t, int &tf, int &tt) {
-    const int per_band = TC_BAND * tiles_t;
+constexpr int TC_BAND_PAIR = 8;
+__device__ __forceinline__ void tile_of_cta(int lin, int tiles_f, int tiles_t, int &tf, int &tt, int band_w = TC_BAND) {
+    const int per_band = band_w * tiles_t;
     const int band = lin / per_band, within = lin - band * per_band;
-    const int width = min(TC_BAND, tiles_f - band * TC_BAND);
+    const int width = min(band_w, tiles_f - band * band_w);
     tt = within / width;
-    tf = band * TC_BAND + (within - tt * width);
+    tf = band * band_w + (within - tt * width);
 }
 
 
