@@ -45,9 +45,9 @@ SWEEP = [(1, 4), (2, 4), (1, 8), (2, 8), (1, 16)]
 SW_M = SW_K = SW_TOK = 4096
 SH_M = SH_K = SH_TOK = 16384
 SH_N, SH_MM = 2, 8
-# DRAM traffic of one full-size call of the default workload (expansion pass 0.683 GB + matmul kernel 9.363 GB), from one
+# DRAM traffic of one full-size call of the default workload (expansion pass 0.683 GB + matmul kernel 9.416 GB), from one
 # ncu capture on a B200; reported in roofline.traffic at N = 1
-NCU_DRAM_BYTES_PER_CALL = 10.05e9
+NCU_DRAM_BYTES_PER_CALL = 10.10e9
 # bounded CPU sample of the sharded workload: one of eight row shards x 1024 tokens
 CPU_ROWS, CPU_TOK = 2048, 1024
 
