@@ -663,12 +663,12 @@ def encoder_numbers(torch, dist, world, rank, dev, steps, warmup, barrier):
     ids_all = torch.randint(0, 30522, (BATCH, SEQ), generator=torch.Generator().manual_seed(1))
     ids = ids_all[rank * per_rank:(rank + 1) * per_rank].to(dev)
 
-    def fwd(m):
+    def fwd(m, batch_ids=None):
         # embeddings + encoder stack called directly with no attention mask (the batch has no padding): the model's own
         # mask preparation keeps an all-ones mask while a CUDA graph is being captured, which pushes attention onto a
         # slow fp32 path in the captured graph only; without a mask eager and captured runs use the same fused attention
         with torch.no_grad():
-            return m.encoder(m.embeddings(input_ids=ids), attention_mask=None).last_hidden_state
+            return m.encoder(m.embeddings(input_ids=ids if batch_ids is None else batch_ids), attention_mask=None).last_hidden_state
 
     for _ in range(max(warmup, 3)):
         out = fwd(sparse_model)
@@ -681,22 +681,35 @@ def encoder_numbers(torch, dist, world, rank, dev, steps, warmup, barrier):
     ms_dense = timed_loop(lambda: fwd(dense_model), steps, barrier, torch, dist, world, dev)
 
     # CUDA graphs of both forwards: removes the host-side dispatch cost (144 sparse linears go through the plugin)
-    def graphed(m):
+    def graphed(m, batch_ids=None):
         try:
             g = torch.cuda.CUDAGraph()
             side = torch.cuda.Stream()
             side.wait_stream(torch.cuda.current_stream())
             with torch.cuda.stream(side):
-                fwd(m)
+                fwd(m, batch_ids)
             torch.cuda.current_stream().wait_stream(side)
             with torch.cuda.graph(g):
-                static_out = fwd(m)  # noqa: F841 - keeps the graph's output alive
+                static_out = fwd(m, batch_ids)  # noqa: F841 - keeps the graph's output alive
             return timed_loop(g.replay, steps, barrier, torch, dist, world, dev)
         except Exception:  # graph capture is an optimisation of the host path, not part of the result's validity
             return None
 
     ms_graph = graphed(sparse_model)
     ms_graph_dense = graphed(dense_model)
+    # Several ranks: besides the split batch, the data-parallel serving case -- every replica takes a whole batch of 32
+    # (no collective either; per-GPU work as at N = 1)
+    replicas = None
+    if world > 1:
+        ids_full = ids_all.to(dev)
+        for _ in range(3):
+            fwd(sparse_model, ids_full)
+            fwd(dense_model, ids_full)
+        ms_full = graphed(sparse_model, ids_full) or timed_loop(lambda: fwd(sparse_model, ids_full), steps, barrier, torch, dist, world, dev)
+        ms_full_dense = graphed(dense_model, ids_full) or timed_loop(lambda: fwd(dense_model, ids_full), steps, barrier, torch, dist, world, dev)
+        replicas = {"tokens_per_s": world * BATCH * SEQ / (ms_full * 1e-3), "dense_tokens_per_s": world * BATCH * SEQ / (ms_full_dense * 1e-3),
+                    "speedup_vs_dense_fp16": ms_full_dense / ms_full,
+                    "workload": f"batch 32 x seq 384 on each of the {world} ranks (weak scaling), slowest rank's time"}
     # opt-in variant: every weight keeps its expanded 16-bit copy (set_spmm_opt(kernel="sm100-expanded")): no expansion pass
     # per call, no memory saving; reported beside the default, never as the headline
     for name, prm in sparse_model.named_parameters():
@@ -725,6 +738,7 @@ def encoder_numbers(torch, dist, world, rank, dev, steps, warmup, barrier):
         "expanded_weights_opt_in": {"tokens_per_s": toks / (ms_exp * 1e-3), "speedup_vs_dense_fp16": ms_dense_best / ms_exp,
                                     "rel_fro_vs_default_path": err_exp,
                                     "note": "set_spmm_opt(kernel='sm100-expanded'): the expanded 16-bit weight is kept across calls"},
+        "one_batch_per_rank": replicas,
         "sparse_linears_per_forward": len(names), "fused_epilogue_modules": fused,
         "rel_fro_vs_densified_model": err, "output_finite": bool(torch.isfinite(out.float()).all()),
         "config": {"workload": "BERT-large-shaped encoder, 24 layers, all encoder linears nmg 2:4 g=16 fp16, batch 32 x seq 384",

@@ -32,6 +32,7 @@ def main():
     ap.add_argument("--gelu", action="store_true", help="fwd: bias + GELU in the matmul's epilogue")
     ap.add_argument("--residual", action="store_true", help="fwd: add a residual tensor of the output's shape in the epilogue")
     ap.add_argument("--expanded", action="store_true", help="fwd: keep the expanded 16-bit weight across calls (no expansion pass per call)")
+    ap.add_argument("--graph", action="store_true", help="time the repetitions as one replayed CUDA graph (no host launch cost between calls)")
     ap.add_argument("--sp24", action="store_true", help="bwd: keep the compressed transposed copy across calls (as the plugin's backward does)")
     a = ap.parse_args()
     n, m = map(int, a.nm.split(":"))
@@ -71,10 +72,21 @@ def main():
     call()
     torch.cuda.synchronize()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record()
-    for _ in range(a.reps):
-        call()
-    e1.record()
+    if a.graph:
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            for _ in range(a.reps):
+                call()
+        graph.replay()
+        torch.cuda.synchronize()
+        e0.record()
+        graph.replay()
+        e1.record()
+    else:
+        e0.record()
+        for _ in range(a.reps):
+            call()
+        e1.record()
     torch.cuda.synchronize()
     ops.read_status(dev)
     print(f"{a.op} {a.nm} g={g} {M}x{K} tokens={a.tokens} {a.dtype}: {e0.elapsed_time(e1) / a.reps:.4f} ms per call")

@@ -187,9 +187,8 @@ __device__ __forceinline__ void tma_store_2d(const CUtensorMap *map, const void 
                  : "memory");
     asm volatile("cp.async.bulk.commit_group;" ::: "memory");
 }
-// all bulk stores of this thread have finished READING shared memory (the source may be overwritten) / have completed
+// all bulk stores of this thread have finished READING shared memory: the source may be overwritten or given up
 __device__ __forceinline__ void tma_store_wait_read() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
-__device__ __forceinline__ void tma_store_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
 __device__ __forceinline__ void cp_async_16(void *smem_dst, const void *gsrc) {
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_u32(smem_dst)), "l"(gsrc) : "memory");
 }

@@ -344,7 +344,7 @@ __global__ void __launch_bounds__(SP_THREADS, 1) gemm_sp_kernel(const SpGemmPara
             }
         }
     }
-    if (warp >= 2 && lane == 0) tma_store_wait_all();
+    if (warp >= 2 && lane == 0) tma_store_wait_read();  // sources read before shared memory is given up; writes complete with the grid
     __syncthreads();
     cluster_sync_all();  // the peer no longer reads this CTA's shared memory or signals its barriers
     if (warp == 1) {

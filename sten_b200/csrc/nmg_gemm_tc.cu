@@ -657,7 +657,9 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_tc_kernel(const GemmPara
                 if (!last) release();  // promotion finished: hand the accumulator back
             }
         }
-        if (TMA_OUT && lane == 0) tma_store_wait_all();
+        // the bulk stores must have read their shared-memory source before the CTA's shared memory is given up; their
+        // global writes are complete when the grid is
+        if (TMA_OUT && lane == 0) tma_store_wait_read();
     }
     __syncthreads();
     if constexpr (PAIR) cluster_sync_all();  // the peer no longer reads this CTA's shared memory or signals its barriers
