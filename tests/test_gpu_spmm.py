@@ -334,6 +334,34 @@ def test_fused_activation_and_residual(dtype, tokens, algo):
     assert ops.read_status() == 0
 
 
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("M,tokens", [(1000, 1390), (264, 1281), (1032, 4100)])
+def test_fused_epilogue_ragged_edges_of_the_bulk_store_path(dtype, M, tokens):
+    """Token-major result of the CTA-pair kernel (operands exchanged, bias along the accumulator's columns, residual rows
+    fetched in 16-byte pieces, tiled bulk stores) when neither the token count nor the feature count fills the last tile:
+    the copy engine clips the stores, the residual's ragged slices take the element-wise path."""
+    from sten_b200 import _native as nat, ops
+    K, n, m, g = 520, 2, 4, 16
+    val, idx, x, dense = _problem(M, K, n, m, g, tokens, 321, dtype)
+    bias = seeded_normal((M,), 17).to(dtype).to(cuda())
+    res = seeded_normal((tokens, M), 18).to(dtype).to(cuda())
+    pre = np_of(x).astype(np.float64) @ np_of(dense).astype(np.float64).T + np_of(bias).astype(np.float64)
+    gelu = torch.nn.functional.gelu(torch.from_numpy(pre)).numpy()
+    # guard rows behind the result: nothing may be written past the last token
+    buf = torch.full((tokens + 8, M), 7.0, dtype=dtype, device=cuda())
+    y = ops.spmm(val, idx, M, K, n, m, g, x, bias=bias, algo=nat.NMG_ALGO_TENSOR, activation="gelu", residual=res, out=buf[:tokens])
+    assert rel_fro(np_of(y), gelu + np_of(res).astype(np.float64)) <= TOL_HALF
+    assert bool((buf[tokens:] == 7.0).all())
+    y2 = ops.spmm(val, idx, M, K, n, m, g, x, bias=bias, algo=nat.NMG_ALGO_TENSOR)
+    assert rel_fro(np_of(y2), pre) <= TOL_HALF
+    # a result that is a column block of a wider matrix (row pitch larger than M): the neighbouring columns stay untouched
+    wide = torch.full((tokens, M + 16), 3.0, dtype=dtype, device=cuda())
+    ops.spmm(val, idx, M, K, n, m, g, x, bias=bias, algo=nat.NMG_ALGO_TENSOR, residual=res, out=wide[:, :M])
+    assert rel_fro(np_of(wide[:, :M]), pre + np_of(res).astype(np.float64)) <= TOL_HALF
+    assert bool((wide[:, M:] == 3.0).all())
+    assert ops.read_status() == 0
+
+
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
 @pytest.mark.parametrize("n,m,g,M,K,tokens", [TC_CASES[1], TC_CASES[4], TWO_PASS_CASES[1], TWO_PASS_CASES[7], (2, 4, 16, 2176, 512, 1536)])
 def test_k_major_activations_on_tensor_cores(dtype, n, m, g, M, K, tokens):
