@@ -307,11 +307,20 @@ def sweep_table(torch, ops, nat, dev, peaks, fma_peak):
             tensor = algo == nat.NMG_ALGO_TENSOR
             peak = peaks["bf16_tflops"] if tensor else fma_peak
             executed = useful * m / n * (6 if (tensor and dtype == torch.float32) else 1) if tensor else useful
-            rows.append({"nm": f"{n}:{m}", "dtype": name, "kernel": how, "ms": t_nmg, "useful_tflops": useful,
-                         "bound": "tensor" if tensor else "fma", "frac_of_peak_useful": useful / peak,
-                         "frac_of_peak_executed": executed / peak,
-                         "cublas_dense_ms": t_dense, "speedup_vs_cublas": t_dense / t_nmg,
-                         "rel_fro_vs_float64": err, "tolerance": TOL[name]})
+            row = {"nm": f"{n}:{m}", "dtype": name, "kernel": how, "ms": t_nmg, "useful_tflops": useful,
+                   "bound": "tensor" if tensor else "fma", "frac_of_peak_useful": useful / peak,
+                   "frac_of_peak_executed": executed / peak,
+                   "cublas_dense_ms": t_dense, "speedup_vs_cublas": t_dense / t_nmg,
+                   "rel_fro_vs_float64": err, "tolerance": TOL[name]}
+            if dtype == torch.bfloat16:
+                # opt-in: the expanded 16-bit weight kept across calls (no expansion pass, no memory saving): the matmul kernel alone
+                kept = ops.expand(val, idx, SW_M, SW_K, n, m, G)
+                t_kept = timed(lambda: ops.spmm_expanded(kept, SW_M, SW_K, xd, out=o))
+                row["ms_kept_expanded_copy"] = t_kept
+                row["speedup_vs_cublas_kept_expanded_copy"] = t_dense / t_kept
+                row["rel_fro_kept_expanded_copy"] = rel_fro(o[:, rows_chk], xd.double() @ dense[rows_chk].double().t())
+                del kept
+            rows.append(row)
             del val, idx, dense, packed, o
     return rows
 
