@@ -238,9 +238,9 @@ __global__ void __launch_bounds__(256) sparsify_kernel(SparsifyParams prm) {
 }
 
 // Shared memory of one warp in the (n, m)-specialised kernel: no copy of the tile (its values are re-read through L1),
-// lists as separate score / column arrays, proposals as column indices.  7.4 KB for a 448-column tile, so that about thirty
-// warps are resident per SM: the selection is a chain of dependent shared-memory accesses, and residency is what hides it.
-struct SparsifyLean { size_t lscore, park, lcol, inbox, state, prop_p, cnt, total; };
+// lists as separate score / column arrays, proposals as column indices.  8.3 KB for a 448-column tile, so that about
+// twenty-seven warps are resident per SM: the selection is a chain of dependent shared-memory accesses, and residency is what hides it.
+struct SparsifyLean { size_t lscore, park, lcol, inbox, state, prop_p, freel, cnt, total; };
 __host__ __device__ inline SparsifyLean sparsify_lean(int cc, int C) {
     SparsifyLean l;
     size_t o = 0;
@@ -250,8 +250,9 @@ __host__ __device__ inline SparsifyLean sparsify_lean(int cc, int C) {
     l.inbox = o;  o += (size_t)cc * 2;   // [cc] this round's proposing columns, grouped by pattern
     l.state = o;  o += (size_t)cc * 2;   // [cc] pattern the column is held by, -1 = free
     l.prop_p = o; o += (size_t)cc * 2;   // [cc] pattern proposed to this round, -1 = none
+    l.freel = o;  o += (size_t)cc * 2;   // columns that propose in the next round (rejected or released in this one)
     o = (o + 3) & ~(size_t)3;
-    l.cnt = o;    o += (size_t)C * 4 * 3;
+    l.cnt = o;    o += (size_t)C * 4 * 3 + 4;  // cnt, icnt, ioff per pattern + the length of freel
     l.total = (o + 15) & ~(size_t)15;
     return l;
 }
@@ -283,9 +284,11 @@ __global__ void __launch_bounds__(256, 4) sparsify_nm_kernel(SparsifyParams prm)
     int16_t *inbox = reinterpret_cast<int16_t *>(slab + lay.inbox);
     int16_t *state = reinterpret_cast<int16_t *>(slab + lay.state);
     int16_t *prop_p = reinterpret_cast<int16_t *>(slab + lay.prop_p);
+    int16_t *freel = reinterpret_cast<int16_t *>(slab + lay.freel);
     int *cnt = reinterpret_cast<int *>(slab + lay.cnt);
     int *icnt = cnt + C;
     int *ioff = icnt + C;
+    int *nfree = ioff + C;
 
     const T *dense = static_cast<const T *>(prm.dense);
     T *val = static_cast<T *>(prm.val);
@@ -309,13 +312,17 @@ __global__ void __launch_bounds__(256, 4) sparsify_nm_kernel(SparsifyParams prm)
 
         // Deferred acceptance.  Every round with a proposal makes at least one (column, pattern) proposal that was never
         // made before, so cc * C rounds cannot be exceeded; real weights settle in a handful.
+        // After the first round only the columns that were rejected or released propose again: they are kept as a list, so
+        // that a late round with a handful of free columns costs a handful of iterations, not a sweep over the tile.
         for (int round = 0; round < cc * C + 2; round++) {
+            const int F = round == 0 ? cc : *nfree;  // proposers of this round: every column, then the list
             if (lane < C) icnt[lane] = 0;
             __syncwarp();
+            if (lane == 0) *nfree = 0;
             bool proposed = false;
-            for (int c = lane; c < cc; c += 32) {
+            for (int e = lane; e < F; e += 32) {
+                const int c = round == 0 ? e : (int)freel[e];
                 prop_p[c] = -1;
-                if (state[c] >= 0) continue;
                 float a[M_];
 #pragma unroll
                 for (int r = 0; r < M_; r++) a[r] = fabsf(DT<T>::to_f32(tile_at(r, c)));
@@ -364,11 +371,12 @@ __global__ void __launch_bounds__(256, 4) sparsify_nm_kernel(SparsifyParams prm)
                 total = __shfl_sync(0xffffffffu, incl, 31);
             }
             __syncwarp();
-            for (int c = lane; c < cc; c += 32) {
+            for (int e = lane; e < F; e += 32) {
+                const int c = round == 0 ? e : (int)freel[e];
                 const int p = prop_p[c];
                 if (p >= 0) inbox[ioff[p] + atomicAdd(&icnt[p], 1)] = (int16_t)c;
             }
-            __syncwarp();
+            __syncwarp();  // the list has been read: the steps below refill it
             if (round == 0) {
                 // all lists are empty: a proposal's place is its rank among the proposals of its pattern
                 for (int e = lane; e < total; e += 32) {
@@ -381,6 +389,7 @@ __global__ void __launch_bounds__(256, 4) sparsify_nm_kernel(SparsifyParams prm)
                         rank += above(park[c2], c2, sc, c) ? 1 : 0;
                     }
                     if (rank < g) { lscore[p * g + rank] = sc; lcol[p * g + rank] = (int16_t)c; state[c] = (int16_t)p; }
+                    else freel[atomicAdd(nfree, 1)] = (int16_t)c;
                 }
                 if (lane < C) cnt[lane] = min(icnt[lane], g);
             } else if (lane < C) {
@@ -393,8 +402,12 @@ __global__ void __launch_bounds__(256, 4) sparsify_nm_kernel(SparsifyParams prm)
                     const int c = inbox[e];
                     const uint32_t sc = park[c];
                     if (L == g) {
-                        if (!above(sc, c, ls[g - 1], lc[g - 1])) continue;  // stays free
-                        state[lc[g - 1]] = -1;                                  // the weakest kept proposer is released
+                        if (!above(sc, c, ls[g - 1], lc[g - 1])) {  // stays free
+                            freel[atomicAdd(nfree, 1)] = (int16_t)c;
+                            continue;
+                        }
+                        state[lc[g - 1]] = -1;                          // the weakest kept proposer is released
+                        freel[atomicAdd(nfree, 1)] = lc[g - 1];
                         L = g - 1;
                     }
                     int j = L;
