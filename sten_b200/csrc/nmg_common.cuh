@@ -86,6 +86,9 @@ struct ProfileEvents { cudaEvent_t start, stop; };
 ProfileEvents take_profile_events();
 
 // One int per device that kernels set to a non-zero code when a bounded wait runs out.
+// the weight-expansion pass of the matmul path used as the densifier (nmg_gemm_tc.cu)
+bool tc_expand_plain_supported(const Geo &geo, int dtype, const void *dense, int64_t ld);
+int tc_expand_plain(const Geo &geo, int dtype, const void *val, const int16_t *idx, void *dense, int64_t ld, cudaStream_t st);
 int get_status_word(int **dev_ptr);
 int get_wave_counter(unsigned **dev_ptr);  // one of a few rotating 4-byte counters of the current device (spare bytes of the status block)
 // Status word of nmg_spmm_noalloc on device `dev` (start of the built-in scratch array), or NULL before its first call there.

@@ -710,6 +710,19 @@ extern "C" int nmg_densify(const void *val, const int16_t *idx, int64_t batch, i
     if (!dense || !val || !idx) NMG_FAIL(NMG_ERR_INVALID, "dense, val and idx must be non-NULL");
     if (batch < 1 || ld_dense < K || (batch > 1 && batch_stride < M * ld_dense))
         NMG_FAIL(NMG_ERR_INVALID, "bad batch / leading dimension (batch=%lld ld=%lld)", (long long)batch, (long long)ld_dense);
+    cudaStream_t st = (cudaStream_t)stream;
+    // Aligned outputs go through the weight-expansion pass of the matmul path (tiles scattered in shared memory, 16-byte
+    // stores that also write the zeros); the kernel below serves the rest.
+    if (tc_expand_plain_supported(geo, dtype, dense, ld_dense) && (batch == 1 || batch_stride % 8 == 0)) {
+        const size_t es0 = dtype_size(dtype);
+        const int64_t tiles1 = geo.nb * geo.nc;
+        for (int64_t b = 0; b < batch; b++) {
+            const char *vb = static_cast<const char *>(val) + (size_t)b * tiles1 * geo.cc * n * es0;
+            if ((rc = tc_expand_plain(geo, dtype, vb, idx + b * tiles1 * geo.cc, static_cast<char *>(dense) + (size_t)b * batch_stride * es0, ld_dense, st)))
+                return rc;
+        }
+        return NMG_OK;
+    }
     PatternTable tab;
     if ((rc = get_pattern_table(n, m, &tab))) return rc;
 
@@ -725,7 +738,6 @@ extern "C" int nmg_densify(const void *val, const int16_t *idx, int64_t batch, i
     int64_t ctas = p.tiles;
     const int64_t max_ctas = (int64_t)sm_count() * 32;
     if (ctas > max_ctas) ctas = max_ctas;
-    cudaStream_t st = (cudaStream_t)stream;
     NMG_DISPATCH_DTYPE(dtype, T, {
         NMG_CUDA(cudaFuncSetAttribute(densify_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
         densify_kernel<T><<<(unsigned)ctas, 128, smem, st>>>(p);

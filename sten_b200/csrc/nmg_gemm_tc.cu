@@ -37,8 +37,19 @@ __device__ __forceinline__ void split3(float f, __nv_bfloat16 &hi, __nv_bfloat16
 
 // Move `cnt` (1..8) consecutive elements of a shared-memory line to the destination planes and clear them in shared
 // memory.  VEC: cnt == 8 and both sides are 16-byte aligned.
-template <typename T, bool VEC> __device__ __forceinline__ void expand_flush(const ExpandParams &p, T *line, int64_t off, int cnt) {
-    if constexpr (sizeof(T) == 2) {
+// PLAIN (fp32 only): the destination is an fp32 matrix, not three bf16 planes (the densifier's use of this pass).
+template <typename T, bool VEC, bool PLAIN> __device__ __forceinline__ void expand_flush(const ExpandParams &p, T *line, int64_t off, int cnt) {
+    if constexpr (sizeof(T) == 4 && PLAIN) {
+        float *d = static_cast<float *>(p.dst) + off;
+        if (VEC) {
+            *reinterpret_cast<float4 *>(d) = *reinterpret_cast<const float4 *>(line);
+            *reinterpret_cast<float4 *>(d + 4) = *reinterpret_cast<const float4 *>(line + 4);
+            *reinterpret_cast<float4 *>(line) = make_float4(0.f, 0.f, 0.f, 0.f);
+            *reinterpret_cast<float4 *>(line + 4) = make_float4(0.f, 0.f, 0.f, 0.f);
+        } else {
+            for (int i = 0; i < cnt; i++) { d[i] = line[i]; line[i] = 0.f; }
+        }
+    } else if constexpr (sizeof(T) == 2) {
         T *d = static_cast<T *>(p.dst) + off;
         if (VEC) {
             *reinterpret_cast<uint4 *>(d) = *reinterpret_cast<const uint4 *>(line);
@@ -81,7 +92,7 @@ template <typename T, bool VEC> __device__ __forceinline__ void expand_flush(con
 // memory (coalesced reads of val and idx, one thread per slot), and the tile is then moved out with 16-byte accesses
 // that also restore the zeros.
 // N_ = n for the vectorised scatter (1 or 2), 0 for the generic one.
-template <typename T, bool TR, int N_>
+template <typename T, bool TR, int N_, bool PLAIN = false>
 __global__ void __launch_bounds__(EXPAND_THREADS) expand_dense_kernel(const ExpandParams prm) {
     extern __shared__ __align__(16) char smem[];
     constexpr bool VEC_OK = N_ > 0;
@@ -124,11 +135,11 @@ __global__ void __launch_bounds__(EXPAND_THREADS) expand_dense_kernel(const Expa
             // A full vector may run past the item's elements only into the row's padding (last chunk / last group:
             // ld = round_up(extent, 8)), never into elements another item owns.
             if (aligned && (e + 8 <= ne || ne >= elem_lim)) {
-                expand_flush<T, true>(prm, line, off, 8);
+                expand_flush<T, true, PLAIN>(prm, line, off, 8);
             } else {
                 int cnt = ne - e < 8 ? ne - e : 8;
                 if (elem_lim - e < cnt) cnt = (int)(elem_lim - e);
-                expand_flush<T, false>(prm, line, off, cnt);
+                expand_flush<T, false, PLAIN>(prm, line, off, cnt);
                 // elements of the vector past cnt were never written by this item's valid slots; clear them anyway
                 for (int i = cnt; i < 8; i++) line[i] = DT<T>::from_f32(0.f);
             }
@@ -685,22 +696,22 @@ size_t tc_dense_workspace_bytes(const Geo &geo, int dtype, bool transposed) {
     return planes * (size_t)rows * (size_t)dense_ld(red) * 2 + 512;
 }
 
-template <typename T, bool TR, int N_> static int expand_launch_n(const ExpandParams &p, size_t smem, int64_t items, cudaStream_t st) {
+template <typename T, bool TR, int N_, bool PLAIN> static int expand_launch_n(const ExpandParams &p, size_t smem, int64_t items, cudaStream_t st) {
     int dev = 0, sms = 148;
     NMG_CUDA(cudaGetDevice(&dev));
     NMG_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
     const int64_t cap = (int64_t)sms * 16;
-    NMG_CUDA(cudaFuncSetAttribute(expand_dense_kernel<T, TR, N_>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    expand_dense_kernel<T, TR, N_><<<(unsigned)(items < cap ? items : cap), EXPAND_THREADS, smem, st>>>(p);
+    NMG_CUDA(cudaFuncSetAttribute(expand_dense_kernel<T, TR, N_, PLAIN>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    expand_dense_kernel<T, TR, N_, PLAIN><<<(unsigned)(items < cap ? items : cap), EXPAND_THREADS, smem, st>>>(p);
     NMG_CUDA(cudaGetLastError());
     return NMG_OK;
 }
-template <typename T, bool TR> static int expand_launch(const ExpandParams &p, size_t smem, int64_t items, cudaStream_t st) {
+template <typename T, bool TR, bool PLAIN = false> static int expand_launch(const ExpandParams &p, size_t smem, int64_t items, cudaStream_t st) {
     // the vectorised scatter reads 16-byte pieces of val / idx: tile bases are 16-byte aligned when cc is a multiple of 8
     const bool aligned = (reinterpret_cast<uintptr_t>(p.val) & 15) == 0 && (reinterpret_cast<uintptr_t>(p.idx) & 15) == 0;
-    if (aligned && p.n == 1) return expand_launch_n<T, TR, 1>(p, smem, items, st);
-    if (aligned && p.n == 2) return expand_launch_n<T, TR, 2>(p, smem, items, st);
-    return expand_launch_n<T, TR, 0>(p, smem, items, st);
+    if (aligned && p.n == 1) return expand_launch_n<T, TR, 1, PLAIN>(p, smem, items, st);
+    if (aligned && p.n == 2) return expand_launch_n<T, TR, 2, PLAIN>(p, smem, items, st);
+    return expand_launch_n<T, TR, 0, PLAIN>(p, smem, items, st);
 }
 
 template <typename T, bool PAIR, bool TMA_OUT> static int gemm_launch_as(const GemmParams &p, const GemmMaps &maps, cudaStream_t st) {
@@ -738,16 +749,18 @@ bool tc_dense_uses_pair(const Geo &geo, int dtype, bool transposed) {
     return dtype != NMG_F32 && (transposed ? geo.K : geo.M) > TC_BM;
 }
 
-// (val, idx) -> dense 16-bit weight (three bf16 planes for fp32) at `dense` (256-byte aligned, tc_dense_workspace_bytes).
-int tc_dense_expand(const Geo &geo, int dtype, bool transposed, const void *val, const int16_t *idx, char *dense, cudaStream_t st) {
-    const int64_t rows = transposed ? geo.K : geo.M, red = transposed ? geo.M : geo.K;
-    const int64_t ld = dense_ld(red);
+// (val, idx) -> the weight with its zeros restored, rows `ld` elements apart at `dst` (16-byte aligned, ld a multiple of 8).
+// plain = false: the matmul's operand, 16-bit or three bf16 planes for fp32 (plane_rows rows each); plain = true: the
+// weight in its own dtype (the densifier), where full 8-element stores must not run past the row: K a multiple of 8.
+static int expand_to(const Geo &geo, int dtype, bool transposed, bool plain, const void *val, const int16_t *idx, void *dst, int64_t ld,
+                     cudaStream_t st) {
+    const int64_t rows = transposed ? geo.K : geo.M;
     const size_t es = dtype == NMG_F32 ? 4 : 2;
     int rc;
     PatternTable tab;
     if ((rc = get_pattern_table(geo.n, geo.m, &tab))) return rc;
     ExpandParams ep{};
-    ep.val = val; ep.idx = idx; ep.order = tab.order; ep.dst = dense;
+    ep.val = val; ep.idx = idx; ep.order = tab.order; ep.dst = dst;
     ep.ld = ld; ep.plane_elems = rows * ld;
     ep.M = geo.M; ep.K = geo.K; ep.nb = geo.nb; ep.nc = geo.nc;
     ep.n = geo.n; ep.m = geo.m; ep.g = geo.g; ep.C = geo.C; ep.cc = geo.cc;
@@ -758,7 +771,22 @@ int tc_dense_expand(const Geo &geo, int dtype, bool transposed, const void *val,
     const int64_t items = ((geo.nb + ep.R - 1) / ep.R) * geo.nc;
     if (dtype == NMG_F16) return transposed ? expand_launch<__half, true>(ep, esmem, items, st) : expand_launch<__half, false>(ep, esmem, items, st);
     if (dtype == NMG_BF16) return transposed ? expand_launch<__nv_bfloat16, true>(ep, esmem, items, st) : expand_launch<__nv_bfloat16, false>(ep, esmem, items, st);
+    if (plain) return expand_launch<float, false, true>(ep, esmem, items, st);
     return transposed ? expand_launch<float, true>(ep, esmem, items, st) : expand_launch<float, false>(ep, esmem, items, st);
+}
+
+int tc_dense_expand(const Geo &geo, int dtype, bool transposed, const void *val, const int16_t *idx, char *dense, cudaStream_t st) {
+    return expand_to(geo, dtype, transposed, false, val, idx, dense, dense_ld(transposed ? geo.M : geo.K), st);
+}
+
+// The densifier through the expansion pass: whole tiles are scattered into shared memory and leave as 16-byte stores.
+bool tc_expand_plain_supported(const Geo &geo, int dtype, const void *dense, int64_t ld) {
+    const size_t es = dtype == NMG_F32 ? 4 : 2;
+    if (geo.cc > 32767 || geo.C > 65535 || geo.K % 8 != 0 || ld % 8 != 0 || (reinterpret_cast<uintptr_t>(dense) & 15) != 0) return false;
+    return expand_smem_bytes(geo, es, false, expand_rows_per_item(geo, es, false)) <= 200 * 1024;
+}
+int tc_expand_plain(const Geo &geo, int dtype, const void *val, const int16_t *idx, void *dense, int64_t ld, cudaStream_t st) {
+    return expand_to(geo, dtype, false, true, val, idx, dense, ld, st);
 }
 
 // out = dense[rows][round_up(red, 8)] (16-bit, or three bf16 planes for fp32) x activations.  act_maps: tensor maps of the
