@@ -26,6 +26,23 @@ namespace nmg {
 // lane + 32, ...) when patterns merge their proposers.  The tile is read with 16-byte loads where alignment allows.
 // =====================================================================================================
 
+// (row-block, column chunk, batch entry) of a tile; 32-bit division whenever the tile count allows it (a 64-bit division
+// costs about as much as scoring a column).
+__device__ __forceinline__ void tile_coords(int64_t tile, int64_t nb, int64_t nc, int64_t tiles, int64_t &mb, int64_t &kc, int64_t &b) {
+    if (tiles < 0x7fffffffll) {
+        const unsigned t = (unsigned)tile, unb = (unsigned)nb, unc = (unsigned)nc;
+        const unsigned q = t / unb;
+        mb = t - q * unb;
+        const unsigned q2 = q / unc;
+        kc = q - q2 * unc;
+        b = q2;
+    } else {
+        mb = tile % nb;
+        kc = (tile / nb) % nc;
+        b = tile / (nb * nc);
+    }
+}
+
 struct SparsifyParams {
     const void *dense;
     void *val;
@@ -134,7 +151,8 @@ __global__ void __launch_bounds__(256) sparsify_kernel(SparsifyParams prm) {
     const int pchunk = (C + 31) / 32;  // patterns per lane in the prefix sum
 
     for (int64_t tile = (int64_t)blockIdx.x * nwarps + warp; tile < prm.tiles; tile += (int64_t)gridDim.x * nwarps) {
-        const int64_t mb = tile % prm.nb, kc = (tile / prm.nb) % prm.nc, b = tile / (prm.nb * prm.nc);
+        int64_t mb, kc, b;
+        tile_coords(tile, prm.nb, prm.nc, prm.tiles, mb, kc, b);
         const int64_t row0 = mb * m, col0 = kc * cc;
         const T *src = dense + b * prm.batch_stride;
         // ---- load the tile (rows beyond M and columns beyond K read as zero)
@@ -298,7 +316,8 @@ __global__ void __launch_bounds__(256, 4) sparsify_nm_kernel(SparsifyParams prm)
     auto above = [](uint32_t s1, int c1, uint32_t s2, int c2) { return s1 > s2 || (s1 == s2 && c1 > c2); };
 
     for (int64_t tile = (int64_t)blockIdx.x * nwarps + warp; tile < prm.tiles; tile += (int64_t)gridDim.x * nwarps) {
-        const int64_t mb = tile % prm.nb, kc = (tile / prm.nb) % prm.nc, b = tile / (prm.nb * prm.nc);
+        int64_t mb, kc, b;
+        tile_coords(tile, prm.nb, prm.nc, prm.tiles, mb, kc, b);
         const int64_t row0 = mb * M_, col0 = kc * cc;
         const T *src = dense + b * prm.batch_stride + row0 * prm.ld + col0;  // element (r, c) of the tile at src[r * ld + c]
         const int rows_ok = (int)(prm.M - row0 < M_ ? prm.M - row0 : M_);    // rows beyond M and columns beyond K read as zero
@@ -508,7 +527,8 @@ __global__ void __launch_bounds__(128) densify_kernel(DensifyParams prm) {
     const T *val = static_cast<const T *>(prm.val);
     T *dense = static_cast<T *>(prm.dense);
     for (int64_t tile = blockIdx.x; tile < prm.tiles; tile += gridDim.x) {
-        const int64_t mb = tile % prm.nb, kc = (tile / prm.nb) % prm.nc, b = tile / (prm.nb * prm.nc);
+        int64_t mb, kc, b;
+        tile_coords(tile, prm.nb, prm.nc, prm.tiles, mb, kc, b);
         __syncthreads();
         for (int c = threadIdx.x; c < cc; c += blockDim.x) pos[c] = -1;
         constexpr int V = 16 / (int)sizeof(T);  // elements per 16-byte access
@@ -600,7 +620,8 @@ __global__ void __launch_bounds__(256) gather_layout_kernel(GatherParams prm) {
     const T *dense = static_cast<const T *>(prm.dense);
     T *val = static_cast<T *>(prm.val);
     for (int64_t tile = (int64_t)blockIdx.x * nwarps + warp; tile < prm.tiles; tile += (int64_t)gridDim.x * nwarps) {
-        const int64_t mb = tile % prm.nb, kc = (tile / prm.nb) % prm.nc, b = tile / (prm.nb * prm.nc);
+        int64_t mb, kc, b;
+        tile_coords(tile, prm.nb, prm.nc, prm.tiles, mb, kc, b);
         const T *src = dense + b * prm.batch_stride;
         const int16_t *isrc = prm.idx + tile * cc;
         T *vdst = val + tile * (int64_t)cc * n;
