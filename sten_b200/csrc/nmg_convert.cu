@@ -348,20 +348,23 @@ __global__ void __launch_bounds__(256, 4) sparsify_nm_kernel(SparsifyParams prm)
                 uint32_t best_s = 0;  // a score of zero never wins: zero scores are placed by the closed form after the rounds
                 int best_p = -1;
                 if (full_mask == 0) {  // first round(s): every pattern is open, nothing but registers
+                    // the sum starts from the first value (0 + x = x exactly for x >= 0) and zero scores are sorted out once,
+                    // after the scan: a zero maximum means that every score of the column is zero
 #pragma unroll
                     for (int p = 0; p < C; p++) {
-                        float sc = 0.f;
+                        float sc = a[ORD.row(p, 0)];
 #pragma unroll
-                        for (int i = 0; i < N_; i++) sc = __fadd_rn(sc, a[ORD.row(p, i)]);
+                        for (int i = 1; i < N_; i++) sc = __fadd_rn(sc, a[ORD.row(p, i)]);
                         const uint32_t sb = __float_as_uint(sc);
-                        if (sb != 0 && sb >= best_s) { best_s = sb; best_p = p; }
+                        if (sb >= best_s) { best_s = sb; best_p = p; }
                     }
+                    if (best_s == 0) best_p = -1;
                 } else {
 #pragma unroll
                     for (int p = 0; p < C; p++) {
-                        float sc = 0.f;
+                        float sc = a[ORD.row(p, 0)];
 #pragma unroll
-                        for (int i = 0; i < N_; i++) sc = __fadd_rn(sc, a[ORD.row(p, i)]);
+                        for (int i = 1; i < N_; i++) sc = __fadd_rn(sc, a[ORD.row(p, i)]);
                         const uint32_t sb = __float_as_uint(sc);
                         bool open = sb != 0 && sb >= best_s;
                         // full pattern: only a proposer that ranks above its weakest kept one gets in
