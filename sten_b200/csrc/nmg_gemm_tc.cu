@@ -383,6 +383,9 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_tc_kernel(const GemmPara
         char *stage_w = staging + (warp - 2) * 4096;
         const T *res = static_cast<const T *>(prm.residual);
         const bool gelu = prm.act == NMG_EPI_GELU;
+        // The bias and the residual are read with ordinary loads, possibly before the first accumulator is ready: like the
+        // producer's loads they must not run ahead of the grid this one was launched behind.
+        asm volatile("griddepcontrol.wait;" ::: "memory");
         int unit = 0;
         bool ok = true;
         for (int ti = 0; ti < my_tiles && ok; ti++) {
